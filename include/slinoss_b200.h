@@ -1,0 +1,218 @@
+/*
+ * slinoss_b200 - C ABI of the B200 (sm_100a) v2x2ssd scan and its mixer hot path.
+ *
+ * Every entry point
+ *   - is `extern "C"`, takes plain device pointers, sizes, a dtype code and a
+ *     CUDA stream handle (`cudaStream_t` passed as `void*`), and returns an
+ *     `int` status (SL_OK == 0); no exception crosses the boundary;
+ *   - launches on the given stream and returns without synchronising;
+ *   - allocates nothing: scratch memory is supplied by the caller
+ *     (`sl_workspace_bytes` gives the size), so calls are CUDA-graph friendly;
+ *   - validates shapes / alignment on the host before any launch.
+ *
+ * Tensor layouts are the reference's canonical ones
+ * (slinoss/ops/v2x2ssd/reference.py:11-28):
+ *   U, Y      (batch, heads, T, P)
+ *   M         (batch, heads, T, 2)        packed complex (re, im), float32
+ *   K         (batch, heads, T, 2, 2)     tap 0 = prev, tap 1 = curr, float32
+ *   B, C      (batch, groups, T, 2N)      interleaved (re, im); groups | heads
+ *   state     (batch, heads, P, 2N)       float32
+ *   B_prev    (batch, groups, 2N),  U_prev (batch, heads, P)
+ * All tensors are dense (contiguous) unless a stride argument says otherwise.
+ */
+#ifndef SLINOSS_B200_H_
+#define SLINOSS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SL_API __attribute__((visibility("default")))
+#else
+#define SL_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+  SL_OK = 0,
+  SL_ERR_NULL_POINTER = 1,
+  SL_ERR_BAD_SHAPE = 2,
+  SL_ERR_BAD_ALIGNMENT = 3,
+  SL_ERR_UNSUPPORTED = 4,
+  SL_ERR_WORKSPACE_TOO_SMALL = 5,
+  SL_ERR_LAUNCH_FAILED = 6,
+  SL_ERR_DEVICE_TIMEOUT = 7
+};
+
+/* element types of the "io" tensors (U, B, C, Y, their gradients, gate, ...) */
+enum { SL_F32 = 0, SL_BF16 = 1, SL_F16 = 2 };
+
+/* kernel family selector for the scan */
+enum {
+  SL_PATH_AUTO = 0, /* tensor-core path when the shape allows, else SIMT */
+  SL_PATH_SIMT = 1, /* exact float32 sequential recurrence (any dtype in)     */
+  SL_PATH_TC = 2    /* tcgen05/TMEM chunked path (bf16 / fp16 operands)       */
+};
+
+/* workspace kinds for sl_workspace_bytes */
+enum {
+  SL_WS_SCAN_FWD = 0,
+  SL_WS_SCAN_BWD = 1,
+  SL_WS_SCANPREP_BWD = 2,
+  SL_WS_TAIL_BWD = 3
+};
+
+/* Library version, major*10000 + minor*100 + patch. */
+SL_API int sl_version(void);
+
+/* Static, human readable text of a status code. */
+SL_API const char* sl_status_string(int status);
+
+/* Scratch bytes a call of the given kind needs for these dimensions
+ * (0 when none).  `path` is one of SL_PATH_*.  For SL_WS_SCANPREP_BWD and
+ * SL_WS_TAIL_BWD only batch, heads, groups, T, P, N are read. */
+SL_API size_t sl_workspace_bytes(int kind, int batch, int heads, int groups, int T, int P, int N,
+                          int chunk, int io_dtype, int path);
+
+/*
+ * Scan forward.  Replaces slinoss.ops.v2x2ssd.v2x2ssd_cute
+ * (slinoss/ops/v2x2ssd/cute/api.py:53-200; semantics = v2x2ssd,
+ * slinoss/ops/v2x2ssd/reference.py:1267-1347).
+ *   U, B, C, B_prev, U_prev : io_dtype;  Y : y_dtype;  M, K, states : float32.
+ *   initial_states, B_prev, U_prev, final_state may be NULL (B_prev and U_prev
+ *   together).  T must be >= 1 (T == 0 is answered by the host wrapper).
+ */
+SL_API int sl_v2x2ssd_fwd(const void* U, const float* M, const float* K, const void* B, const void* C,
+                   const float* initial_states, const void* B_prev, const void* U_prev,
+                   void* Y, float* final_state, int batch, int heads, int groups, int T, int P,
+                   int N, int chunk, int io_dtype, int y_dtype, int path, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
+ * Scan backward.  Replaces _V2x2SSDCuTeTrainingFn.backward
+ * (slinoss/ops/v2x2ssd/cute/autograd.py:148-296).
+ *   dY : dy_dtype (NULL = zero);  d_final_state : float32 or NULL.
+ *   dU, dB, dC, dB_prev, dU_prev : io_dtype;  dM, dK, d_initial : float32.
+ *   d_initial, dB_prev, dU_prev may be NULL.  Grouped dB/dC/dB_prev are summed
+ *   over the heads of a group in float32 before the cast.
+ */
+SL_API int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
+                   const float* initial_states, const void* B_prev, const void* U_prev,
+                   const void* dY, const float* d_final_state, void* dU, float* dM, float* dK,
+                   void* dB, void* dC, float* d_initial, void* dB_prev, void* dU_prev,
+                   int batch, int heads, int groups, int T, int P, int N, int chunk,
+                   int io_dtype, int dy_dtype, int path, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
+ * One-token decode of the scan (T = 1) over the carried float32 state.
+ * Replaces the v2x2ssm(T=1) call of run_reference_decode_step
+ * (slinoss/ops/mixer/step.py:201-258) and the scan part of
+ * mixer_decode_step_cute (slinoss/ops/v2x2ssd/cute/step.py:224-627).
+ *   U (batch,heads,P), B,C (batch,groups,2N), B_prev (batch,groups,2N),
+ *   U_prev (batch,heads,P) : io_dtype;  M (batch,heads,2), K (batch,heads,2,2),
+ *   state_in/state_out (batch,heads,P,2N) : float32;  Y (batch,heads,P) : y_dtype.
+ *   state_out may alias state_in (in-place update).  B_prev/U_prev may be NULL
+ *   (zeros).  The caller carries B -> B_prev and U -> U_prev itself.
+ */
+SL_API int sl_v2x2ssd_decode(const void* U, const float* M, const float* K, const void* B,
+                      const void* C, const float* state_in, const void* B_prev,
+                      const void* U_prev, void* Y, float* state_out, int batch, int heads,
+                      int groups, int P, int N, int io_dtype, int y_dtype, void* stream);
+
+/* Scalar configuration of scan preparation (slinoss/layers/scanprep.py:41-58). */
+typedef struct {
+  float dt_min, dt_max;
+  float alpha_min, alpha_max;
+  float theta_init_min, theta_init_max, theta_mod_scale;
+  float r_min, r_max;
+  float eps;
+} sl_scanprep_config;
+
+/*
+ * Fused causal depthwise conv1d + bias + SiLU + scan preparation, forward.
+ * Replaces cconv1d_fwd (csrc/causal_conv1d/causal_conv1d.cpp:559, through
+ * slinoss/ops/mixer/convolution.py:104-173) followed by scanprep_cute
+ * (slinoss/ops/scanprep/cute/api.py:88; math of slinoss/layers/scanprep.py:237-283
+ * and slinoss/ops/scanprep/parameterization.py:60-107).
+ *   value  (batch, T, heads*P), row stride `value_row_stride` elements
+ *   conv_weight (heads*P, d_conv), conv_bias (heads*P) : io_dtype; d_conv in 1..4;
+ *          conv_weight == NULL skips the convolution (value is only re-laid out)
+ *   conv_state_in  (batch, heads*P, d_conv-1) or NULL (zeros) : io_dtype
+ *   conv_state_out (batch, heads*P, d_conv-1) or NULL
+ *   params (batch, T, heads*3) : io_dtype;  bc (batch, T, groups, 4, N) : io_dtype
+ *   dt_bias, alpha_bias, theta_mod_bias, theta_bias, theta_sign (heads) : float32
+ *   U out: element (b,h,t,p) at b*u_stride_b + h*u_stride_h + t*u_stride_t + p
+ *          ((batch,heads,T,P) dense, or (batch,T,heads*P) for a conv-only call)
+ *   M (batch,heads,T,2), K (batch,heads,T,2,2) : float32;  Bo, Co (batch,groups,T,2N).
+ *   Any of {params,M,K} / {bc,Bo,Co} / {value,U} may be NULL as a set to skip it.
+ */
+SL_API int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride, const void* conv_weight,
+                         const void* conv_bias, const void* conv_state_in,
+                         void* conv_state_out, int d_conv, const void* params, const void* bc,
+                         const float* dt_bias, const float* alpha_bias,
+                         const float* theta_mod_bias, const float* theta_bias,
+                         const float* theta_sign, const sl_scanprep_config* cfg, void* U,
+                         int64_t u_stride_b, int64_t u_stride_h, int64_t u_stride_t, float* M,
+                         float* K, void* Bo, void* Co, int batch, int heads, int groups, int T,
+                         int P, int N, int io_dtype, void* stream);
+
+/*
+ * Backward of sl_scanprep_conv_fwd.  Replaces cconv1d_bwd
+ * (csrc/causal_conv1d/causal_conv1d.cpp:560) and the scanprep backward kernels
+ * (slinoss/ops/scanprep/cute/kernels/bwd.py:79-915).
+ *   dU laid out by the same u_stride_* as U; dM, dK float32; dBo, dCo io_dtype.
+ *   Outputs: d_value (batch,T,heads*P) dense io_dtype; d_conv_weight
+ *   (heads*P,d_conv), d_conv_bias (heads*P), d_conv_state (batch,heads*P,d_conv-1
+ *   or NULL), d_params (batch,T,3*heads), d_bc like bc : io_dtype except the
+ *   float32 accumulators d_conv_weight/d_conv_bias/d_*_bias (heads), which this
+ *   call ACCUMULATES into (caller zeroes them).
+ */
+SL_API int sl_scanprep_conv_bwd(const void* value, int64_t value_row_stride, const void* conv_weight,
+                         const void* conv_bias, const void* conv_state_in, int d_conv,
+                         const void* params, const void* bc, const float* dt_bias,
+                         const float* alpha_bias, const float* theta_mod_bias,
+                         const float* theta_bias, const float* theta_sign,
+                         const sl_scanprep_config* cfg, const void* dU, int64_t u_stride_b,
+                         int64_t u_stride_h, int64_t u_stride_t, const float* dM,
+                         const float* dK, const void* dBo, const void* dCo, void* d_value,
+                         float* d_conv_weight, float* d_conv_bias, void* d_conv_state,
+                         void* d_params, void* d_bc, float* d_dt_bias, float* d_alpha_bias,
+                         float* d_theta_mod_bias, float* d_theta_bias, int batch, int heads,
+                         int groups, int T, int P, int N, int io_dtype, void* stream);
+
+/*
+ * Mixer tail, row-wise part: normed = RMSNorm((Y + d_skip*U) * SiLU(gate)) * w.
+ * Replaces MixerTailRowwiseFwdFused (slinoss/ops/mixer/cute/fwd.py:64-205; math of
+ * slinoss/ops/mixer/tail.py:63-142).  out_proj stays a library GEMM in the caller.
+ *   Y, skip (batch,heads,T,P) : io_dtype (skip/d_skip may be NULL together)
+ *   gate (batch,T,heads*P) with row stride `gate_row_stride` elements : io_dtype
+ *   d_skip (heads) float32;  norm_weight (heads*P) : io_dtype
+ *   normed (batch,T,heads*P) dense : io_dtype
+ */
+SL_API int sl_mixer_tail_fwd(const void* Y, const void* gate, int64_t gate_row_stride,
+                      const void* skip, const float* d_skip, const void* norm_weight,
+                      float eps, void* normed, int batch, int heads, int T, int P,
+                      int io_dtype, void* stream);
+
+/*
+ * Backward of sl_mixer_tail_fwd.  Replaces MixerTailRowwiseBwdFused
+ * (slinoss/ops/mixer/cute/bwd.py:73-260).
+ *   d_normed (batch,T,heads*P) dense.  Outputs dY, d_skip_input (batch,heads,T,P),
+ *   d_gate (batch,T,heads*P) dense : io_dtype;  d_d_skip (heads) and
+ *   d_norm_weight (heads*P) float32, ACCUMULATED into (caller zeroes them).
+ */
+SL_API int sl_mixer_tail_bwd(const void* Y, const void* gate, int64_t gate_row_stride,
+                      const void* skip, const float* d_skip, const void* norm_weight,
+                      float eps, const void* d_normed, void* dY, void* d_gate,
+                      void* d_skip_input, float* d_d_skip, float* d_norm_weight, int batch,
+                      int heads, int T, int P, int io_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLINOSS_B200_H_ */

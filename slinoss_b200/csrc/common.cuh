@@ -1,0 +1,90 @@
+// Shared device/host helpers for the slinoss_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/slinoss_b200.h"
+
+namespace sl {
+
+// ---- element access in float32 -------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) {
+  // saturate to the finite range like the reference's output cast
+  v = fminf(fmaxf(v, -65504.f), 65504.f);
+  return __float2half_rn(v);
+}
+
+struct cf {  // complex float
+  float re, im;
+};
+__device__ __forceinline__ cf cmul(cf a, cf b) {
+  return {a.re * b.re - a.im * b.im, a.re * b.im + a.im * b.re};
+}
+__device__ __forceinline__ cf cmul_conj_a(cf a, cf b) {  // conj(a) * b
+  return {a.re * b.re + a.im * b.im, a.re * b.im - a.im * b.re};
+}
+__device__ __forceinline__ cf cadd(cf a, cf b) { return {a.re + b.re, a.im + b.im}; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// ---- host side -----------------------------------------------------------------
+inline size_t dtype_size(int dt) { return dt == SL_F32 ? 4 : 2; }
+inline bool dtype_ok(int dt) { return dt == SL_F32 || dt == SL_BF16 || dt == SL_F16; }
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+inline int launch_status() {
+  return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_LAUNCH_FAILED;
+}
+
+// Dispatch a callable templated on the io element type.
+#define SL_DISPATCH_DTYPE(dt, T, ...)                         \
+  do {                                                        \
+    if ((dt) == SL_F32) {                                     \
+      using T = float;                                        \
+      __VA_ARGS__;                                            \
+    } else if ((dt) == SL_BF16) {                             \
+      using T = __nv_bfloat16;                                \
+      __VA_ARGS__;                                            \
+    } else {                                                  \
+      using T = __half;                                       \
+      __VA_ARGS__;                                            \
+    }                                                         \
+  } while (0)
+
+// ---- internal entry points implemented in the other translation units ----------
+struct ScanDims {
+  int batch, heads, groups, T, P, N, chunk;
+};
+
+int scan_simt_fwd(const void* U, const float* M, const float* K, const void* B, const void* C,
+                  const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
+                  const ScanDims& d, int io_dtype, int y_dtype, cudaStream_t st);
+size_t scan_simt_bwd_workspace(const ScanDims& d);
+int scan_simt_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
+                  const float* z0, const void* Bprev, const void* Uprev, const void* dY,
+                  const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC,
+                  float* dinit, void* dBprev, void* dUprev, const ScanDims& d, int io_dtype,
+                  int dy_dtype, void* ws, size_t ws_bytes, cudaStream_t st);
+bool scan_simt_supported(const ScanDims& d);
+
+}  // namespace sl

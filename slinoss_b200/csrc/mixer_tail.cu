@@ -1,0 +1,205 @@
+// Row-wise part of the mixer tail: skip connection, SiLU gate and RMSNorm.
+//
+//   pre    = Y + d_skip[h] * U                 (float32, rounded to the io dtype)
+//   hidden = pre * SiLU(gate)                  (float32, rounded to the io dtype)
+//   normed = hidden * rsqrt(mean(hidden^2) + eps) * w
+//
+// Reference: slinoss/ops/mixer/tail.py:63-142 (the roundings above are the ones
+// the reference makes between its steps).  One CTA owns one (batch, token) row of
+// heads*P channels; Y and U are read in their (batch, heads, T, P) layout and the
+// result is written channel-last, ready for the out_proj GEMM.
+#include "common.cuh"
+
+namespace sl {
+namespace {
+
+constexpr int TAIL_THREADS = 256;
+constexpr int TAIL_MAX_PER_THREAD = 16;  // channels <= 4096
+
+template <typename T>
+__device__ __forceinline__ float round_io(float v) { return to_f32(from_f32<T>(v)); }
+
+__device__ __forceinline__ float block_sum(float v, float* s_red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) s_red[w] = v;
+  __syncthreads();
+  float s = 0.f;
+  for (int k = 0; k < (int)(blockDim.x >> 5); ++k) s += s_red[k];
+  return s;
+}
+
+struct TailParams {
+  const void *Y, *gate, *skip, *w, *dn;
+  const float* d_skip;
+  void *normed, *dY, *dgate, *dskip_in;
+  float *d_d_skip, *d_w;
+  int64_t gs;
+  float eps;
+  int batch, H, T, P;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(TAIL_THREADS) tail_fwd_kernel(TailParams p) {
+  __shared__ float s_red[TAIL_THREADS / 32];
+  const int C = p.H * p.P;
+  const T* Y = reinterpret_cast<const T*>(p.Y);
+  const T* S = reinterpret_cast<const T*>(p.skip);
+  const T* gate = reinterpret_cast<const T*>(p.gate);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  T* out = reinterpret_cast<T*>(p.normed);
+  for (long long row = blockIdx.x; row < (long long)p.batch * p.T; row += gridDim.x) {
+    const int t = (int)(row % p.T), b = (int)(row / p.T);
+    float hid[TAIL_MAX_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < TAIL_MAX_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * TAIL_THREADS;
+      hid[i] = 0.f;
+      if (c < C) {
+        const int h = c / p.P, pp = c - h * p.P;
+        const size_t yi = (((size_t)b * p.H + h) * p.T + t) * p.P + pp;
+        float pre = to_f32(Y[yi]);
+        if (S) pre = round_io<T>(pre + to_f32(S[yi]) * p.d_skip[h]);
+        const float g = to_f32(gate[(size_t)row * p.gs + c]);
+        hid[i] = round_io<T>(pre * silu_f(g));
+        ss += hid[i] * hid[i];
+      }
+    }
+    ss = block_sum(ss, s_red);
+    const float rstd = rsqrtf(ss / (float)C + p.eps);
+#pragma unroll
+    for (int i = 0; i < TAIL_MAX_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * TAIL_THREADS;
+      if (c < C) out[(size_t)row * C + c] = from_f32<T>(hid[i] * rstd * to_f32(w[c]));
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_kernel(TailParams p) {
+  __shared__ float s_red[TAIL_THREADS / 32];
+  extern __shared__ float s_dskip[];  // H floats
+  const int C = p.H * p.P;
+  const T* Y = reinterpret_cast<const T*>(p.Y);
+  const T* S = reinterpret_cast<const T*>(p.skip);
+  const T* gate = reinterpret_cast<const T*>(p.gate);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const T* dn = reinterpret_cast<const T*>(p.dn);
+  T* dY = reinterpret_cast<T*>(p.dY);
+  T* dgate = reinterpret_cast<T*>(p.dgate);
+  T* dS = reinterpret_cast<T*>(p.dskip_in);
+  float dw_acc[TAIL_MAX_PER_THREAD];
+#pragma unroll
+  for (int i = 0; i < TAIL_MAX_PER_THREAD; ++i) dw_acc[i] = 0.f;
+  for (int i = threadIdx.x; i < p.H; i += blockDim.x) s_dskip[i] = 0.f;
+  __syncthreads();
+  for (long long row = blockIdx.x; row < (long long)p.batch * p.T; row += gridDim.x) {
+    const int t = (int)(row % p.T), b = (int)(row / p.T);
+    float hid[TAIL_MAX_PER_THREAD], gw[TAIL_MAX_PER_THREAD];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < TAIL_MAX_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * TAIL_THREADS;
+      hid[i] = gw[i] = 0.f;
+      if (c < C) {
+        const int h = c / p.P, pp = c - h * p.P;
+        const size_t yi = (((size_t)b * p.H + h) * p.T + t) * p.P + pp;
+        float pre = to_f32(Y[yi]);
+        if (S) pre = round_io<T>(pre + to_f32(S[yi]) * p.d_skip[h]);
+        const float g = to_f32(gate[(size_t)row * p.gs + c]);
+        hid[i] = round_io<T>(pre * silu_f(g));
+        gw[i] = to_f32(dn[(size_t)row * C + c]) * to_f32(w[c]);
+        ss += hid[i] * hid[i];
+        dot += hid[i] * gw[i];
+      }
+    }
+    ss = block_sum(ss, s_red);
+    dot = block_sum(dot, s_red);
+    const float rstd = rsqrtf(ss / (float)C + p.eps);
+    const float coef = dot * rstd * rstd * rstd / (float)C;
+#pragma unroll
+    for (int i = 0; i < TAIL_MAX_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * TAIL_THREADS;
+      if (c < C) {
+        const int h = c / p.P, pp = c - h * p.P;
+        const size_t yi = (((size_t)b * p.H + h) * p.T + t) * p.P + pp;
+        const float dnv = to_f32(dn[(size_t)row * C + c]);
+        dw_acc[i] += dnv * hid[i] * rstd;
+        const float dh = rstd * gw[i] - hid[i] * coef;
+        float pre = to_f32(Y[yi]);
+        float sv = 0.f;
+        if (S) { sv = to_f32(S[yi]); pre = round_io<T>(pre + sv * p.d_skip[h]); }
+        const float g = to_f32(gate[(size_t)row * p.gs + c]);
+        const float sg = sigmoid_f(g);
+        const float dpre = dh * g * sg;
+        dgate[(size_t)row * C + c] = from_f32<T>(dh * pre * sg * (1.f + g * (1.f - sg)));
+        dY[yi] = from_f32<T>(dpre);
+        if (S) {
+          if (dS) dS[yi] = from_f32<T>(dpre * p.d_skip[h]);
+          atomicAdd(&s_dskip[h], dpre * sv);
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < TAIL_MAX_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * TAIL_THREADS;
+    if (c < C) atomicAdd(p.d_w + c, dw_acc[i]);
+  }
+  if (S && p.d_d_skip)
+    for (int i = threadIdx.x; i < p.H; i += blockDim.x) atomicAdd(p.d_d_skip + i, s_dskip[i]);
+}
+
+int tail_check(const void* Y, const void* gate, const void* skip, const float* d_skip,
+               const void* w, int batch, int heads, int T, int P, int io_dtype) {
+  if (!Y || !gate || !w) return SL_ERR_NULL_POINTER;
+  if ((skip == nullptr) != (d_skip == nullptr)) return SL_ERR_NULL_POINTER;
+  if (batch < 1 || heads < 1 || T < 1 || P < 1) return SL_ERR_BAD_SHAPE;
+  if ((long long)heads * P > (long long)TAIL_THREADS * TAIL_MAX_PER_THREAD) return SL_ERR_UNSUPPORTED;
+  if (!dtype_ok(io_dtype)) return SL_ERR_UNSUPPORTED;
+  return SL_OK;
+}
+
+}  // namespace
+}  // namespace sl
+
+extern "C" int sl_mixer_tail_fwd(const void* Y, const void* gate, int64_t gate_row_stride,
+                                 const void* skip, const float* d_skip, const void* norm_weight,
+                                 float eps, void* normed, int batch, int heads, int T, int P,
+                                 int io_dtype, void* stream) {
+  using namespace sl;
+  if (int e = tail_check(Y, gate, skip, d_skip, norm_weight, batch, heads, T, P, io_dtype)) return e;
+  if (!normed) return SL_ERR_NULL_POINTER;
+  TailParams p{};
+  p.Y = Y; p.gate = gate; p.skip = skip; p.w = norm_weight; p.d_skip = d_skip; p.normed = normed;
+  p.gs = gate_row_stride; p.eps = eps; p.batch = batch; p.H = heads; p.T = T; p.P = P;
+  const long long rows = (long long)batch * T;
+  const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  SL_DISPATCH_DTYPE(io_dtype, Tt, { tail_fwd_kernel<Tt><<<grid, TAIL_THREADS, 0, st>>>(p); });
+  return launch_status();
+}
+
+extern "C" int sl_mixer_tail_bwd(const void* Y, const void* gate, int64_t gate_row_stride,
+                                 const void* skip, const float* d_skip, const void* norm_weight,
+                                 float eps, const void* d_normed, void* dY, void* d_gate,
+                                 void* d_skip_input, float* d_d_skip, float* d_norm_weight,
+                                 int batch, int heads, int T, int P, int io_dtype, void* stream) {
+  using namespace sl;
+  if (int e = tail_check(Y, gate, skip, d_skip, norm_weight, batch, heads, T, P, io_dtype)) return e;
+  if (!d_normed || !dY || !d_gate || !d_norm_weight) return SL_ERR_NULL_POINTER;
+  TailParams p{};
+  p.Y = Y; p.gate = gate; p.skip = skip; p.w = norm_weight; p.d_skip = d_skip; p.dn = d_normed;
+  p.dY = dY; p.dgate = d_gate; p.dskip_in = d_skip_input; p.d_d_skip = d_d_skip;
+  p.d_w = d_norm_weight; p.gs = gate_row_stride; p.eps = eps;
+  p.batch = batch; p.H = heads; p.T = T; p.P = P;
+  const long long rows = (long long)batch * T;
+  const unsigned grid = (unsigned)(rows < 148 * 4 ? rows : 148 * 4);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)heads * sizeof(float);
+  SL_DISPATCH_DTYPE(io_dtype, Tt, { tail_bwd_kernel<Tt><<<grid, TAIL_THREADS, smem, st>>>(p); });
+  return launch_status();
+}

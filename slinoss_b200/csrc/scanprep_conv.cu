@@ -1,0 +1,493 @@
+// Scan preparation fused with the causal depthwise conv1d + SiLU of the value stream.
+//
+// Forward (one C-ABI call, three coalesced elementwise kernels on one stream):
+//   value kernel  out[b,t,c] = SiLU(bias_c + sum_j W[c,j] x[b,t-(d_conv-1)+j,c]) written
+//                 straight into the (batch,heads,T,P) layout of U
+//                 (reference: slinoss/ops/mixer/convolution.py:68-101 followed by the
+//                 transpose of slinoss/layers/scanprep.py:307-321)
+//   bc kernel     amplitude = softplus, phase = pi*tanh, pair = amp*(cos,sin)/rms_n(amp)
+//                 (slinoss/ops/scanprep/parameterization.py:45-107)
+//   coeff kernel  dt/alpha/theta maps, rho = r e^{i theta}, exact first-order-hold taps
+//                 (slinoss/layers/scanprep.py:237-283, slinoss/ops/scanprep/reference.py:25-56)
+// The tap formulas cancel catastrophically in float32 for small |z| (the
+// numerator of kappa2 loses ~1/|z|^2 ulps), so the coefficient kernels evaluate them
+// in float64; the count is one complex per (batch, head, token), which is negligible.
+//
+// Backward mirrors the three kernels; parameter-bias and conv weight/bias
+// gradients are reduced per CTA and accumulated with float atomics.
+#include "common.cuh"
+
+namespace sl {
+namespace {
+
+constexpr int CONV_TT = 32;  // tokens per CTA in the value kernels
+
+struct ValueParams {
+  const void *x, *w, *bias, *state_in;
+  void *state_out, *U;
+  int64_t xs;                   // row stride of x (elements)
+  int64_t usb, ush, ust;        // strides of U
+  int batch, T, C, P, W;
+};
+
+template <typename T>
+__device__ __forceinline__ float load_x(const ValueParams& p, const T* x, const T* st, int b,
+                                        int t, int c) {
+  // input at time t (t may be negative: carried conv state or zero)
+  if (t >= 0) return to_f32(x[((size_t)b * p.T + t) * p.xs + c]);
+  const int j = p.W - 1 + t;
+  if (st && j >= 0) return to_f32(st[((size_t)b * p.C + c) * (p.W - 1) + j]);
+  return 0.f;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) value_fwd_kernel(ValueParams p) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+  if (c >= p.C) return;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* st = reinterpret_cast<const T*>(p.state_in);
+  T* U = reinterpret_cast<T*>(p.U);
+  const int h = c / p.P, pp = c - h * p.P;
+  const int t1 = min(t0 + CONV_TT, p.T);
+  if (!p.w) {
+    for (int t = t0; t < t1; ++t)
+      U[(size_t)b * p.usb + (size_t)h * p.ush + (size_t)t * p.ust + pp] =
+          x[((size_t)b * p.T + t) * p.xs + c];
+    return;
+  }
+  const T* w = reinterpret_cast<const T*>(p.w);
+  float wj[4] = {0.f, 0.f, 0.f, 0.f}, win[4] = {0.f, 0.f, 0.f, 0.f};
+  // right-align the taps in a width-4 window: wj[4-W+j] = W[c][j]
+  for (int j = 0; j < p.W; ++j) wj[4 - p.W + j] = to_f32(w[(size_t)c * p.W + j]);
+  const float bias = p.bias ? to_f32(reinterpret_cast<const T*>(p.bias)[c]) : 0.f;
+  // win[k] holds x at time t-3+k
+  for (int k = 1; k < 4; ++k) win[k] = (4 - k <= p.W - 1) ? load_x(p, x, st, b, t0 - 4 + k, c) : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    win[0] = win[1]; win[1] = win[2]; win[2] = win[3];
+    win[3] = to_f32(x[((size_t)b * p.T + t) * p.xs + c]);
+    const float a = bias + wj[0] * win[0] + wj[1] * win[1] + wj[2] * win[2] + wj[3] * win[3];
+    U[(size_t)b * p.usb + (size_t)h * p.ush + (size_t)t * p.ust + pp] = from_f32<T>(silu_f(a));
+  }
+  if (p.state_out && t1 == p.T) {
+    T* so = reinterpret_cast<T*>(p.state_out);
+    for (int j = 0; j < p.W - 1; ++j)
+      so[((size_t)b * p.C + c) * (p.W - 1) + j] =
+          from_f32<T>(load_x(p, x, st, b, p.T - (p.W - 1) + j, c));
+  }
+}
+
+struct ValueBwdParams {
+  ValueParams f;
+  const void* dU;
+  void *dx, *dstate;
+  float *dw, *dbias;
+};
+
+__device__ __forceinline__ float dsilu_f(float a) {
+  const float s = sigmoid_f(a);
+  return s * (1.f + a * (1.f - s));
+}
+
+// One thread per channel walks CONV_TT tokens; da at tokens t..t+W-1 is needed
+// for dx[t], so da is recomputed over a (W-1)-token look-ahead halo.
+template <typename T>
+__global__ void __launch_bounds__(256) value_bwd_kernel(ValueBwdParams q) {
+  const ValueParams& p = q.f;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+  if (c >= p.C) return;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* st = reinterpret_cast<const T*>(p.state_in);
+  const T* dU = reinterpret_cast<const T*>(q.dU);
+  T* dx = reinterpret_cast<T*>(q.dx);
+  const int h = c / p.P, pp = c - h * p.P;
+  const int t1 = min(t0 + CONV_TT, p.T);
+  auto dy_at = [&](int t) -> float {
+    return to_f32(dU[(size_t)b * p.usb + (size_t)h * p.ush + (size_t)t * p.ust + pp]);
+  };
+  if (!p.w) {
+    for (int t = t0; t < t1; ++t) dx[((size_t)b * p.T + t) * p.C + c] = from_f32<T>(dy_at(t));
+    return;
+  }
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const int W = p.W;
+  float wj[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < W; ++j) wj[4 - W + j] = to_f32(w[(size_t)c * W + j]);
+  const float bias = p.bias ? to_f32(reinterpret_cast<const T*>(p.bias)[c]) : 0.f;
+  float win[4] = {0.f, 0.f, 0.f, 0.f};   // x at times s-3..s for the da being formed
+  float da[4] = {0.f, 0.f, 0.f, 0.f};    // da at times s-3..s
+  float dwacc[4] = {0.f, 0.f, 0.f, 0.f}, dbacc = 0.f;
+  // The first tile also owns the gradient of the carried conv state (times < 0).
+  const int s_begin = (t0 == 0) ? 0 : t0;
+  for (int k = 1; k < 4; ++k) win[k] = (4 - k <= W - 1) ? load_x(p, x, st, b, s_begin - 4 + k, c) : 0.f;
+  // s runs over the tokens whose da is formed; dx[s-3] becomes complete at step s
+  // when W == 4 (in general dx[t] needs da[t .. t+W-1]).
+  const int s_end = min(t1 + 3, p.T + 3);
+  for (int s = s_begin; s < s_end; ++s) {
+    win[0] = win[1]; win[1] = win[2]; win[2] = win[3];
+    da[0] = da[1]; da[1] = da[2]; da[2] = da[3];
+    float d = 0.f;
+    if (s < p.T) {
+      win[3] = to_f32(x[((size_t)b * p.T + s) * p.xs + c]);
+      const float a = bias + wj[0] * win[0] + wj[1] * win[1] + wj[2] * win[2] + wj[3] * win[3];
+      d = dy_at(s) * dsilu_f(a);
+      if (s >= t0 && s < t1) {  // each token's weight/bias contribution is counted once
+        dwacc[0] += d * win[0]; dwacc[1] += d * win[1];
+        dwacc[2] += d * win[2]; dwacc[3] += d * win[3];
+        dbacc += d;
+      }
+    } else {
+      win[3] = 0.f;
+    }
+    da[3] = d;
+    // dx[t] = sum_k wj[k] * da[t + 3 - k], complete for t = s - 3
+    const int t = s - 3;
+    const float g = wj[3] * da[0] + wj[2] * da[1] + wj[1] * da[2] + wj[0] * da[3];
+    if (t >= t0 && t < t1) dx[((size_t)b * p.T + t) * p.C + c] = from_f32<T>(g);
+    else if (t < 0 && t0 == 0 && q.dstate && t >= -(W - 1))
+      reinterpret_cast<T*>(q.dstate)[((size_t)b * p.C + c) * (W - 1) + (W - 1 + t)] = from_f32<T>(g);
+  }
+  for (int j = 0; j < W; ++j) atomicAdd(q.dw + (size_t)c * W + j, dwacc[4 - W + j]);
+  if (q.dbias) atomicAdd(q.dbias + c, dbacc);
+}
+
+// ---- B / C parameterisation ------------------------------------------------------
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) bc_fwd_kernel(const T* __restrict__ bc, T* __restrict__ Bo,
+                                                     T* __restrict__ Co, int batch, int Tn,
+                                                     int G, int N, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= (long long)batch * Tn * G) return;
+  const int g = (int)(row % G);
+  const long long bt = row / G;
+  const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+  const T* src = bc + (size_t)row * 4 * N;
+  T* outs[2] = {Bo + (((size_t)b * G + g) * Tn + t) * 2 * N, Co + (((size_t)b * G + g) * Tn + t) * 2 * N};
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const T* amp_row = src + (size_t)(2 * which) * N;
+    const T* ph_row = amp_row + N;
+    float ss = 0.f;
+    for (int n = lane; n < N; n += 32) {
+      const float a = softplus_f(to_f32(amp_row[n]));
+      ss += a * a;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(fmaxf(ss / (float)N, eps));
+    for (int n = lane; n < N; n += 32) {
+      const float a = softplus_f(to_f32(amp_row[n])) * inv;
+      const float ph = 3.14159265358979323846f * tanhf(to_f32(ph_row[n]));
+      float sn, cs;
+      sincosf(ph, &sn, &cs);
+      outs[which][2 * n] = from_f32<T>(a * cs);
+      outs[which][2 * n + 1] = from_f32<T>(a * sn);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bc_bwd_kernel(const T* __restrict__ bc,
+                                                     const T* __restrict__ dBo,
+                                                     const T* __restrict__ dCo,
+                                                     T* __restrict__ dbc, int batch, int Tn,
+                                                     int G, int N, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= (long long)batch * Tn * G) return;
+  const int g = (int)(row % G);
+  const long long bt = row / G;
+  const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+  const T* src = bc + (size_t)row * 4 * N;
+  T* dst = dbc + (size_t)row * 4 * N;
+  const T* gs[2] = {dBo + (((size_t)b * G + g) * Tn + t) * 2 * N, dCo + (((size_t)b * G + g) * Tn + t) * 2 * N};
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const T* amp_row = src + (size_t)(2 * which) * N;
+    const T* ph_row = amp_row + N;
+    float ss = 0.f, gsum = 0.f;
+    for (int n = lane; n < N; n += 32) {
+      const float a = softplus_f(to_f32(amp_row[n]));
+      const float ph = 3.14159265358979323846f * tanhf(to_f32(ph_row[n]));
+      float sn, cs;
+      sincosf(ph, &sn, &cs);
+      ss += a * a;
+      gsum += a * (cs * to_f32(gs[which][2 * n]) + sn * to_f32(gs[which][2 * n + 1]));
+    }
+    ss = warp_sum(ss); gsum = warp_sum(gsum);
+    const float ms = ss / (float)N;
+    const float inv = rsqrtf(fmaxf(ms, eps));
+    const float g_ms = ms > eps ? -0.5f * inv * inv * inv * gsum : 0.f;
+    for (int n = lane; n < N; n += 32) {
+      const float xa = to_f32(amp_row[n]);
+      const float a = softplus_f(xa);
+      const float th = tanhf(to_f32(ph_row[n]));
+      const float ph = 3.14159265358979323846f * th;
+      float sn, cs;
+      sincosf(ph, &sn, &cs);
+      const float gre = to_f32(gs[which][2 * n]), gim = to_f32(gs[which][2 * n + 1]);
+      const float g_amp = inv * (cs * gre + sn * gim) + g_ms * 2.f * a / (float)N;
+      const float g_ph = a * inv * (cs * gim - sn * gre);
+      dst[(size_t)(2 * which) * N + n] = from_f32<T>(g_amp * sigmoid_f(xa));
+      dst[(size_t)(2 * which + 1) * N + n] = from_f32<T>(g_ph * 3.14159265358979323846f * (1.f - th * th));
+    }
+  }
+}
+
+// ---- transition / tap coefficients (float64 inside) ---------------------------------
+struct zc { double re, im; };
+__device__ __forceinline__ zc zmul(zc a, zc b) { return {a.re * b.re - a.im * b.im, a.re * b.im + a.im * b.re}; }
+__device__ __forceinline__ zc zdiv(zc a, zc b) {
+  const double d = b.re * b.re + b.im * b.im;
+  return {(a.re * b.re + a.im * b.im) / d, (a.im * b.re - a.re * b.im) / d};
+}
+__device__ __forceinline__ zc zconj_mul(zc a, zc b) {  // conj(a) * b
+  return {a.re * b.re + a.im * b.im, a.re * b.im - a.im * b.re};
+}
+
+struct CoeffOut {
+  double dt, r, theta, ea;          // ea = exp(-alpha)
+  double sg_dt, sg_al, th_u, tanh2; // intermediates for the backward
+  zc rho, k1, k2, dk1, dk2;         // kappa1, kappa2 and their z-derivatives
+};
+
+__device__ __forceinline__ float wrap_angle_f(float theta) {
+  // remainder(theta + pi, 2 pi) - pi evaluated in float32 like the reference
+  const float pi = 3.14159265358979323846f, two_pi = 6.28318530717958647692f;
+  float r = fmodf(theta + pi, two_pi);
+  if (r < 0.f) r += two_pi;
+  return r - pi;
+}
+
+__device__ __forceinline__ CoeffOut coeff_eval(float p0, float p1, float p2, float th_bias,
+                                               float th_sign, const sl_scanprep_config& c) {
+  CoeffOut o;
+  // bounded maps in float32 (as the reference), then float64 for the taps
+  const float sdt = 1.f / (1.f + expf(-p0));
+  const float sal = 1.f / (1.f + expf(-p1));
+  const float th = tanhf(p2);
+  const float thu = 1.f / (1.f + expf(-(th_bias + c.theta_mod_scale * th)));
+  const float span = fmaxf(c.theta_init_max - c.theta_init_min, 1.0e-6f);
+  const float dt = c.dt_min + (c.dt_max - c.dt_min) * sdt;
+  const float alpha = c.alpha_min + (c.alpha_max - c.alpha_min) * sal;
+  const float theta = wrap_angle_f(th_sign * (c.theta_init_min + span * thu));
+  const float ea = expf(-alpha);
+  const float r = c.r_min + (c.r_max - c.r_min) * ea;
+  o.dt = dt; o.r = r; o.theta = theta; o.ea = ea;
+  o.sg_dt = sdt; o.sg_al = sal; o.th_u = thu; o.tanh2 = (double)th * th;
+  const double a = log((double)r);
+  double sn, cs;
+  sincos((double)theta, &sn, &cs);
+  o.rho = {(double)r * cs, (double)r * sn};
+  const zc z = {a, (double)theta};
+  const float lr = logf(r);
+  const double thr = fmax(1.0e-4, sqrt(fmax((double)c.eps, 1.0e-12)));
+  const bool small = (double)(lr * lr + theta * theta) < thr * thr;
+  if (small) {
+    const zc z2 = zmul(z, z), z3 = zmul(z2, z);
+    o.k1 = {1.0 + 0.5 * z.re + z2.re / 6.0 + z3.re / 24.0, 0.5 * z.im + z2.im / 6.0 + z3.im / 24.0};
+    o.k2 = {0.5 + z.re / 3.0 + z2.re / 8.0 + z3.re / 30.0, z.im / 3.0 + z2.im / 8.0 + z3.im / 30.0};
+    o.dk1 = {0.5 + z.re / 3.0 + z2.re / 8.0, z.im / 3.0 + z2.im / 8.0};
+    o.dk2 = {1.0 / 3.0 + z.re / 4.0 + z2.re / 10.0, z.im / 4.0 + z2.im / 10.0};
+  } else {
+    const zc rm1 = {o.rho.re - 1.0, o.rho.im};
+    o.k1 = zdiv(rm1, z);
+    const zc zm1 = {z.re - 1.0, z.im};
+    zc num = zmul(o.rho, zm1);
+    num.re += 1.0;
+    o.k2 = zdiv(num, zmul(z, z));
+    // kappa1' = (rho - kappa1)/z ; kappa2' = (rho - 2 kappa2)/z
+    o.dk1 = zdiv({o.rho.re - o.k1.re, o.rho.im - o.k1.im}, z);
+    o.dk2 = zdiv({o.rho.re - 2.0 * o.k2.re, o.rho.im - 2.0 * o.k2.im}, z);
+  }
+  return o;
+}
+
+struct CoeffParams {
+  const void* params;
+  const float *dt_bias, *alpha_bias, *theta_mod_bias, *theta_bias, *theta_sign;
+  sl_scanprep_config cfg;
+  float *M, *K;
+  const float *dM, *dK;
+  void* dparams;
+  float *d_dt_bias, *d_alpha_bias, *d_theta_mod_bias, *d_theta_bias;
+  int batch, T, H;
+};
+
+// grid (ceil(T/128), H, batch), thread = token: outputs are coalesced along T.
+template <typename T>
+__global__ void __launch_bounds__(128) coeff_fwd_kernel(CoeffParams p) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y, b = blockIdx.z;
+  if (t >= p.T) return;
+  const T* pr = reinterpret_cast<const T*>(p.params) + ((size_t)b * p.T + t) * 3 * p.H + 3 * h;
+  const CoeffOut o = coeff_eval(to_f32(pr[0]) + p.dt_bias[h], to_f32(pr[1]) + p.alpha_bias[h],
+                                to_f32(pr[2]) + p.theta_mod_bias[h], p.theta_bias[h],
+                                p.theta_sign[h], p.cfg);
+  const size_t i = ((size_t)b * p.H + h) * p.T + t;
+  reinterpret_cast<float2*>(p.M)[i] = make_float2((float)o.rho.re, (float)o.rho.im);
+  const zc kp = {o.dt * o.k2.re, o.dt * o.k2.im};
+  const zc kc = {o.dt * o.k1.re - kp.re, o.dt * o.k1.im - kp.im};
+  reinterpret_cast<float4*>(p.K)[i] = make_float4((float)kp.re, (float)kp.im, (float)kc.re, (float)kc.im);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) coeff_bwd_kernel(CoeffParams p) {
+  __shared__ float s_red[4][4];
+  const int t = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y, b = blockIdx.z;
+  float g0 = 0.f, g1 = 0.f, g2 = 0.f, gx = 0.f;
+  if (t < p.T) {
+    const T* pr = reinterpret_cast<const T*>(p.params) + ((size_t)b * p.T + t) * 3 * p.H + 3 * h;
+    const CoeffOut o = coeff_eval(to_f32(pr[0]) + p.dt_bias[h], to_f32(pr[1]) + p.alpha_bias[h],
+                                  to_f32(pr[2]) + p.theta_mod_bias[h], p.theta_bias[h],
+                                  p.theta_sign[h], p.cfg);
+    const size_t i = ((size_t)b * p.H + h) * p.T + t;
+    const float2 gm = reinterpret_cast<const float2*>(p.dM)[i];
+    const float4 gk = reinterpret_cast<const float4*>(p.dK)[i];
+    const zc gM = {gm.x, gm.y}, gKp = {gk.x, gk.y}, gKc = {gk.z, gk.w};
+    // kp = dt k2 ; kc = dt (k1 - k2)
+    const zc gk1 = {o.dt * gKc.re, o.dt * gKc.im};
+    const zc gk2 = {o.dt * (gKp.re - gKc.re), o.dt * (gKp.im - gKc.im)};
+    const zc k12 = {o.k1.re - o.k2.re, o.k1.im - o.k2.im};
+    const double g_dt = (o.k2.re * gKp.re + o.k2.im * gKp.im) + (k12.re * gKc.re + k12.im * gKc.im);
+    zc gz = zconj_mul(o.rho, gM);
+    const zc a1 = zconj_mul(o.dk1, gk1), a2 = zconj_mul(o.dk2, gk2);
+    gz.re += a1.re + a2.re; gz.im += a1.im + a2.im;
+    const double g_r = gz.re / o.r;
+    const double g_alpha = -(double)(p.cfg.r_max - p.cfg.r_min) * o.ea * g_r;
+    const double span = fmax((double)p.cfg.theta_init_max - (double)p.cfg.theta_init_min, 1.0e-6);
+    const double g_thu = span * (double)p.theta_sign[h] * gz.im;
+    const double g_x = o.th_u * (1.0 - o.th_u) * g_thu;
+    g0 = (float)((double)(p.cfg.dt_max - p.cfg.dt_min) * o.sg_dt * (1.0 - o.sg_dt) * g_dt);
+    g1 = (float)((double)(p.cfg.alpha_max - p.cfg.alpha_min) * o.sg_al * (1.0 - o.sg_al) * g_alpha);
+    g2 = (float)((double)p.cfg.theta_mod_scale * (1.0 - o.tanh2) * g_x);
+    gx = (float)g_x;
+    T* dp = reinterpret_cast<T*>(p.dparams) + ((size_t)b * p.T + t) * 3 * p.H + 3 * h;
+    dp[0] = from_f32<T>(g0); dp[1] = from_f32<T>(g1); dp[2] = from_f32<T>(g2);
+  }
+  g0 = warp_sum(g0); g1 = warp_sum(g1); g2 = warp_sum(g2); gx = warp_sum(gx);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) { s_red[w][0] = g0; s_red[w][1] = g1; s_red[w][2] = g2; s_red[w][3] = gx; }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    const float s = s_red[0][threadIdx.x] + s_red[1][threadIdx.x] + s_red[2][threadIdx.x] + s_red[3][threadIdx.x];
+    float* dst = threadIdx.x == 0 ? p.d_dt_bias : threadIdx.x == 1 ? p.d_alpha_bias
+                 : threadIdx.x == 2 ? p.d_theta_mod_bias : p.d_theta_bias;
+    if (dst) atomicAdd(dst + h, s);
+  }
+}
+
+int check_common(int batch, int heads, int groups, int T, int P, int N, int io_dtype, int d_conv) {
+  if (batch < 1 || heads < 1 || groups < 1 || heads % groups || T < 1 || P < 1 || N < 1)
+    return SL_ERR_BAD_SHAPE;
+  if (d_conv < 1 || d_conv > 4) return SL_ERR_UNSUPPORTED;
+  if (!dtype_ok(io_dtype)) return SL_ERR_UNSUPPORTED;
+  return SL_OK;
+}
+
+}  // namespace
+}  // namespace sl
+
+extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
+                                    const void* conv_weight, const void* conv_bias,
+                                    const void* conv_state_in, void* conv_state_out, int d_conv,
+                                    const void* params, const void* bc, const float* dt_bias,
+                                    const float* alpha_bias, const float* theta_mod_bias,
+                                    const float* theta_bias, const float* theta_sign,
+                                    const sl_scanprep_config* cfg, void* U, int64_t u_stride_b,
+                                    int64_t u_stride_h, int64_t u_stride_t, float* M, float* K,
+                                    void* Bo, void* Co, int batch, int heads, int groups, int T,
+                                    int P, int N, int io_dtype, void* stream) {
+  using namespace sl;
+  if (int e = check_common(batch, heads, groups, T, P, N, io_dtype, conv_weight ? d_conv : 1)) return e;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (value) {
+    if (!U) return SL_ERR_NULL_POINTER;
+    ValueParams p{};
+    p.x = value; p.w = conv_weight; p.bias = conv_bias; p.state_in = conv_state_in;
+    p.state_out = conv_state_out; p.U = U; p.xs = value_row_stride;
+    p.usb = u_stride_b; p.ush = u_stride_h; p.ust = u_stride_t;
+    p.batch = batch; p.T = T; p.C = heads * P; p.P = P; p.W = conv_weight ? d_conv : 1;
+    dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
+    SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, st>>>(p); });
+  }
+  if (bc) {
+    if (!Bo || !Co || !cfg) return SL_ERR_NULL_POINTER;
+    const long long rows = (long long)batch * T * groups;
+    const unsigned blocks = (unsigned)((rows + 7) / 8);
+    SL_DISPATCH_DTYPE(io_dtype, Tt, {
+      bc_fwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc),
+                                               reinterpret_cast<Tt*>(Bo),
+                                               reinterpret_cast<Tt*>(Co), batch, T, groups, N,
+                                               cfg->eps);
+    });
+  }
+  if (params) {
+    if (!M || !K || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias || !theta_bias || !theta_sign)
+      return SL_ERR_NULL_POINTER;
+    if (!aligned(M, 8) || !aligned(K, 16)) return SL_ERR_BAD_ALIGNMENT;
+    CoeffParams p{};
+    p.params = params; p.dt_bias = dt_bias; p.alpha_bias = alpha_bias;
+    p.theta_mod_bias = theta_mod_bias; p.theta_bias = theta_bias; p.theta_sign = theta_sign;
+    p.cfg = *cfg; p.M = M; p.K = K; p.batch = batch; p.T = T; p.H = heads;
+    dim3 grid((T + 127) / 128, heads, batch);
+    SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_fwd_kernel<Tt><<<grid, 128, 0, st>>>(p); });
+  }
+  return launch_status();
+}
+
+extern "C" int sl_scanprep_conv_bwd(
+    const void* value, int64_t value_row_stride, const void* conv_weight, const void* conv_bias,
+    const void* conv_state_in, int d_conv, const void* params, const void* bc,
+    const float* dt_bias, const float* alpha_bias, const float* theta_mod_bias,
+    const float* theta_bias, const float* theta_sign, const sl_scanprep_config* cfg,
+    const void* dU, int64_t u_stride_b, int64_t u_stride_h, int64_t u_stride_t, const float* dM,
+    const float* dK, const void* dBo, const void* dCo, void* d_value, float* d_conv_weight,
+    float* d_conv_bias, void* d_conv_state, void* d_params, void* d_bc, float* d_dt_bias,
+    float* d_alpha_bias, float* d_theta_mod_bias, float* d_theta_bias, int batch, int heads,
+    int groups, int T, int P, int N, int io_dtype, void* stream) {
+  using namespace sl;
+  if (int e = check_common(batch, heads, groups, T, P, N, io_dtype, conv_weight ? d_conv : 1)) return e;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dU) {
+    if (!d_value || !value) return SL_ERR_NULL_POINTER;
+    if (conv_weight && !d_conv_weight) return SL_ERR_NULL_POINTER;
+    ValueBwdParams q{};
+    ValueParams& p = q.f;
+    p.x = value; p.w = conv_weight; p.bias = conv_bias; p.state_in = conv_state_in;
+    p.xs = value_row_stride; p.usb = u_stride_b; p.ush = u_stride_h; p.ust = u_stride_t;
+    p.batch = batch; p.T = T; p.C = heads * P; p.P = P; p.W = conv_weight ? d_conv : 1;
+    q.dU = dU; q.dx = d_value; q.dstate = d_conv_state; q.dw = d_conv_weight; q.dbias = d_conv_bias;
+    dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
+    SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+  }
+  if (dBo) {
+    if (!dCo || !bc || !d_bc || !cfg) return SL_ERR_NULL_POINTER;
+    const long long rows = (long long)batch * T * groups;
+    const unsigned blocks = (unsigned)((rows + 7) / 8);
+    SL_DISPATCH_DTYPE(io_dtype, Tt, {
+      bc_bwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc),
+                                               reinterpret_cast<const Tt*>(dBo),
+                                               reinterpret_cast<const Tt*>(dCo),
+                                               reinterpret_cast<Tt*>(d_bc), batch, T, groups, N,
+                                               cfg->eps);
+    });
+  }
+  if (dM) {
+    if (!dK || !params || !d_params || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias ||
+        !theta_bias || !theta_sign)
+      return SL_ERR_NULL_POINTER;
+    if (!aligned(dM, 8) || !aligned(dK, 16)) return SL_ERR_BAD_ALIGNMENT;
+    CoeffParams p{};
+    p.params = params; p.dt_bias = dt_bias; p.alpha_bias = alpha_bias;
+    p.theta_mod_bias = theta_mod_bias; p.theta_bias = theta_bias; p.theta_sign = theta_sign;
+    p.cfg = *cfg; p.dM = dM; p.dK = dK; p.dparams = d_params; p.d_dt_bias = d_dt_bias;
+    p.d_alpha_bias = d_alpha_bias; p.d_theta_mod_bias = d_theta_mod_bias;
+    p.d_theta_bias = d_theta_bias; p.batch = batch; p.T = T; p.H = heads;
+    dim3 grid((T + 127) / 128, heads, batch);
+    SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_bwd_kernel<Tt><<<grid, 128, 0, st>>>(p); });
+  }
+  return launch_status();
+}

@@ -1,0 +1,247 @@
+"""Host side of the v2x2ssd scan: validation, dtype policy, autograd wiring."""
+
+from __future__ import annotations
+
+import torch
+
+from ... import _C
+
+_IO_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def _contig(name: str, x: torch.Tensor) -> None:
+    if not x.is_contiguous():
+        raise ValueError(f"{name} must be contiguous; got strides {x.stride()}.")
+
+
+def validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev):
+    """Shape / device / layout contract of the scan; same conditions and messages as
+    the reference's ``_validate_inputs`` (slinoss/ops/v2x2ssd/reference.py:152-234).
+    Returns ``(batch, heads, T, N, P)``."""
+    tensors = (U, M, K, B, C)
+    if not all(torch.is_floating_point(t) for t in tensors):
+        raise ValueError("U, M, K, B, and C must be floating-point tensors.")
+    if not all(t.device == U.device for t in tensors):
+        raise ValueError(
+            f"All inputs must be on the same device. Got {[t.device for t in tensors]}.")
+    for name, t in zip("UMKBC", tensors):
+        _contig(name, t)
+    if U.ndim != 4:
+        raise ValueError(f"U must be (batch,heads,T,P). Got {tuple(U.shape)}.")
+    if M.ndim != 4 or M.shape[-1] != 2:
+        raise ValueError(f"M must be (batch,heads,T,2). Got {tuple(M.shape)}.")
+    if K.ndim != 5 or K.shape[-2:] != (2, 2):
+        raise ValueError(f"K must be (batch,heads,T,2,2). Got {tuple(K.shape)}.")
+    if B.ndim != 4:
+        raise ValueError(f"B must be (batch,groups,T,2N). Got {tuple(B.shape)}.")
+    if C.ndim != 4:
+        raise ValueError(f"C must be (batch,groups,T,2N). Got {tuple(C.shape)}.")
+    batch, heads, T, P = map(int, U.shape)
+    if M.shape[:3] != (batch, heads, T):
+        raise ValueError("Leading (batch,heads,T) dims of M must match U.")
+    if K.shape[:3] != (batch, heads, T):
+        raise ValueError("Leading (batch,heads,T) dims of K must match U.")
+    if B.shape[0] != batch or B.shape[2] != T:
+        raise ValueError("B must match U on batch/time dims.")
+    if C.shape[0] != batch or C.shape[2] != T:
+        raise ValueError("C must match U on batch/time dims.")
+    D = int(B.shape[-1])
+    if D % 2 != 0:
+        raise ValueError(f"B/C 2N dim must be divisible by 2. Got {D}.")
+    groups = int(B.shape[1])
+    if groups <= 0:
+        raise ValueError("B/C must have a positive group dimension.")
+    if heads % groups != 0:
+        raise ValueError(
+            f"B/C group dimension must divide heads. Got heads={heads}, groups={groups}.")
+    if tuple(C.shape) != (batch, groups, T, D):
+        raise ValueError("C must match grouped B exactly.")
+    if (B_prev is None) ^ (U_prev is None):
+        raise ValueError("B_prev and U_prev must be passed together (or both omitted).")
+    if initial_states is not None:
+        if initial_states.shape != (batch, heads, P, D):
+            raise ValueError(
+                "initial_states must be (batch,heads,P,2N) "
+                f"={(batch, heads, P, D)}. Got {tuple(initial_states.shape)}.")
+        _contig("initial_states", initial_states)
+        if initial_states.device != U.device:
+            raise ValueError("initial_states must be on the same device as inputs.")
+    if B_prev is not None:
+        if B_prev.shape != (batch, groups, D):
+            raise ValueError(
+                f"B_prev must be (batch,groups,2N)={(batch, groups, D)}. Got {tuple(B_prev.shape)}.")
+        if U_prev.shape != (batch, heads, P):
+            raise ValueError(
+                f"U_prev must be (batch,heads,P)={(batch, heads, P)}. Got {tuple(U_prev.shape)}.")
+        _contig("B_prev", B_prev)
+        _contig("U_prev", U_prev)
+        if B_prev.device != U.device or U_prev.device != U.device:
+            raise ValueError("B_prev and U_prev must be on the same device as inputs.")
+    return batch, heads, T, D // 2, P
+
+
+def resolve_dtypes(input_dtypes, compute_dtype, output_dtype, default_output_dtype):
+    """Compute / output dtype policy (reference.py:61-82); the CUDA kernels compute
+    in float32 only (cute/api.py:91-95)."""
+    if compute_dtype is None:
+        promoted = input_dtypes[0]
+        for dt in input_dtypes[1:]:
+            promoted = torch.promote_types(promoted, dt)
+        compute_dtype = torch.float32 if promoted in (torch.float16, torch.bfloat16) else promoted
+    if compute_dtype not in (torch.float32, torch.float64):
+        raise ValueError(f"compute_dtype must be float32 or float64, got {compute_dtype}.")
+    if compute_dtype != torch.float32:
+        raise ValueError(
+            "The sm_100a v2x2ssd kernels support only float32 compute. "
+            f"Got compute_dtype={compute_dtype}.")
+    odtype = default_output_dtype if output_dtype is None else output_dtype
+    if odtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
+        raise ValueError(f"output_dtype must be a real floating dtype, got {odtype}.")
+    return compute_dtype, odtype
+
+
+def _empty_outputs(batch, heads, groups, P, D, device, odtype, initial_states, B_prev, U_prev):
+    """T == 0: the carried state passes through unchanged (reference.py:704-736)."""
+    Y = torch.empty((batch, heads, 0, P), device=device, dtype=odtype)
+    final = torch.zeros((batch, heads, P, D), device=device, dtype=odtype) \
+        if initial_states is None else initial_states.to(dtype=odtype).contiguous()
+    if B_prev is None:
+        return (Y, final, torch.zeros((batch, groups, D), device=device, dtype=odtype),
+                torch.zeros((batch, heads, P), device=device, dtype=odtype))
+    return Y, final, B_prev.to(dtype=odtype).contiguous(), U_prev.to(dtype=odtype).contiguous()
+
+
+def _io_dtype(U: torch.Tensor) -> torch.dtype:
+    return U.dtype if U.dtype in _IO_DTYPES else torch.float32
+
+
+def _prep(U, M, K, B, C, initial_states, B_prev, U_prev):
+    """Cast to what the C ABI takes: U/B/C/B_prev/U_prev in one io dtype, the rest float32."""
+    io = _io_dtype(U)
+    cast = lambda x, dt: None if x is None else x.detach().to(dtype=dt).contiguous()
+    return (cast(U, io), cast(M, torch.float32), cast(K, torch.float32), cast(B, io), cast(C, io),
+            cast(initial_states, torch.float32), cast(B_prev, io), cast(U_prev, io))
+
+
+class _ScanFn(torch.autograd.Function):
+    """Saves only the inputs; the backward kernels recompute what they need
+    (same saved set as slinoss/ops/v2x2ssd/cute/autograd.py:110-118)."""
+
+    @staticmethod
+    def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, chunk_size, odtype,
+                return_state, path):
+        args = _prep(U, M, K, B, C, initial_states, B_prev, U_prev)
+        y_dtype = odtype if odtype in _IO_DTYPES else torch.float32
+        Y, final = _C.scan_fwd(*args, chunk_size=chunk_size, y_dtype=y_dtype,
+                               want_final=return_state, path=path)
+        ctx.save_for_backward(*[a for a in args if a is not None])
+        ctx.present = [a is not None for a in args]
+        ctx.in_dtypes = [None if x is None else x.dtype
+                         for x in (U, M, K, B, C, initial_states, B_prev, U_prev)]
+        ctx.chunk_size, ctx.path, ctx.return_state = chunk_size, path, return_state
+        Y = Y.to(dtype=odtype)
+        if not return_state:
+            return Y
+        return (Y, final.to(dtype=odtype), B[:, :, -1, :].detach().to(dtype=odtype).contiguous(),
+                U[:, :, -1, :].detach().to(dtype=odtype).contiguous())
+
+    @staticmethod
+    def backward(ctx, *grads):
+        it = iter(ctx.saved_tensors)
+        U, M, K, B, C, z0, B_prev, U_prev = [next(it) if p else None for p in ctx.present]
+        dY = grads[0]
+        d_final = dB_last = dU_last = None
+        if ctx.return_state:
+            _, d_final, dB_last, dU_last = grads
+        out = [None] * 8
+        if dY is not None or d_final is not None:
+            if dY is not None:
+                if dY.dtype not in _IO_DTYPES:
+                    dY = dY.to(torch.float32)
+                dY = dY.contiguous()
+            if d_final is not None:
+                d_final = d_final.to(torch.float32).contiguous()
+            out = list(_C.scan_bwd(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final,
+                                   chunk_size=ctx.chunk_size, path=ctx.path))
+        if dB_last is not None:
+            if out[3] is None:
+                out[3] = torch.zeros_like(B)
+            out[3][:, :, -1, :].add_(dB_last.to(dtype=out[3].dtype))
+        if dU_last is not None:
+            if out[0] is None:
+                out[0] = torch.zeros_like(U)
+            out[0][:, :, -1, :].add_(dU_last.to(dtype=out[0].dtype))
+        res = []
+        for g, dt, need in zip(out, ctx.in_dtypes, ctx.needs_input_grad[:8]):
+            res.append(g.to(dtype=dt) if (g is not None and dt is not None and need) else None)
+        return (*res, None, None, None, None)
+
+
+def v2x2ssd_cute(U, M, K, B, C, *, chunk_size, initial_states=None, B_prev=None, U_prev=None,
+                 compute_dtype=None, output_dtype=None, return_state=False, path="auto"):
+    """GPU scan.  Returns ``Y`` or ``(Y, final_state, B_last, U_last)``.
+
+    ``path`` selects the kernel family: "auto" (tensor cores when the shape and dtype
+    allow, else the exact float32 recurrence), "simt" or "tc"."""
+    batch, heads, T, N, P = validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
+    _C.require_cuda(U)
+    if chunk_size <= 0:
+        raise ValueError(f"chunk_size must be positive. Got {chunk_size}.")
+    _, odtype = resolve_dtypes([U.dtype, M.dtype, K.dtype, B.dtype, C.dtype], compute_dtype,
+                               output_dtype, U.dtype)
+    if T == 0:
+        empty = _empty_outputs(batch, heads, int(B.shape[1]), P, 2 * N, U.device, odtype,
+                               initial_states, B_prev, U_prev)
+        return empty if return_state else empty[0]
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (U, M, K, B, C, initial_states, B_prev, U_prev))
+    if needs_grad:
+        return _ScanFn.apply(U, M, K, B, C, initial_states, B_prev, U_prev, int(chunk_size),
+                             odtype, bool(return_state), path)
+    args = _prep(U, M, K, B, C, initial_states, B_prev, U_prev)
+    y_dtype = odtype if odtype in _IO_DTYPES else torch.float32
+    Y, final = _C.scan_fwd(*args, chunk_size=int(chunk_size), y_dtype=y_dtype,
+                           want_final=return_state, path=path)
+    Y = Y.to(dtype=odtype)
+    if not return_state:
+        return Y
+    return (Y, final.to(dtype=odtype), B[:, :, -1, :].to(dtype=odtype).contiguous(),
+            U[:, :, -1, :].to(dtype=odtype).contiguous())
+
+
+def v2x2ssd(U, M, K, B, C, *, chunk_size=64, initial_states=None, B_prev=None, U_prev=None,
+            compute_dtype=None, output_dtype=None, path="auto"):
+    """Same call and 4-tuple result as the reference's ``v2x2ssd``."""
+    return v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=initial_states,
+                        B_prev=B_prev, U_prev=U_prev, compute_dtype=compute_dtype,
+                        output_dtype=output_dtype, return_state=True, path=path)
+
+
+def v2x2ssd_decode(U, M, K, B, C, *, state, B_prev=None, U_prev=None, output_dtype=None,
+                   inplace=False):
+    """One decode token.  ``U (batch,heads,P)``, ``M (batch,heads,2)``, ``K (batch,heads,2,2)``,
+    ``B, C (batch,groups,2N)``, ``state (batch,heads,P,2N)`` float32.
+
+    Returns ``(Y, next_state, B_last, U_last)`` with the same meaning as one ``T = 1``
+    call of the sequential scan (slinoss/ops/v2x2ssd/reference.py:739-847).  With
+    ``inplace`` the float32 ``state`` tensor is updated where it lies."""
+    if U.ndim != 3 or M.shape != U.shape[:2] + (2,) or K.shape != U.shape[:2] + (2, 2):
+        raise ValueError("decode expects U (batch,heads,P), M (batch,heads,2), K (batch,heads,2,2).")
+    if B.ndim != 3 or B.shape != C.shape or B.shape[-1] % 2:
+        raise ValueError("decode expects B, C (batch,groups,2N).")
+    if (B_prev is None) ^ (U_prev is None):
+        raise ValueError("B_prev and U_prev must be passed together (or both omitted).")
+    batch, heads, P = U.shape
+    if state.shape != (batch, heads, P, B.shape[-1]):
+        raise ValueError(f"state must be {(batch, heads, P, B.shape[-1])}. Got {tuple(state.shape)}.")
+    io = _io_dtype(U)
+    odtype = U.dtype if output_dtype is None else output_dtype
+    cast = lambda x, dt: None if x is None else x.to(dtype=dt).contiguous()
+    if inplace and (state.dtype != torch.float32 or not state.is_contiguous()):
+        raise ValueError("in-place decode needs a contiguous float32 state.")
+    st = cast(state, torch.float32)
+    y_dtype = odtype if odtype in _IO_DTYPES else torch.float32
+    Y, nxt = _C.scan_decode(cast(U, io), cast(M, torch.float32), cast(K, torch.float32),
+                            cast(B, io), cast(C, io), st, cast(B_prev, io), cast(U_prev, io),
+                            y_dtype=y_dtype, state_out=st if inplace else None)
+    return Y.to(dtype=odtype), nxt, B, U
