@@ -1,0 +1,316 @@
+"""Benchmark of the v2x2ssd scan forward+backward (BASELINE config 1) on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One "step" = one forward + one backward pass of the scan over one batch of synthetic
+input (batch 8, heads 16, T 4096, P 64, N 64, chunk 64, bf16 operands, float32 state)
+per GPU.  Every rank owns an independent shard of (batch, head) streams, so there is
+no data-path collective ("weak" scaling: per-GPU work is fixed).  Rank 0 prints ONE
+JSON line:
+
+  value / ms_per_step   device-timed (CUDA events on the launching stream, max over
+                        ranks) with inputs resident in HBM, through the C ABI launchers
+  e2e                   the same step through the public op with HOST (pinned) buffers:
+                        host->device copies of all inputs and device->host copies of Y and
+                        all gradients are inside the timed region
+  roofline              algorithmic bytes of fwd+bwd / measured step time vs the measured
+                        HBM copy bandwidth of this pool (MEASURED_PEAKS.json)
+  cpu_baseline          the C/OpenMP port of the reference's sequential scan (oracle/),
+                        timed on the host cores on a bounded sample (N=1, rank 0 only)
+
+``--impl reference`` times only that CPU port (all host threads) and prints the same
+line with ``"impl": "reference"``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG = dict(batch=8, heads=16, T=4096, P=64, N=64, chunk=64)
+METRIC = "v2x2ssd fwd+bwd tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(c) -> dict:
+    """Each input read once, each output written once (bf16 operands, float32 M/K)."""
+    bht = c["batch"] * c["heads"] * c["T"]
+    u = bht * c["P"] * 2
+    bc = bht * 2 * c["N"] * 2
+    m, k = bht * 2 * 4, bht * 4 * 4
+    fwd = u + 2 * bc + m + k + u
+    bwd = (u + 2 * bc + m + k) + u + (u + 2 * bc + m + k)
+    return {"fwd": fwd, "bwd": bwd, "total": fwd + bwd}
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, f"/tmp/slinoss_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.proc.wait()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_baseline(sample_heads: int = 16, repeats: int = 1) -> dict:
+    """Times the C/OpenMP oracle port (forward + backward) on a slice of the workload:
+    batch 1, ``sample_heads`` heads, full T/P/N.  Returns tokens/s on the host cores."""
+    from oracle import scan_c
+    from slinoss_b200.synthetic import make_scan_case
+    c = CFG
+    case = make_scan_case(1, sample_heads, c["T"], c["P"], c["N"], dtype=torch.bfloat16, seed=0)
+    arrs = [t.float().numpy() for t in case.tensors()]
+    dY = case.dY.float().numpy()
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        scan_c.forward(*arrs)
+        scan_c.backward(*arrs, dY)
+        best = min(best, time.perf_counter() - t0)
+    tokens = c["T"]  # batch 1
+    # the full workload has batch*heads streams; this sample has sample_heads of them
+    scale = c["batch"] * c["heads"] / sample_heads
+    full_step_s = best * scale
+    return {"value": c["batch"] * c["T"] / full_step_s, "unit": "tokens/s", "cores": scan_c.num_threads(),
+            "kind": "port",
+            "sample": f"fwd+bwd of batch 1 x {sample_heads} heads x T {c['T']} (1/{scale:.0f} of a step) "
+                      f"in {best:.2f} s, scaled linearly", "sample_seconds": best}
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    base = cpu_baseline(sample_heads=8, repeats=1)
+    times = [base["sample_seconds"]]
+    for _ in range(max(0, args.steps - 1)):
+        times.append(cpu_baseline(sample_heads=8)["sample_seconds"])
+    scale = CFG["batch"] * CFG["heads"] / 8
+    step_s = statistics.mean(times) * scale
+    value = CFG["batch"] * CFG["T"] / step_s
+    base["value"] = value
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": len(times), "warmup": 0, "ms_per_step": step_s * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "BASELINE config 1: v2x2ssd fwd+bwd, batch 8 x heads 16 x T 4096, P 64, N 64, "
+                        "chunk 64, bf16 operands, float32 state/accumulation, per GPU",
+            "sharding": f"{n} independent shards of (batch, head) streams, no collective",
+            "l2": "inputs of one step (415 MB) exceed the 126 MB L2; no explicit flush",
+            **CFG}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="T=512 variant for profiler captures")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if args.small:
+        CFG["T"] = 512
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path.")
+    args.warmup = max(args.warmup, 3)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from slinoss_b200 import _C
+    from slinoss_b200.ops.v2x2ssd import v2x2ssd_cute
+    from slinoss_b200.synthetic import make_scan_case
+
+    c = CFG
+    case_h = make_scan_case(c["batch"], c["heads"], c["T"], c["P"], c["N"], dtype=torch.bfloat16,
+                            seed=rank)
+    case = case_h.to(dev)
+    U, M, K, B, C, dY = case.U, case.M, case.K, case.B, case.C, case.dY
+
+    def step_device():
+        _C.scan_fwd(U, M, K, B, C, None, None, None, chunk_size=c["chunk"], y_dtype=torch.bfloat16,
+                    want_final=False, path=args.path)
+        _C.scan_bwd(U, M, K, B, C, None, None, None, dY, None, chunk_size=c["chunk"], path=args.path)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    fwd_ms = bwd_ms = 0.0
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    barrier()
+    launches_before = _C.kernel_launches()
+    t_start.record()
+    for _ in range(args.steps):
+        step_device()
+    t_end.record()
+    barrier()
+    launches_timed = _C.kernel_launches() - launches_before
+    total_ms = t_start.elapsed_time(t_end)
+    # per-phase split (separate short loop so that the events do not perturb the headline)
+    for _ in range(min(args.steps, 5)):
+        e0.record()
+        _C.scan_fwd(U, M, K, B, C, None, None, None, chunk_size=c["chunk"], y_dtype=torch.bfloat16,
+                    want_final=False, path=args.path)
+        e1.record()
+        _C.scan_bwd(U, M, K, B, C, None, None, None, dY, None, chunk_size=c["chunk"], path=args.path)
+        e2.record()
+        torch.cuda.synchronize()
+        fwd_ms += e0.elapsed_time(e1)
+        bwd_ms += e1.elapsed_time(e2)
+    fwd_ms /= min(args.steps, 5)
+    bwd_ms /= min(args.steps, 5)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public op with host buffers --------------------------------
+    pin = lambda t: t.pin_memory()
+    h_in = [pin(t) for t in (case_h.U, case_h.M, case_h.K, case_h.B, case_h.C, case_h.dY)]
+    h2d = sum(t.numel() * t.element_size() for t in h_in)
+    d_in = [torch.empty_like(t, device=dev) for t in h_in]
+    h_out = None
+    d2h = 0
+
+    def step_e2e():
+        nonlocal h_out, d2h
+        for d, h in zip(d_in, h_in):
+            d.copy_(h, non_blocking=True)
+        leaves = [t.requires_grad_(True) for t in (x.detach() for x in d_in[:5])]
+        Y = v2x2ssd_cute(*leaves, chunk_size=c["chunk"], path=args.path)
+        grads = torch.autograd.grad(Y, leaves, d_in[5])
+        outs = (Y.detach(), *grads)
+        if h_out is None:
+            h_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+            d2h = sum(t.numel() * t.element_size() for t in h_out)
+        for h, o in zip(h_out, outs):
+            h.copy_(o, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    t_start.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    t_end.record()
+    barrier()
+    e2e_ms = t_start.elapsed_time(t_end)
+
+    times = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, fwd_ms, bwd_ms = times.tolist()
+    if rank == 0:
+        tokens_step = world * c["batch"] * c["T"]
+        ms_step = total_ms / args.steps
+        ab = algorithmic_bytes(c)
+        peak, peak_kind = measured_peak()
+        achieved = ab["total"] / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": tokens_step / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": tokens_step / (e2e_ms / e2e_steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches_timed,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
+                         "scope": "whole fwd+bwd step (all kernels); algorithmic bytes "
+                                  f"{ab['total']} per step",
+                         "fwd": {"ms": fwd_ms, "achieved": ab["fwd"] / (fwd_ms * 1e-3) / 1e9,
+                                 "frac": ab["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak},
+                         "bwd": {"ms": bwd_ms, "achieved": ab["bwd"] / (bwd_ms * 1e-3) / 1e9,
+                                 "frac": ab["bwd"] / (bwd_ms * 1e-3) / 1e9 / peak}},
+            "clocks": clocks,
+            "kernel_path": args.path,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(sample_heads=8)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

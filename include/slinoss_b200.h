@@ -69,6 +69,10 @@ enum {
 /* Library version, major*10000 + minor*100 + patch. */
 SL_API int sl_version(void);
 
+/* Number of CUDA kernels this library has launched in this process so far
+ * (monotonic; used by benchmarks to report their launch count). */
+SL_API unsigned long long sl_kernel_launches(void);
+
 /* Static, human readable text of a status code. */
 SL_API const char* sl_status_string(int status);
 

@@ -62,14 +62,18 @@ def foh_taps(dt, log_r, theta, rho, eps):
 
 
 def scan_coefficients(params, cfg, dt_bias, alpha_bias, theta_mod_bias, theta_bias,
-                      theta_sign):
+                      theta_sign, dtype=torch.float32):
     """params (B,T,H*3) -> M (B,H,T,2), K (B,H,T,2,2), both float32.
 
     ``cfg`` is a dict with dt_min, dt_max, alpha_min, alpha_max, theta_init_min,
-    theta_init_max, theta_mod_scale, r_min, r_max, eps."""
+    theta_init_max, theta_mod_scale, r_min, r_max, eps.  ``dtype`` is the arithmetic
+    type: float32 is what the reference does; float64 gives the exact value of the
+    same formulas (the tap quotients cancel badly in float32 for small |z|)."""
     bsz, T, _ = params.shape
     H = dt_bias.numel()
-    p = params.view(bsz, T, H, 3).permute(0, 2, 1, 3).to(torch.float32)
+    dt_bias, alpha_bias, theta_mod_bias, theta_bias, theta_sign = (
+        x.to(dtype) for x in (dt_bias, alpha_bias, theta_mod_bias, theta_bias, theta_sign))
+    p = params.view(bsz, T, H, 3).permute(0, 2, 1, 3).to(dtype)
     p = p + torch.stack((dt_bias, alpha_bias, theta_mod_bias), dim=-1).view(1, H, 1, 3)
     dt = cfg["dt_min"] + (cfg["dt_max"] - cfg["dt_min"]) * torch.sigmoid(p[..., 0])
     alpha = cfg["alpha_min"] + (cfg["alpha_max"] - cfg["alpha_min"]) * torch.sigmoid(p[..., 1])
@@ -103,7 +107,7 @@ def bc_pairs(bc, eps):
 
 
 def scanprep(value, params, bc, cfg, dt_bias, alpha_bias, theta_mod_bias, theta_bias,
-             theta_sign, d_head):
+             theta_sign, d_head, coeff_dtype=torch.float32):
     """(value (B,T,H*P), params (B,T,3H), bc (B,T,G,4,N)) -> U, M, K, B, C."""
     bsz, T, _ = value.shape
     H = dt_bias.numel()
@@ -113,7 +117,7 @@ def scanprep(value, params, bc, cfg, dt_bias, alpha_bias, theta_mod_bias, theta_
     Bo = bp.permute(0, 2, 1, 3, 4).reshape(bsz, G, T, 2 * N).contiguous()
     Co = cp.permute(0, 2, 1, 3, 4).reshape(bsz, G, T, 2 * N).contiguous()
     M, K = scan_coefficients(params, cfg, dt_bias, alpha_bias, theta_mod_bias, theta_bias,
-                             theta_sign)
+                             theta_sign, dtype=coeff_dtype)
     return U, M, K, Bo, Co
 
 

@@ -1,7 +1,12 @@
 // C-ABI entry points of the scan (argument validation and path selection).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace sl {
+
+static std::atomic<unsigned long long> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 // Implemented in scan_tc.cu (tcgen05 / TMEM chunked path).
 bool scan_tc_supported(const ScanDims& d, int io_dtype);
@@ -41,6 +46,10 @@ bool use_tc(int path, const ScanDims& d, int io_dtype) {
 }  // namespace sl
 
 extern "C" int sl_version(void) { return 100; }
+
+extern "C" unsigned long long sl_kernel_launches(void) {
+  return sl::g_launches.load(std::memory_order_relaxed);
+}
 
 extern "C" const char* sl_status_string(int status) {
   switch (status) {

@@ -52,6 +52,9 @@ inline bool dtype_ok(int dt) { return dt == SL_F32 || dt == SL_BF16 || dt == SL_
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// process-wide count of kernels this library has launched (see sl_kernel_launches)
+void note_launches(int n);
+
 inline int launch_status() {
   return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_LAUNCH_FAILED;
 }

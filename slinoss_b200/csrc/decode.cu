@@ -103,5 +103,6 @@ extern "C" int sl_v2x2ssd_decode(const void* U, const float* M, const float* K, 
         reinterpret_cast<const TIn*>(U_prev), reinterpret_cast<TY*>(Y), state_out, heads,
         groups, P, N);
   }));
+  note_launches(1);
   return launch_status();
 }

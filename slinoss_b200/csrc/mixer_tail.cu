@@ -180,6 +180,7 @@ extern "C" int sl_mixer_tail_fwd(const void* Y, const void* gate, int64_t gate_r
   const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   SL_DISPATCH_DTYPE(io_dtype, Tt, { tail_fwd_kernel<Tt><<<grid, TAIL_THREADS, 0, st>>>(p); });
+  note_launches(1);
   return launch_status();
 }
 
@@ -201,5 +202,6 @@ extern "C" int sl_mixer_tail_bwd(const void* Y, const void* gate, int64_t gate_r
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)heads * sizeof(float);
   SL_DISPATCH_DTYPE(io_dtype, Tt, { tail_bwd_kernel<Tt><<<grid, TAIL_THREADS, smem, st>>>(p); });
+  note_launches(1);
   return launch_status();
 }

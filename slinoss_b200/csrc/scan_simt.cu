@@ -634,6 +634,7 @@ int launch_fwd(const SweepParams& p, const SimtConfig& c, cudaStream_t st) {
   if (int e = set_smem(k, c.smem_fwd)) return e;
   dim3 grid(p.heads, p.batch, c.ptiles);
   k<<<grid, c.threads, c.smem_fwd, st>>>(p);
+  note_launches(1);
   return launch_status();
 }
 
@@ -646,6 +647,7 @@ int launch_bwd(const SweepParams& p, const SimtConfig& c, cudaStream_t st) {
   dim3 grid(p.heads, p.batch, c.ptiles);
   ka<<<grid, c.threads, c.smem_fwd, st>>>(p);
   kb<<<grid, c.threads, c.smem_rev, st>>>(p);
+  note_launches(2);
   return launch_status();
 }
 
@@ -711,6 +713,7 @@ int scan_simt_bwd(const void* U, const float* M, const float* K, const void* B, 
   const unsigned blocks = (unsigned)((rows + 7) / 8);
   SL_DISPATCH_DTYPE(io_dtype, TIn, { bwd_finish_kernel<TIn><<<blocks, 256, 0, st>>>(f); });
   bwd_dm_scan_kernel<<<d.batch * d.heads, 256, 0, st>>>(sterm, sT, M, dM, d.T);
+  note_launches(2);
   return launch_status();
 }
 

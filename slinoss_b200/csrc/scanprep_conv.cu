@@ -412,6 +412,7 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     p.batch = batch; p.T = T; p.C = heads * P; p.P = P; p.W = conv_weight ? d_conv : 1;
     dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, st>>>(p); });
+    note_launches(1);
   }
   if (bc) {
     if (!Bo || !Co || !cfg) return SL_ERR_NULL_POINTER;
@@ -423,6 +424,7 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
                                                reinterpret_cast<Tt*>(Co), batch, T, groups, N,
                                                cfg->eps);
     });
+    note_launches(1);
   }
   if (params) {
     if (!M || !K || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias || !theta_bias || !theta_sign)
@@ -434,6 +436,7 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     p.cfg = *cfg; p.M = M; p.K = K; p.batch = batch; p.T = T; p.H = heads;
     dim3 grid((T + 127) / 128, heads, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_fwd_kernel<Tt><<<grid, 128, 0, st>>>(p); });
+    note_launches(1);
   }
   return launch_status();
 }
@@ -462,6 +465,7 @@ extern "C" int sl_scanprep_conv_bwd(
     q.dU = dU; q.dx = d_value; q.dstate = d_conv_state; q.dw = d_conv_weight; q.dbias = d_conv_bias;
     dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+    note_launches(1);
   }
   if (dBo) {
     if (!dCo || !bc || !d_bc || !cfg) return SL_ERR_NULL_POINTER;
@@ -474,6 +478,7 @@ extern "C" int sl_scanprep_conv_bwd(
                                                reinterpret_cast<Tt*>(d_bc), batch, T, groups, N,
                                                cfg->eps);
     });
+    note_launches(1);
   }
   if (dM) {
     if (!dK || !params || !d_params || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias ||
@@ -488,6 +493,7 @@ extern "C" int sl_scanprep_conv_bwd(
     p.d_theta_bias = d_theta_bias; p.batch = batch; p.T = T; p.H = heads;
     dim3 grid((T + 127) / 128, heads, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_bwd_kernel<Tt><<<grid, 128, 0, st>>>(p); });
+    note_launches(1);
   }
   return launch_status();
 }

@@ -107,8 +107,9 @@ class SLinOSSMixer(nn.Module):
         return state
 
     def _fused_frontend(self) -> bool:
-        return (isinstance(self.cconv_backend, B200CConv1dBackend)
-                and isinstance(self.scanprep.backend, B200ScanPrepBackend) and self.d_conv <= 4)
+        # exact types: a subclass is an injected backend and gets the protocol path
+        return (type(self.cconv_backend) is B200CConv1dBackend
+                and type(self.scanprep.backend) is B200ScanPrepBackend and self.d_conv <= 4)
 
     def _frontend(self, value_proj, params, bc, conv_state, want_state):
         if self._fused_frontend():

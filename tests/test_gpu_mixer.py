@@ -1,0 +1,217 @@
+"""Parity of the CUDA scan-preparation / conv / tail kernels and of the whole mixer
+with the oracle and with golden vectors of the reference (through the C ABI)."""
+
+import numpy as np
+import pytest
+import torch
+
+import slinoss_b200 as sb
+from oracle import mixer_torch as mt
+from slinoss_b200.ops.mixer import mixer_gated_norm
+from slinoss_b200.ops.scanprep import causal_conv_silu_b200, conv_scanprep_b200, scanprep_b200
+from tests.util import rel, tol
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cfg(sp):
+    return {k: getattr(sp, k) for k in ("dt_min", "dt_max", "alpha_min", "alpha_max",
+                                        "theta_init_min", "theta_init_max", "theta_mod_scale",
+                                        "r_min", "r_max", "eps")}
+
+
+def _scanprep_module(heads, groups, N, P, seed=0):
+    torch.manual_seed(seed)
+    sp = sb.SLinOSSScanPrep(n_heads=heads, bc_groups=groups, d_state=N, d_head=P)
+    with torch.no_grad():
+        for p in sp.parameters():
+            p.add_(0.3 * torch.randn_like(p))
+    return sp
+
+
+def _oracle_prep(sp_cpu, value, params, bc, w=None, b=None, st=None):
+    v = value
+    nstate = None
+    if w is not None:
+        v, nstate = mt.causal_conv_silu(value, w, b, st)
+    # The tap quotients lose up to ~1e-4 relative accuracy in float32 (the reference's
+    # own arithmetic); the kernels evaluate them in float64, so they are held to 1e-5
+    # against the float64 evaluation of the same formulas.
+    out = mt.scanprep(v, params, bc, _cfg(sp_cpu), sp_cpu.dt_bias, sp_cpu.alpha_bias,
+                      sp_cpu.theta_mod_bias, sp_cpu.theta_bias, sp_cpu.theta_sign, sp_cpu.d_head,
+                      coeff_dtype=torch.float64)
+    return (*out, nstate)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dims", [(4, 2, 8, 16, 2, 12), (3, 3, 5, 8, 1, 37), (32, 32, 64, 64, 2, 70)])
+def test_scanprep_forward_backward(dims, dtype):
+    H, G, N, P, bsz, T = dims
+    sp_cpu = _scanprep_module(H, G, N, P)
+    sp = _scanprep_module(H, G, N, P).to(DEV)
+    gen = torch.Generator().manual_seed(1)
+    mk = lambda *s: torch.randn(*s, generator=gen).to(dtype)
+    value, params, bc = mk(bsz, T, H * P), mk(bsz, T, 3 * H), mk(bsz, T, G, 4, N)
+    cots = [mk(bsz, H, T, P), mk(bsz, H, T, 2).float(), mk(bsz, H, T, 2, 2).float(),
+            mk(bsz, G, T, 2 * N), mk(bsz, G, T, 2 * N)]
+    # oracle in float32 on the same (rounded) inputs
+    lv = lambda x: x.float().clone().requires_grad_(True)
+    ov, op_, obc = lv(value), lv(params), lv(bc)
+    want = _oracle_prep(sp_cpu, ov, op_, obc)[:5]
+    obias = [sp_cpu.dt_bias, sp_cpu.alpha_bias, sp_cpu.theta_mod_bias, sp_cpu.theta_bias]
+    wgrads = torch.autograd.grad(want, [ov, op_, obc, *obias], [c.float() for c in cots])
+    gv, gp, gbc = (x.to(DEV).requires_grad_(True) for x in (value, params, bc))
+    got = scanprep_b200(sp, gv, gp, gbc)
+    for name, a, w_ in zip("UMKBC", got, want):
+        t = 1e-5 if name in "MK" else tol(dtype)
+        assert rel(a, w_) <= t, (name, rel(a, w_))
+    gbias = [sp.dt_bias, sp.alpha_bias, sp.theta_mod_bias, sp.theta_bias]
+    ggrads = torch.autograd.grad(got, [gv, gp, gbc, *gbias], [c.to(DEV) for c in cots])
+    for name, a, w_ in zip(("value", "params", "bc", "dt_bias", "alpha_bias", "theta_mod_bias",
+                            "theta_bias"), ggrads, wgrads):
+        t = tol(dtype) if name in ("value", "params", "bc") else max(tol(dtype), 1e-4)
+        assert rel(a, w_) <= t, (name, rel(a, w_))
+
+
+def test_scanprep_against_reference_golden(golden):
+    g = golden("scanprep")
+    H, G, N, P = map(int, g["dims"])
+    sp = sb.SLinOSSScanPrep(n_heads=H, bc_groups=G, d_state=N, d_head=P).to(DEV)
+    with torch.no_grad():
+        for k in ("dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias"):
+            getattr(sp, k).copy_(torch.from_numpy(g[k]))
+    t = lambda k: torch.from_numpy(g[k]).to(DEV).requires_grad_(True)
+    value, params, bc = t("value"), t("params"), t("bc")
+    out = sp(value, params, bc)
+    for name in "UMKBC":
+        # K: the golden holds the reference's float32 taps, exact only to ~1e-4
+        assert rel(getattr(out, name), g[name]) <= (1e-4 if name == "K" else 1e-5), name
+    grads = torch.autograd.grad([out.U, out.M, out.K, out.B, out.C],
+                                [value, params, bc, sp.dt_bias, sp.alpha_bias, sp.theta_mod_bias,
+                                 sp.theta_bias],
+                                [torch.from_numpy(g["cot_" + k]).to(DEV) for k in "UMKBC"])
+    for name, gr in zip(("value", "params", "bc", "dt_bias", "alpha_bias", "theta_mod_bias",
+                         "theta_bias"), grads):
+        assert rel(gr, g["d_" + name]) <= 1e-4, (name, rel(gr, g["d_" + name]))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dims", [(2, 11, 64, 4, True), (1, 2, 40, 4, True), (3, 70, 96, 3, False),
+                                  (2, 33, 8, 2, True), (1, 5, 16, 1, False)])
+def test_conv_forward_backward(dims, dtype):
+    bsz, T, C, W, with_state = dims
+    gen = torch.Generator().manual_seed(3)
+    mk = lambda *s: torch.randn(*s, generator=gen).to(dtype)
+    x, w, b = mk(bsz, T, C), 0.5 * mk(C, W), mk(C)
+    st = mk(bsz, C, W - 1) if with_state and W > 1 else None
+    cot = mk(bsz, T, C)
+    lv = lambda v: None if v is None else v.float().clone().requires_grad_(True)
+    ox, ow, ob, ost = lv(x), lv(w), lv(b), lv(st)
+    wy, wn = mt.causal_conv_silu(ox, ow, ob, ost)
+    wl = [v for v in (ox, ow, ob, ost) if v is not None]
+    wg = torch.autograd.grad(wy, wl, cot.float())
+    gl = lambda v: None if v is None else v.to(DEV).requires_grad_(True)
+    gx, gw, gb, gst = gl(x), gl(w), gl(b), gl(st)
+    y, nxt = causal_conv_silu_b200(gx, gw, gb, gst)
+    assert rel(y, wy) <= tol(dtype) and rel(nxt, wn) <= 1e-6
+    gg = torch.autograd.grad(y, [v for v in (gx, gw, gb, gst) if v is not None], cot.to(DEV))
+    for a, w_ in zip(gg, wg):
+        assert rel(a, w_) <= tol(dtype), rel(a, w_)
+
+
+def test_conv_on_a_column_slice_and_reference_golden(golden):
+    g = golden("conv")
+    t = lambda k: torch.from_numpy(g[k]).to(DEV)
+    wide = torch.cat([torch.zeros_like(t("x")), t("x")], dim=-1)      # value is a column slice
+    x = wide[..., wide.shape[-1] // 2:].requires_grad_(True)
+    w, b, st = (t(k).requires_grad_(True) for k in ("weight", "bias", "state"))
+    y, nxt = causal_conv_silu_b200(x, w, b, st)
+    assert rel(y, g["y"]) <= 1e-5 and rel(nxt, g["next_state"]) <= 1e-6
+    grads = torch.autograd.grad(y, [x, st, w, b], t("cot"))
+    for name, gr in zip(("x", "state", "weight", "bias"), grads):
+        assert rel(gr, g["d_" + name]) <= 1e-5, name
+    y0, n0 = causal_conv_silu_b200(x, w, b, None)
+    assert rel(y0, g["y_nostate"]) <= 1e-5 and rel(n0, g["next_state_nostate"]) <= 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dims", [(2, 4, 9, 16), (1, 32, 70, 64), (2, 3, 5, 24)])
+def test_tail_forward_backward(dims, dtype):
+    bsz, H, T, P = dims
+    gen = torch.Generator().manual_seed(4)
+    mk = lambda *s: torch.randn(*s, generator=gen).to(dtype)
+    Y, U, gate = mk(bsz, H, T, P), mk(bsz, H, T, P), mk(bsz, T, H * P)
+    ds, nw = torch.randn(H, generator=gen), (1 + 0.2 * torch.randn(H * P, generator=gen)).to(dtype)
+    cot = mk(bsz, T, H * P)
+    lv = lambda v: v.clone().requires_grad_(True)
+    oY, oU, og, ods, onw = lv(Y), lv(U), lv(gate), lv(ds), lv(nw)
+    want = mt.gated_rmsnorm(oY, og, onw, 1e-5, oU, ods)
+    wg = torch.autograd.grad(want, [oY, og, oU, ods, onw], cot)
+    gl = lambda v: v.to(DEV).requires_grad_(True)
+    gY, gU, gg, gds, gnw = gl(Y), gl(U), gl(gate), gl(ds), gl(nw)
+    got = mixer_gated_norm(gY, gg, gnw, 1e-5, skip_input=gU, d_skip=gds)
+    assert rel(got, want) <= tol(dtype)
+    ggr = torch.autograd.grad(got, [gY, gg, gU, gds, gnw], cot.to(DEV))
+    for name, a, w_ in zip(("Y", "gate", "U", "d_skip", "norm_weight"), ggr, wg):
+        assert rel(a, w_) <= (tol(dtype) if dtype == torch.bfloat16 else 1e-4), (name, rel(a, w_))
+
+
+def _load_mixer(g, dtype=torch.float32, **kw):
+    m = sb.SLinOSSMixer(32, d_state=8, expand=2, d_head=16, d_conv=4, chunk_size=8, bc_groups=2, **kw)
+    m.load_state_dict({k[3:]: torch.from_numpy(v) for k, v in g.items() if k.startswith("sd_")})
+    return m.to(DEV)
+
+
+def test_mixer_against_reference_golden(golden):
+    g = golden("mixer")
+    m = _load_mixer(g)
+    x = torch.from_numpy(g["x"]).to(DEV).requires_grad_(True)
+    out = m(x)
+    assert rel(out, g["out"]) <= 5e-5
+    grads = torch.autograd.grad(out, [x, *m.parameters()], torch.from_numpy(g["cot"]).to(DEV))
+    assert rel(grads[0], g["d_x"]) <= 1e-4
+    for (name, _), gr in zip(m.named_parameters(), grads[1:]):
+        assert rel(gr, g["dp_" + name]) <= 1e-4, (name, rel(gr, g["dp_" + name]))
+    with torch.no_grad():
+        o1, st = m(x[:, :13], return_state=True)
+        o2, st2 = m(x[:, 13:], state=st, return_state=True)
+        assert rel(torch.cat([o1, o2], 1), g["out_segmented"]) <= 5e-5
+        assert rel(st2.scan.state, g["seg_state"]) <= 5e-5 and rel(st2.conv, g["seg_conv"]) <= 1e-6
+        state, ys = None, []
+        for t in range(3):
+            y, state = m.step(x[:, t], state)
+            ys.append(y)
+        assert rel(torch.stack(ys, 1), g["out_steps"]) <= 5e-5
+
+
+def test_mixer_bf16_close_to_float32():
+    torch.manual_seed(0)
+    m32 = sb.SLinOSSMixer(256, d_state=64, expand=2, d_head=64, chunk_size=64).to(DEV)
+    m16 = sb.SLinOSSMixer(256, d_state=64, expand=2, d_head=64, chunk_size=64).to(DEV)
+    m16.load_state_dict(m32.state_dict())
+    m16 = m16.to(torch.bfloat16)
+    x = torch.randn(2, 130, 256, device=DEV)
+    a = m32(x)
+    b = m16(x.to(torch.bfloat16))
+    assert b.dtype == torch.bfloat16 and rel(b, a) <= 5e-2
+    b.float().square().mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in m16.parameters())
+
+
+def test_stack_trains_one_step():
+    torch.manual_seed(0)
+    cfg = sb.SLinOSSStackConfig.uniform(
+        sb.SLinOSSBlockConfig(d_model=128, mixer=sb.SLinOSSMixerConfig(d_state=64, expand=1.0, d_head=64),
+                              ffn=sb.SLinOSSMLPConfig(kind="gelu", expand=4.0)), n_layers=2)
+    stack = sb.SLinOSSStack(cfg).to(DEV)
+    opt = torch.optim.AdamW(stack.parameters(), lr=1e-3)
+    x = torch.randn(2, 96, 128, device=DEV)
+    losses = []
+    for _ in range(3):
+        loss = stack(x).square().mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0]

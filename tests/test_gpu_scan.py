@@ -1,0 +1,193 @@
+"""Parity of the CUDA scan (forward, backward, decode) with the oracle.
+
+Every case runs through the public op, i.e. through the C ABI.  The oracle is
+evaluated in float64 on the very same (already rounded) inputs; the bar is
+``max|got-want| / max|want| <= 1e-5`` for float32 and ``<= 2e-2`` for bf16/fp16,
+per tensor, outputs and gradients alike.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import scan_np
+from slinoss_b200.ops.v2x2ssd import v2x2ssd, v2x2ssd_cute, v2x2ssd_decode
+from slinoss_b200.synthetic import make_scan_case
+from tests.util import n64, rel, tol
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+# (batch, heads, groups, T, P, N, chunk, streaming, init)
+SHAPES = [
+    (2, 4, 4, 256, 64, 32, 64, False, False),   # config 0
+    (2, 4, 2, 43, 16, 8, 16, True, True),       # grouped, ragged, streaming
+    (1, 2, 2, 1, 5, 3, 4, True, True),          # single token, odd sizes
+    (2, 2, 1, 17, 33, 5, 8, False, True),       # P not a multiple of 32, N odd
+    (1, 2, 2, 70, 64, 128, 64, True, False),    # N = 128 (the mixer default d_state)
+    (1, 3, 3, 33, 130, 8, 32, True, True),      # P > 64: several P tiles per head
+    (1, 2, 2, 63, 64, 64, 64, False, False),    # chunk - 1
+    (1, 2, 2, 64, 64, 64, 64, False, False),    # chunk
+    (1, 2, 2, 65, 64, 64, 64, True, True),      # chunk + 1
+]
+
+
+def _oracle_fwd(case):
+    return scan_np.v2x2ssm(*[n64(t) for t in case.tensors()], initial_states=n64(case.initial_states),
+                           B_prev=n64(case.B_prev), U_prev=n64(case.U_prev))
+
+
+def _run(case, chunk, path, **kw):
+    c = case.to(DEV)
+    return v2x2ssd(*c.tensors(), chunk_size=chunk, initial_states=c.initial_states,
+                   B_prev=c.B_prev, U_prev=c.U_prev, path=path, **kw)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_forward_simt(shape, dtype):
+    b, h, g, T, P, N, L, streaming, init = shape
+    case = make_scan_case(b, h, T, P, N, groups=g, dtype=dtype, seed=T + P, streaming=streaming,
+                          with_init=init)
+    Y, fin, Bl, Ul = _run(case, L, "simt")
+    wY, wfin, _, _ = _oracle_fwd(case)
+    assert Y.dtype == dtype and fin.dtype == dtype
+    assert rel(Y, wY) <= tol(dtype), rel(Y, wY)
+    assert rel(fin, wfin) <= tol(dtype)
+    assert torch.equal(Bl.cpu(), case.B[:, :, -1]) and torch.equal(Ul.cpu(), case.U[:, :, -1])
+
+
+def test_forward_config0_against_reference_golden(golden):
+    g = golden("scan_c0")
+    case = make_scan_case(2, 4, 256, 64, 32, seed=0)
+    Y, fin, _, _ = _run(case, 64, "simt")
+    assert rel(Y, g["Y"]) <= 1e-5 and rel(fin, g["final_state"]) <= 1e-5
+    assert rel(Y, g["Y_seq_fp64"]) <= 1e-5
+
+
+def test_float32_state_output_on_request():
+    case = make_scan_case(1, 2, 20, 8, 4, dtype=torch.bfloat16)
+    out = _run(case, 8, "simt", output_dtype=torch.float32)
+    assert all(t.dtype == torch.float32 for t in out)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_backward_simt(shape, dtype):
+    b, h, g, T, P, N, L, streaming, init = shape
+    case = make_scan_case(b, h, T, P, N, groups=g, dtype=dtype, seed=7 * T + N, streaming=streaming,
+                          with_init=init)
+    c = case.to(DEV)
+    names = ["U", "M", "K", "B", "C"] + (["initial_states"] if init else []) \
+        + (["B_prev", "U_prev"] if streaming else [])
+    leaves = {k: getattr(c, k).clone().requires_grad_(True) for k in names}
+    out = v2x2ssd(leaves["U"], leaves["M"], leaves["K"], leaves["B"], leaves["C"], chunk_size=L,
+                  initial_states=leaves.get("initial_states"), B_prev=leaves.get("B_prev"),
+                  U_prev=leaves.get("U_prev"), path="simt")
+    gen = torch.Generator().manual_seed(5)
+    d_final = torch.randn(out[1].shape, generator=gen).to(dtype)
+    grads = torch.autograd.grad([out[0], out[1]], list(leaves.values()), [c.dY, d_final.to(DEV)])
+    want = scan_np.v2x2ssd_bwd(*[n64(t) for t in case.tensors()], n64(case.dY),
+                               d_final_state=n64(d_final), initial_states=n64(case.initial_states),
+                               B_prev=n64(case.B_prev), U_prev=n64(case.U_prev))
+    for name, gr in zip(names, grads):
+        assert gr.dtype == leaves[name].dtype
+        assert rel(gr, want[name]) <= tol(dtype), (name, rel(gr, want[name]))
+
+
+def test_backward_against_reference_golden(golden):
+    g = golden("scan_grad")
+    t = lambda k: torch.from_numpy(g[k]).float().to(DEV).requires_grad_(True)
+    names = ("U", "M", "K", "B", "C", "initial_states", "B_prev", "U_prev")
+    ins = {k: t(k) for k in names}
+    Y, fin, _, _ = v2x2ssd(ins["U"], ins["M"], ins["K"], ins["B"], ins["C"], chunk_size=int(g["chunk"]),
+                           initial_states=ins["initial_states"], B_prev=ins["B_prev"],
+                           U_prev=ins["U_prev"], path="simt")
+    assert rel(Y, g["Y"]) <= 1e-5 and rel(fin, g["final_state"]) <= 1e-5
+    grads = torch.autograd.grad([Y, fin], list(ins.values()),
+                                [torch.from_numpy(g["dY"]).float().to(DEV),
+                                 torch.from_numpy(g["d_final_state"]).float().to(DEV)])
+    for name, gr in zip(names, grads):
+        assert rel(gr, g["d" + name]) <= 1e-5, (name, rel(gr, g["d" + name]))
+
+
+def test_gradients_of_b_last_and_u_last_reach_the_last_row():
+    case = make_scan_case(1, 2, 9, 4, 3).to(DEV)
+    U, B = case.U.clone().requires_grad_(True), case.B.clone().requires_grad_(True)
+    out = v2x2ssd(U, case.M, case.K, B, case.C, chunk_size=4, path="simt")
+    gU, gB = torch.autograd.grad([out[2].sum() + out[3].sum()], [U, B])
+    assert torch.all(gU[:, :, -1] == 1) and torch.all(gU[:, :, :-1] == 0)
+    assert torch.all(gB[:, :, -1] == 1) and torch.all(gB[:, :, :-1] == 0)
+
+
+def test_forward_is_deterministic_and_leaves_inputs_untouched():
+    case = make_scan_case(2, 4, 100, 64, 64, dtype=torch.bfloat16).to(DEV)
+    before = [t.clone() for t in case.tensors()]
+    a = v2x2ssd(*case.tensors(), chunk_size=64, path="simt")
+    b = v2x2ssd(*case.tensors(), chunk_size=64, path="simt")
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    assert all(torch.equal(x, y) for x, y in zip(before, case.tensors()))
+
+
+def test_segmented_equals_full_pass():
+    case = make_scan_case(2, 2, 150, 64, 64, seed=9, streaming=True, with_init=True).to(DEV)
+    kw = dict(chunk_size=64, path="simt")
+    Y, fin, _, _ = v2x2ssd(*case.tensors(), initial_states=case.initial_states, B_prev=case.B_prev,
+                           U_prev=case.U_prev, **kw)
+    cut = 77
+    sl = lambda t, a, b: t[:, :, a:b].contiguous()
+    Y1, f1, b1, u1 = v2x2ssd(*[sl(t, 0, cut) for t in case.tensors()],
+                             initial_states=case.initial_states, B_prev=case.B_prev,
+                             U_prev=case.U_prev, **kw)
+    Y2, f2, _, _ = v2x2ssd(*[sl(t, cut, 150) for t in case.tensors()], initial_states=f1, B_prev=b1,
+                           U_prev=u1, **kw)
+    assert rel(torch.cat([Y1, Y2], 2), Y) <= 1e-5 and rel(f2, fin) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_equals_forward_tokenwise(dtype):
+    case = make_scan_case(3, 4, 6, 64, 64, groups=2, dtype=dtype, streaming=True, with_init=True)
+    wY, wfin, _, _ = _oracle_fwd(case)
+    c = case.to(DEV)
+    state, bp, up = c.initial_states.clone(), c.B_prev, c.U_prev
+    for t in range(6):
+        y, state, bp, up = v2x2ssd_decode(c.U[:, :, t], c.M[:, :, t], c.K[:, :, t], c.B[:, :, t],
+                                          c.C[:, :, t], state=state, B_prev=bp, U_prev=up,
+                                          inplace=(t % 2 == 0))
+        assert rel(y, wY[:, :, t]) <= tol(dtype)
+    assert state.dtype == torch.float32 and rel(state, wfin) <= 1e-5
+
+
+def test_decode_odd_sizes():
+    case = make_scan_case(2, 3, 1, 5, 3, streaming=True, with_init=True)
+    wY, wfin, _, _ = _oracle_fwd(case)
+    c = case.to(DEV)
+    y, st, _, _ = v2x2ssd_decode(c.U[:, :, 0], c.M[:, :, 0], c.K[:, :, 0], c.B[:, :, 0], c.C[:, :, 0],
+                                 state=c.initial_states, B_prev=c.B_prev, U_prev=c.U_prev)
+    assert rel(y, wY[:, :, 0]) <= 1e-5 and rel(st, wfin) <= 1e-5
+
+
+def test_full_size_config1_properties():
+    """Config 1 (batch 8, heads 16, T 4096, P 64, N 64, bf16): too large for the CPU
+    oracle, so it is checked through size-independent properties: a slice of streams
+    against the oracle, exact homogeneity in U, and the segmented == full identity."""
+    case = make_scan_case(8, 16, 4096, 64, 64, dtype=torch.bfloat16, seed=0).to(DEV)
+    Y, fin, _, _ = v2x2ssd(*case.tensors(), chunk_size=64, output_dtype=torch.float32)
+    assert torch.isfinite(Y).all() and torch.isfinite(fin).all()
+    # one (batch, head) stream, first 512 tokens, against the float64 oracle
+    sl = lambda t: t[3:4, 5:6, :512].contiguous()
+    wY, _, _, _ = scan_np.v2x2ssm(*[n64(sl(t)) for t in case.tensors()])
+    assert rel(Y[3:4, 5:6, :512], wY) <= 2e-2
+    # doubling U doubles Y exactly (power-of-two scaling commutes with every rounding)
+    Y2, fin2, _, _ = v2x2ssd(case.U * 2, case.M, case.K, case.B, case.C, chunk_size=64,
+                             output_dtype=torch.float32)
+    assert torch.equal(Y2, Y * 2) and torch.equal(fin2, fin * 2)
+    # two segments with the carried state reproduce the single pass
+    cut = 2048 + 64
+    s1 = [t[:, :, :cut].contiguous() for t in case.tensors()]
+    s2 = [t[:, :, cut:].contiguous() for t in case.tensors()]
+    Ya, fa, ba, ua = v2x2ssd(*s1, chunk_size=64, output_dtype=torch.float32)
+    Yb, fb, _, _ = v2x2ssd(*s2, chunk_size=64, initial_states=fa, B_prev=ba.to(torch.bfloat16),
+                           U_prev=ua.to(torch.bfloat16), output_dtype=torch.float32)
+    assert rel(torch.cat([Ya, Yb], 2), Y) <= 2e-2 and rel(fb, fin) <= 2e-2
