@@ -250,7 +250,7 @@ __device__ __forceinline__ zc zconj_mul(zc a, zc b) {  // conj(a) * b
 
 struct CoeffOut {
   double dt, r, theta, ea;          // ea = exp(-alpha)
-  double sg_dt, sg_al, th_u, tanh2; // intermediates for the backward
+  double dsg_dt, dsg_al, dsg_thu, tanh2; // sigmoid derivatives etc. for the backward
   zc rho, k1, k2, dk1, dk2;         // kappa1, kappa2 and their z-derivatives
 };
 
@@ -277,7 +277,12 @@ __device__ __forceinline__ CoeffOut coeff_eval(float p0, float p1, float p2, flo
   const float ea = expf(-alpha);
   const float r = c.r_min + (c.r_max - c.r_min) * ea;
   o.dt = dt; o.r = r; o.theta = theta; o.ea = ea;
-  o.sg_dt = sdt; o.sg_al = sal; o.th_u = thu; o.tanh2 = (double)th * th;
+  // sigma'(x) = sigma(x) sigma(-x) = e / (1 + e)^2 with e = exp(-|x|): exact even where
+  // the sigmoid saturates (1 - sigma(x) would cancel in float32)
+  auto dsig = [](double x) { const double e = exp(-fabs(x)); return e / ((1.0 + e) * (1.0 + e)); };
+  o.dsg_dt = dsig((double)p0); o.dsg_al = dsig((double)p1);
+  o.dsg_thu = dsig((double)th_bias + (double)c.theta_mod_scale * (double)th);
+  o.tanh2 = (double)th * th;
   const double a = log((double)r);
   double sn, cs;
   sincos((double)theta, &sn, &cs);
@@ -359,9 +364,9 @@ __global__ void __launch_bounds__(128) coeff_bwd_kernel(CoeffParams p) {
     const double g_alpha = -(double)(p.cfg.r_max - p.cfg.r_min) * o.ea * g_r;
     const double span = fmax((double)p.cfg.theta_init_max - (double)p.cfg.theta_init_min, 1.0e-6);
     const double g_thu = span * (double)p.theta_sign[h] * gz.im;
-    const double g_x = o.th_u * (1.0 - o.th_u) * g_thu;
-    g0 = (float)((double)(p.cfg.dt_max - p.cfg.dt_min) * o.sg_dt * (1.0 - o.sg_dt) * g_dt);
-    g1 = (float)((double)(p.cfg.alpha_max - p.cfg.alpha_min) * o.sg_al * (1.0 - o.sg_al) * g_alpha);
+    const double g_x = o.dsg_thu * g_thu;
+    g0 = (float)((double)(p.cfg.dt_max - p.cfg.dt_min) * o.dsg_dt * g_dt);
+    g1 = (float)((double)(p.cfg.alpha_max - p.cfg.alpha_min) * o.dsg_al * g_alpha);
     g2 = (float)((double)p.cfg.theta_mod_scale * (1.0 - o.tanh2) * g_x);
     gx = (float)g_x;
     T* dp = reinterpret_cast<T*>(p.dparams) + ((size_t)b * p.T + t) * 3 * p.H + 3 * h;
