@@ -45,7 +45,8 @@ enum {
   SL_ERR_UNSUPPORTED = 4,
   SL_ERR_WORKSPACE_TOO_SMALL = 5,
   SL_ERR_LAUNCH_FAILED = 6,
-  SL_ERR_DEVICE_TIMEOUT = 7
+  SL_ERR_DEVICE_TIMEOUT = 7,
+  SL_ERR_STATIC_SCRATCH_EXCEEDED = 8
 };
 
 /* element types of the "io" tensors (U, B, C, Y, their gradients, gate, ...) */
@@ -111,6 +112,35 @@ SL_API int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, const v
                    int batch, int heads, int groups, int T, int P, int N, int chunk,
                    int io_dtype, int dy_dtype, int path, void* workspace,
                    size_t workspace_bytes, void* stream);
+
+/*
+ * Scan backward that allocates nothing and needs no scratch from the caller.
+ * (No counterpart in the reference: it exists for hosts of this library that cannot
+ * call cudaMalloc - the GPU already belongs to their own memory pool, their hot loop
+ * bans allocator calls, or they are inside a stream capture.)
+ *
+ * Same arguments and results as sl_v2x2ssd_bwd on the exact float32 (SIMT) path,
+ * minus chunk / path / workspace.  The scratch is a fixed array of
+ * SL_STATIC_SCRATCH_BYTES inside the library image, resident on every GPU that loads
+ * the library until the process exits.  Limits and rules:
+ *   - a problem needing more scratch (about batch*heads*T*(24*N+8) bytes) is refused
+ *     with SL_ERR_STATIC_SCRATCH_EXCEEDED and nothing is launched;
+ *   - every call shares the array, so calls whose kernels can overlap on the GPU
+ *     race: keep them on one stream or otherwise serialised;
+ *   - the array keeps the previous call's contents; each call itself clears the
+ *     part it accumulates into, so results never depend on them;
+ *   - the first call on each device looks up the array's device address on the host;
+ *     issue that first call before starting any stream capture.
+ */
+#define SL_STATIC_SCRATCH_BYTES (64u << 20)
+SL_API size_t sl_static_scratch_bytes(void);
+SL_API int sl_v2x2ssd_bwd_static(const void* U, const float* M, const float* K, const void* B,
+                                 const void* C, const float* initial_states, const void* B_prev,
+                                 const void* U_prev, const void* dY, const float* d_final_state,
+                                 void* dU, float* dM, float* dK, void* dB, void* dC,
+                                 float* d_initial, void* dB_prev, void* dU_prev, int batch,
+                                 int heads, int groups, int T, int P, int N, int io_dtype,
+                                 int dy_dtype, void* stream);
 
 /*
  * One-token decode of the scan (T = 1) over the carried float32 state.

@@ -45,6 +45,8 @@ _PROTOTYPES = {
     "sl_workspace_bytes": (c_size_t, [c_int] * 10),
     "sl_v2x2ssd_fwd": (c_int, [_P] * 10 + [c_int] * 10 + [_P, c_size_t, _P]),
     "sl_v2x2ssd_bwd": (c_int, [_P] * 18 + [c_int] * 10 + [_P, c_size_t, _P]),
+    "sl_static_scratch_bytes": (c_size_t, []),
+    "sl_v2x2ssd_bwd_static": (c_int, [_P] * 18 + [c_int] * 8 + [_P]),
     "sl_v2x2ssd_decode": (c_int, [_P] * 10 + [c_int] * 7 + [_P]),
     "sl_scanprep_conv_fwd": (c_int, [_P, c_int64, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, _P,
                                      ctypes.POINTER(ScanPrepConfig), _P, c_int64, c_int64, c_int64,
@@ -181,6 +183,25 @@ def scan_bwd(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *, chunk_size, path
             _ptr(d_init), _ptr(dB_prev), _ptr(dU_prev), batch, heads, groups, T, P, N,
             chunk_size, io, dy_code, pcode, _ptr(ws), nbytes, _stream(dev)), "sl_v2x2ssd_bwd")
     return dU, dM, dK, dB, dC, d_init, dB_prev, dU_prev
+
+
+def scan_bwd_static(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, outs):
+    """Launch ``sl_v2x2ssd_bwd_static``: the float32-exact backward with its scratch in the
+    library's built-in array, for callers that may not allocate device memory.
+
+    Nothing is allocated here either: ``outs`` is the tuple of caller-provided result
+    tensors ``(dU, dM, dK, dB, dC, d_initial, dB_prev, dU_prev)`` (the last three may be
+    None).  Calls share the one scratch array, so keep them on one stream."""
+    dev = require_cuda(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *outs)
+    batch, heads, T, P = U.shape
+    groups, N = B.shape[1], B.shape[3] // 2
+    dy_code = dtype_code(dY.dtype) if dY is not None else dtype_code(U.dtype)
+    with torch.cuda.device(dev):
+        check(lib().sl_v2x2ssd_bwd_static(
+            _ptr(U), _ptr(M), _ptr(K), _ptr(B), _ptr(C), _ptr(z0), _ptr(B_prev), _ptr(U_prev),
+            _ptr(dY), _ptr(d_final), *[_ptr(o) for o in outs], batch, heads, groups, T, P, N,
+            dtype_code(U.dtype), dy_code, _stream(dev)), "sl_v2x2ssd_bwd_static")
+    return outs
 
 
 def scan_decode(U, M, K, B, C, state, B_prev, U_prev, *, y_dtype, state_out=None):

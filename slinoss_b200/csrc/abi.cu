@@ -61,6 +61,8 @@ extern "C" const char* sl_status_string(int status) {
     case SL_ERR_WORKSPACE_TOO_SMALL: return "workspace missing or too small";
     case SL_ERR_LAUNCH_FAILED: return "CUDA launch failed";
     case SL_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case SL_ERR_STATIC_SCRATCH_EXCEEDED:
+      return "problem needs more scratch than the built-in static array holds";
     default: return "unknown status";
   }
 }

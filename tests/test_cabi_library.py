@@ -22,7 +22,7 @@ def lib():
 def test_header_symbols_are_exported(lib):
     header = (ROOT / "include" / "slinoss_b200.h").read_text()
     declared = re.findall(r"SL_API\s+[\w\s\*]+?\b(sl_\w+)\s*\(", header)
-    assert len(declared) == 11 and set(declared) == set(_C.EXPORTED_SYMBOLS)
+    assert len(declared) == 13 and set(declared) == set(_C.EXPORTED_SYMBOLS)
     for name in declared:
         assert getattr(lib, name) is not None
 
@@ -30,8 +30,8 @@ def test_header_symbols_are_exported(lib):
 def test_version_and_status_strings(lib):
     assert lib.sl_version() >= 100
     assert lib.sl_status_string(0) == b"ok"
-    texts = {lib.sl_status_string(i) for i in range(8)}
-    assert len(texts) == 8 and lib.sl_status_string(99) == b"unknown status"
+    texts = {lib.sl_status_string(i) for i in range(9)}
+    assert len(texts) == 9 and lib.sl_status_string(99) == b"unknown status"
 
 
 def test_workspace_sizes(lib):
