@@ -74,6 +74,12 @@ SL_API int sl_version(void);
  * (monotonic; used by benchmarks to report their launch count). */
 SL_API unsigned long long sl_kernel_launches(void);
 
+/* First error recorded by a kernel of this library on the current device since load
+ * (0 = none; a bounded device-side wait that expired reports its site here).  The
+ * entry points are asynchronous, so such errors surface here, not in their return
+ * value.  Synchronises with the device. */
+SL_API int sl_device_status(void);
+
 /* Static, human readable text of a status code. */
 SL_API const char* sl_status_string(int status);
 

@@ -41,6 +41,7 @@ _P = c_void_p
 _PROTOTYPES = {
     "sl_version": (c_int, []),
     "sl_kernel_launches": (ctypes.c_ulonglong, []),
+    "sl_device_status": (c_int, []),
     "sl_status_string": (ctypes.c_char_p, [c_int]),
     "sl_workspace_bytes": (c_size_t, [c_int] * 10),
     "sl_v2x2ssd_fwd": (c_int, [_P] * 10 + [c_int] * 10 + [_P, c_size_t, _P]),
@@ -86,6 +87,11 @@ def lib():
 def kernel_launches() -> int:
     """Kernels launched by the library in this process so far."""
     return int(lib().sl_kernel_launches())
+
+
+def device_status() -> int:
+    """First device-side error recorded by the kernels (0 = none); synchronises."""
+    return int(lib().sl_device_status())
 
 
 def check(status: int, what: str) -> None:

@@ -22,6 +22,8 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
                 float* dinit, void* dBprev, void* dUprev, const ScanDims& d, int io_dtype,
                 int dy_dtype, void* ws, size_t ws_bytes, cudaStream_t st);
 
+int scan_tc_device_status();
+
 namespace {
 
 int check_scan(const void* U, const float* M, const float* K, const void* B, const void* C,
@@ -50,6 +52,8 @@ extern "C" int sl_version(void) { return 100; }
 extern "C" unsigned long long sl_kernel_launches(void) {
   return sl::g_launches.load(std::memory_order_relaxed);
 }
+
+extern "C" int sl_device_status(void) { return sl::scan_tc_device_status(); }
 
 extern "C" const char* sl_status_string(int status) {
   switch (status) {

@@ -191,3 +191,58 @@ def test_full_size_config1_properties():
     Yb, fb, _, _ = v2x2ssd(*s2, chunk_size=64, initial_states=fa, B_prev=ba.to(torch.bfloat16),
                            U_prev=ua.to(torch.bfloat16), output_dtype=torch.float32)
     assert rel(torch.cat([Ya, Yb], 2), Y) <= 2e-2 and rel(fb, fin) <= 2e-2
+
+
+# ---- tensor-core (tcgen05) path: P = 64, N = 64, 16-bit operands -------------------------------
+TC_SHAPES = [
+    (1, 1, 1, 64, False, False),
+    (2, 4, 2, 1, True, True),
+    (1, 2, 2, 63, False, True),
+    (1, 2, 2, 65, True, False),
+    (2, 4, 4, 200, True, True),
+    (1, 4, 1, 333, False, False),
+    (2, 2, 2, 1024, True, True),
+]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_forward_tensor_core_path(shape, dtype):
+    from slinoss_b200 import _C
+    b, h, g, T, streaming, init = shape
+    case = make_scan_case(b, h, T, 64, 64, groups=g, dtype=dtype, seed=3 * T + b, streaming=streaming,
+                          with_init=init)
+    Y, fin, _, _ = _run(case, 64, "tc", output_dtype=torch.float32)
+    wY, wfin, _, _ = _oracle_fwd(case)
+    assert _C.device_status() == 0
+    assert rel(Y, wY) <= 2e-2, rel(Y, wY)
+    assert rel(fin, wfin) <= 2e-2, rel(fin, wfin)
+    Yh = _run(case, 64, "tc")[0]
+    assert Yh.dtype == dtype and rel(Yh, wY) <= 2e-2
+
+
+def test_tensor_core_path_agrees_with_exact_path_on_reference_test_distribution():
+    """|m| in [0.6, 0.95] (the reference's own test generator): strong decay inside a chunk."""
+    import math
+    gen = torch.Generator().manual_seed(0)
+    b, h, T = 2, 3, 300
+    radius = 0.6 + 0.35 * torch.rand(b, h, T, generator=gen)
+    angle = (2 * torch.rand(b, h, T, generator=gen) - 1) * math.pi
+    M = torch.stack((radius * torch.cos(angle), radius * torch.sin(angle)), -1).to(DEV)
+    K = (0.1 * torch.randn(b, h, T, 2, 2, generator=gen)).to(DEV)
+    U = torch.randn(b, h, T, 64, generator=gen).to(torch.bfloat16).to(DEV)
+    B = (0.1 * torch.randn(b, h, T, 128, generator=gen)).to(torch.bfloat16).to(DEV)
+    C = (0.1 * torch.randn(b, h, T, 128, generator=gen)).to(torch.bfloat16).to(DEV)
+    a = v2x2ssd(U, M, K, B, C, chunk_size=64, path="tc", output_dtype=torch.float32)
+    e = v2x2ssd(U, M, K, B, C, chunk_size=64, path="simt", output_dtype=torch.float32)
+    assert rel(a[0], e[0]) <= 2e-2 and rel(a[1], e[1]) <= 2e-2
+
+
+def test_auto_path_prefers_tensor_cores_and_falls_back_for_float32():
+    from slinoss_b200 import _C
+    assert _C.workspace_bytes(_C.WS_SCAN_FWD, 1, 1, 1, 64, 64, 64, 64, torch.bfloat16, "auto") == 0
+    case = make_scan_case(1, 2, 70, 64, 64, dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        _run(case, 64, "tc")
+    Y = _run(case, 64, "auto")[0]
+    assert rel(Y, _oracle_fwd(case)[0]) <= 1e-5
