@@ -28,6 +28,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -58,7 +60,7 @@ struct alignas(64) TcFwdParams {
   const void* Uprev;
   void* Y;
   float* zfinal;
-  float* chunk_states;  // optional (batch, heads, nchunks, P, 2N): start state of every chunk
+  void* states16;       // optional (batch*heads, nchunks, 64, 128) 16-bit: conjugated start state of every chunk
   int heads, groups, T, nchunks;
 };
 
@@ -91,7 +93,7 @@ __device__ __forceinline__ void report_timeout(int code) { atomicCAS(&g_tc_statu
 //  sc[4],sc[5] w_t = conj(phi_t) g_t                (K'  = w b)
 //  sc[6],sc[7] v_t = exp(l_end - l_t) phi_end w_t   (K'' = v b)
 //  sc[8],sc[9] kc_t                                 (diagonal)
-//  chunk-level: sc[10][0..1] = Pi_end
+//  chunk-level: sc[10][0..1] = Pi_end, sc[10][2..3] = its unit phase
 __device__ void chunk_scalars(float* sc, const float* __restrict__ Mb, const float* __restrict__ Kb,
                               int t0, int T, int lane) {
   float mr[3], mi[3], kpr[3], kpi[3], kcr[2], kci[2];
@@ -157,10 +159,12 @@ __device__ void chunk_scalars(float* sc, const float* __restrict__ Mb, const flo
   if (lane == 0) {
     const float e = __expf(l_end);
     sc[10 * 64 + 0] = e * per; sc[10 * 64 + 1] = e * pei;
+    sc[10 * 64 + 2] = per; sc[10 * 64 + 3] = pei;   // unit phase of Pi_end
   }
 }
 
-template <typename TIn, typename TY>
+// STATES_ONLY: the state pre-sweep of the backward pass (no C, no scores, no Y).
+template <typename TIn, typename TY, bool STATES_ONLY>
 __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -196,12 +200,14 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
   auto issue_loads = [&](int c) {   // one thread
     uint8_t* st = smem + (c & 1) * STAGE;
     uint64_t* bar = &bar_tma[c & 1];
-    mbar_expect_tx(bar, STAGE);
+    mbar_expect_tx(bar, STATES_ONLY ? 3 * TILE : STAGE);
     tma_load_3d(st, &p.tmU, bar, 0, c * L, bh);
     tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bg);
     tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bg);
-    tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bg);
-    tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bg);
+    if (!STATES_ONLY) {
+      tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bg);
+      tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bg);
+    }
   };
   if (tid == 0) issue_loads(0);
 
@@ -243,13 +249,16 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
       *reinterpret_cast<uint4*>(zt + sw128(row, ch)) = v;
     }
   };
-  auto store_chunk_state = [&](int c) {
-    if (!p.chunk_states) return;
-    float* dst = p.chunk_states + (((size_t)bh * p.nchunks + c) * 64 + row) * 128 + 64 * hf;
+  auto store_chunk_state = [&](int c) {   // conjugated form, 16-bit, row-major [p][128]
+    if (!p.states16) return;
+    TIn* dst = reinterpret_cast<TIn*>(p.states16) + (((size_t)bh * p.nchunks + c) * 64 + row) * 128 + 64 * hf;
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      *reinterpret_cast<float4*>(dst + 4 * j) =
-          make_float4(zv[4 * j], -zv[4 * j + 1], zv[4 * j + 2], -zv[4 * j + 3]);
+    for (int ch = 0; ch < 8; ++ch) {
+      uint4 v;
+      v.x = PK::pack(zv[8 * ch + 0], zv[8 * ch + 1]); v.y = PK::pack(zv[8 * ch + 2], zv[8 * ch + 3]);
+      v.z = PK::pack(zv[8 * ch + 4], zv[8 * ch + 5]); v.w = PK::pack(zv[8 * ch + 6], zv[8 * ch + 7]);
+      *reinterpret_cast<uint4*>(dst + 8 * ch) = v;
+    }
   };
   store_zv_tile();
 
@@ -285,7 +294,8 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
         const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
         const float vr = sc[6 * 64 + r], vi = sc[7 * 64 + r];
         const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
-        const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
+        uint4 cv = make_uint4(0u, 0u, 0u, 0u);
+        if (!STATES_ONLY) cv = *reinterpret_cast<const uint4*>(tC + off);
         const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
         const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
         uint32_t qo[4], ko[4], vo[4];
@@ -299,17 +309,20 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
           const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
           dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
         }
-        *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
-        *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
         *reinterpret_cast<uint4*>(tK + off) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
+        if (!STATES_ONLY) {
+          *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+          *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
-        if (rcol == 0) s_diag[r] = dg;
+          for (int o = 8; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
+          if (rcol == 0) s_diag[r] = dg;
+        }
       }
     }
     fence_async_smem();
     __syncthreads();
 
+    if (!STATES_ONLY) {
     // ---- MMA group 1: scores and off-term ------------------------------------------------------
     if (tid == 0) {
       tc_fence_after_sync();
@@ -361,6 +374,7 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
     tc_fence_before_sync();
     __syncthreads();
     if (s_abort) { ok = false; break; }
+    }  // !STATES_ONLY
 
     // ---- MMA group 2: Y_diag = S U, Inc = U^T K'' ------------------------------------------------------
     if (tid == 0) {
@@ -371,8 +385,9 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
         const uint32_t dY = tmem + ((16u * q) << 16) + 64, dZ = tmem + ((16u * q) << 16) + 128;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma(dY, make_desc(aS + 32 * k, 16, 1024), make_desc(aU + 64 * q + 2048 * k, 8192, 1024), ID_Y,
-               k > 0);
+          if (!STATES_ONLY)
+            umma(dY, make_desc(aS + 32 * k, 16, 1024), make_desc(aU + 64 * q + 2048 * k, 8192, 1024), ID_Y,
+                 k > 0);
           umma(dZ, make_desc(aU + 2048 * k, 8192, 1024), make_desc(aKPP + TILE * q + 2048 * k, 8192, 1024),
                ID_Z, k > 0);
         }
@@ -384,7 +399,7 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
     tc_fence_after_sync();
 
     // ---- output epilogue: y = Y_diag + exp(l_t) Y_off ---------------------------------------------------
-    {
+    if (!STATES_ONLY) {
       uint32_t yd[32], yo[32];
       tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 64, yd);
       tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 32, yo);
@@ -457,6 +472,8 @@ __global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_consta
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+#include "scan_tc_bwd.cuh"
+
 }  // namespace
 
 bool scan_tc_supported(const ScanDims& d, int io_dtype) {
@@ -464,11 +481,33 @@ bool scan_tc_supported(const ScanDims& d, int io_dtype) {
          tc::encode_tiled_fn() != nullptr;
 }
 size_t scan_tc_fwd_workspace(const ScanDims&) { return 0; }
-size_t scan_tc_bwd_workspace(const ScanDims& d) { return scan_simt_bwd_workspace(d); }
+namespace {
+struct TcBwdLayout {
+  size_t states, zfinal, dg, sterm, dkcd, anchor, total;
+};
+TcBwdLayout tc_bwd_layout(const ScanDims& d) {
+  const size_t BH = (size_t)d.batch * d.heads, nC = (d.T + L - 1) / L;
+  TcBwdLayout o{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t r = off; off += round_up(bytes, 256); return r; };
+  o.states = take(BH * nC * 64 * 128 * 2);
+  o.zfinal = take(BH * 64 * 128 * 4);
+  o.dg = take(BH * d.T * 8);
+  o.sterm = take(BH * d.T * 8);
+  o.dkcd = take(BH * d.T * 8);
+  o.anchor = take(BH * nC * 8);
+  o.total = off;
+  return o;
+}
+}  // namespace
 
-template <typename TIn, typename TY>
+size_t scan_tc_bwd_workspace(const ScanDims& d) {
+  return std::max(scan_simt_bwd_workspace(d), tc_bwd_layout(d).total);
+}
+
+template <typename TIn, typename TY, bool STATES_ONLY>
 static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
-  auto k = scan_tc_fwd_kernel<TIn, TY>;
+  auto k = scan_tc_fwd_kernel<TIn, TY, STATES_ONLY>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess)
     return SL_ERR_LAUNCH_FAILED;
   k<<<grid, 128, SMEM_BYTES, st>>>(p);
@@ -476,25 +515,29 @@ static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
   return launch_status();
 }
 
+// Y == nullptr runs the state pre-sweep only (chunk-start states + final state).
 int scan_tc_fwd_impl(const void* U, const float* M, const float* K, const void* B, const void* C,
                      const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
-                     float* chunk_states, const ScanDims& d, int io_dtype, int y_dtype,
+                     void* states16, const ScanDims& d, int io_dtype, int y_dtype,
                      cudaStream_t st) {
   TcFwdParams p{};
   const bool bf = io_dtype == SL_BF16;
   const uint64_t BH = (uint64_t)d.batch * d.heads, BG = (uint64_t)d.batch * d.groups;
   if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BG, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BG, 64, bf))
+      !tc::make_tmap_3d(&p.tmC, C ? C : B, 128, d.T, BG, 64, bf))
     return SL_ERR_LAUNCH_FAILED;
   p.M = M; p.K = K; p.z0 = z0; p.Bprev = Bprev; p.Uprev = Uprev; p.Y = Y; p.zfinal = zfinal;
-  p.chunk_states = chunk_states;
+  p.states16 = states16;
   p.heads = d.heads; p.groups = d.groups; p.T = d.T; p.nchunks = (d.T + L - 1) / L;
   const int grid = (int)BH;
   int rc = SL_ERR_UNSUPPORTED;
-  if (bf) {
-    SL_DISPATCH_DTYPE(y_dtype, TY, { rc = launch_tc_fwd<__nv_bfloat16, TY>(p, grid, st); });
+  if (!Y) {
+    rc = bf ? launch_tc_fwd<__nv_bfloat16, float, true>(p, grid, st)
+            : launch_tc_fwd<__half, float, true>(p, grid, st);
+  } else if (bf) {
+    SL_DISPATCH_DTYPE(y_dtype, TY, { rc = launch_tc_fwd<__nv_bfloat16, TY, false>(p, grid, st); });
   } else {
-    SL_DISPATCH_DTYPE(y_dtype, TY, { rc = launch_tc_fwd<__half, TY>(p, grid, st); });
+    SL_DISPATCH_DTYPE(y_dtype, TY, { rc = launch_tc_fwd<__half, TY, false>(p, grid, st); });
   }
   return rc;
 }
@@ -505,14 +548,50 @@ int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, co
   return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, nullptr, d, io_dtype, y_dtype, st);
 }
 
-// The backward still runs the exact float32 sweeps (tensor-core backward: next step).
+// Tensor-core backward: state pre-sweep, reverse sweep, scalar finish.  Cases it does not
+// cover (grouped B/C, carried B_prev/U_prev, dY of another dtype or absent) take the exact
+// float32 sweeps.
 int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                 const float* z0, const void* Bprev, const void* Uprev, const void* dY,
                 const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC, float* dinit,
                 void* dBprev, void* dUprev, const ScanDims& d, int io_dtype, int dy_dtype, void* ws,
                 size_t ws_bytes, cudaStream_t st) {
-  return scan_simt_bwd(U, M, K, B, C, z0, Bprev, Uprev, dY, dfinal, dU, dM, dK, dB, dC, dinit, dBprev,
-                       dUprev, d, io_dtype, dy_dtype, ws, ws_bytes, st);
+  if (d.groups != d.heads || Bprev || !dY || dy_dtype != io_dtype)
+    return scan_simt_bwd(U, M, K, B, C, z0, Bprev, Uprev, dY, dfinal, dU, dM, dK, dB, dC, dinit, dBprev,
+                         dUprev, d, io_dtype, dy_dtype, ws, ws_bytes, st);
+  const TcBwdLayout lay = tc_bwd_layout(d);
+  if (!ws || ws_bytes < lay.total) return SL_ERR_WORKSPACE_TOO_SMALL;
+  uint8_t* w = reinterpret_cast<uint8_t*>(ws);
+  const bool bf = io_dtype == SL_BF16;
+  const uint64_t BH = (uint64_t)d.batch * d.heads;
+  const int nC = (d.T + L - 1) / L;
+  float* zfinal = reinterpret_cast<float*>(w + lay.zfinal);
+  if (int e = scan_tc_fwd_impl(U, M, K, B, nullptr, z0, nullptr, nullptr, nullptr, zfinal, w + lay.states, d,
+                               io_dtype, SL_F32, st))
+    return e;
+  TcBwdParams p{};
+  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmZ, w + lay.states, 128, (uint64_t)nC * 64, BH, 64, bf))
+    return SL_ERR_LAUNCH_FAILED;
+  p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal; p.dU = dU; p.dB = dB; p.dC = dC;
+  p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
+  p.dkcd = reinterpret_cast<float2*>(w + lay.dkcd); p.anchor = reinterpret_cast<float2*>(w + lay.anchor);
+  p.dinit = dinit; p.T = d.T; p.nchunks = nC;
+  if (bf) {
+    auto k = scan_tc_bwd_kernel<__nv_bfloat16>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
+      return SL_ERR_LAUNCH_FAILED;
+    k<<<(int)BH, 128, B_SMEM_BYTES, st>>>(p);
+  } else {
+    auto k = scan_tc_bwd_kernel<__half>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
+      return SL_ERR_LAUNCH_FAILED;
+    k<<<(int)BH, 128, B_SMEM_BYTES, st>>>(p);
+  }
+  scan_tc_bwd_finish_kernel<<<(int)BH, 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
+  note_launches(2);
+  return launch_status();
 }
 
 int scan_tc_device_status() {

@@ -1,0 +1,531 @@
+// Backward of the chunked scan on tcgen05 (included by scan_tc.cu inside its namespaces).
+//
+// With V_t = m_t W_{t-1} (state after the decay, before the injection of token t):
+//     y_t = Re<c_t, V_t> + u_t Re(conj(c_t) kc_t b_t),      W_t = V_t + u_t (x) (g_t b_t).
+// One CTA walks the chunks of one (batch, head) in REVERSE order carrying
+// dz = adjoint of the chunk-end state (conjugated pairs, float32, in registers).
+// Per chunk, with the same rotated operands as the forward (unit phases on the 16-bit
+// operands, decays exp(<=0) on float32 accumulators):
+//     P~ = Q K'^T,  dS = dY U^T      -> Pdec = mask_{s<t} e^{l_t-l_s} P~ ,  dP = mask_{s<t} e^{l_t-l_s} dS
+//     dQ = dP K' + e^{l_t} (dY Zv)                     -> dC  (un-rotate, + diagonal term)
+//     dX = dP^T Q + e^{l_end-l_s} (U dWv)              -> dB, dg   (dWv = dz rotated by the unit phase of Pi_end)
+//     dU = Pdec^T dY + e^{l_end-l_s} (K' dWv^T)        (+ dy_s diag_s)
+//     dz <- e^{l_end} dWv + (e^{l_t} dY)^T Q           (adjoint of the chunk-start state)
+// Per-token scalars for dM / dK go to the workspace and are finished by
+// scan_tc_bwd_finish_kernel using
+//     conj(m_t) dm_t = S_t,   S_t = S_{t+1} + <q_t, dq_t> - conj(g_t) dg_t,
+// anchored at every chunk end by S = <dZ, Z> of the state carried across that boundary.
+
+constexpr uint32_t B_STAGE = 8 * TILE;                 // U | B(2) | C(2) | dY | Zv(2)
+constexpr uint32_t B_OFF_Q = 2 * B_STAGE;              // Q (2)
+constexpr uint32_t B_OFF_KP = B_OFF_Q + 2 * TILE;      // K' (2)
+constexpr uint32_t B_OFF_DYO = B_OFF_KP + 2 * TILE;    // e^{l_t} dY (1)
+constexpr uint32_t B_OFF_PD = B_OFF_DYO + TILE;        // Pdec (1)
+constexpr uint32_t B_OFF_DP = B_OFF_PD + TILE;         // dP (1)
+constexpr uint32_t B_OFF_DW = B_OFF_DP + TILE;         // dWv (2)
+constexpr uint32_t B_OFF_SCAL = B_OFF_DW + 2 * TILE;
+constexpr int B_NSCAL = 24;
+constexpr uint32_t B_SMEM_BYTES = B_OFF_SCAL + B_NSCAL * 64 * 4 + 1024;
+// TMEM columns: P~ 0 | dS 32 | dQa 64 | dQb 128 | dXa 192 | dXb 256 | dUa 320 | dUb 352 | dZ 384
+constexpr uint32_t B_TMEM_COLS = 512;
+
+struct alignas(64) TcBwdParams {
+  CUtensorMap tmU, tmB, tmC, tmdY, tmZ;
+  const float* M;
+  const float* K;
+  const float* dfinal;   // (BH, 64, 128) or null
+  const float* zfinal;   // forward final state (pre-sweep), read when dfinal is given
+  void *dU, *dB, *dC;
+  float2 *dg, *sterm, *dkcd, *anchor;   // per token / per chunk scalars (workspace)
+  float* dinit;          // (BH, 64, 128) adjoint of the carried start state, or null
+  int T, nchunks;
+};
+
+// Per-token table: rows 0..10 as written by chunk_scalars, then
+//  11 e^{l_end-l_t}   12 sigma_t = <dy_t,u_t>   13 diag_t   14,15 sum_n c conj(b)
+//  16,17 / 18,19  re / im of <q,dq> per column half     20,21 / 22,23  re / im of sum conj(b) dX
+template <typename TIn>
+__global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ uint64_t bar_tma[2], bar_mma[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  __shared__ float s_red[8];
+  float* sc = reinterpret_cast<float*>(smem + B_OFF_SCAL);
+  using PK = Pack2<TIn>;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = 16 * warp + (lane & 15), hf = lane >> 4;
+  const int rcol = tid & 15, rrow0 = tid >> 4;
+  const int bh = blockIdx.x;
+  const int T = p.T, nC = p.nchunks;
+  const float* Mb = p.M + (size_t)bh * T * 2;
+  const float* Kb = p.K + (size_t)bh * T * 4;
+  const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+
+  if (tid == 0) {
+    mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
+    mbar_init(&bar_mma[0], 1); mbar_init(&bar_mma[1], 1);
+    fence_barrier_init();
+    s_abort = 0;
+    tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
+    tma_prefetch_desc(&p.tmdY); tma_prefetch_desc(&p.tmZ);
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, B_TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  auto issue_loads = [&](int c, int it) {   // one thread
+    uint8_t* st = smem + (it & 1) * B_STAGE;
+    uint64_t* bar = &bar_tma[it & 1];
+    mbar_expect_tx(bar, B_STAGE);
+    tma_load_3d(st, &p.tmU, bar, 0, c * L, bh);
+    tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bh);
+    tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bh);
+    tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bh);
+    tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bh);
+    tma_load_3d(st + 5 * TILE, &p.tmdY, bar, 0, c * L, bh);
+    tma_load_3d(st + 6 * TILE, &p.tmZ, bar, 0, c * 64, bh);
+    tma_load_3d(st + 7 * TILE, &p.tmZ, bar, 64, c * 64, bh);
+  };
+  if (tid == 0) issue_loads(nC - 1, 0);
+
+  auto block_sum2 = [&](float a, float b, float& oa, float& ob) {
+    a = warp_sum(a); b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) { s_red[2 * warp] = a; s_red[2 * warp + 1] = b; }
+    __syncthreads();
+    oa = s_red[0] + s_red[2] + s_red[4] + s_red[6];
+    ob = s_red[1] + s_red[3] + s_red[5] + s_red[7];
+  };
+
+  // adjoint state, conjugated pairs (da, db):  dz = da - i db
+  float dz[64];
+  {
+    float ar = 0.f, ai = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float re = 0.f, im = 0.f;
+      if (p.dfinal) {
+        const size_t o = ((size_t)bh * 64 + row) * 128 + 64 * hf + 2 * j;
+        const float2 g = *reinterpret_cast<const float2*>(p.dfinal + o);
+        const float2 z = *reinterpret_cast<const float2*>(p.zfinal + o);
+        re = g.x; im = g.y;
+        ar += re * z.x + im * z.y;   // d_final * conj(z_final)
+        ai += im * z.x - re * z.y;
+      }
+      dz[2 * j] = re; dz[2 * j + 1] = -im;
+    }
+    float sr, si;
+    block_sum2(ar, ai, sr, si);
+    if (tid == 0) p.anchor[(size_t)bh * nC + nC - 1] = make_float2(sr, si);
+  }
+
+  constexpr uint32_t ID_KK32 = make_idesc(64, 32, PK::fmt, 0, 0);
+  constexpr uint32_t ID_KM64 = make_idesc(64, 64, PK::fmt, 0, 1);
+  constexpr uint32_t ID_MM64 = make_idesc(64, 64, PK::fmt, 1, 1);
+  constexpr uint32_t ID_MM32 = make_idesc(64, 32, PK::fmt, 1, 1);
+  const uint32_t aQ = smem_u32(smem + B_OFF_Q), aKP = smem_u32(smem + B_OFF_KP),
+                 aDYO = smem_u32(smem + B_OFF_DYO), aPD = smem_u32(smem + B_OFF_PD),
+                 aDP = smem_u32(smem + B_OFF_DP), aDW = smem_u32(smem + B_OFF_DW);
+  bool ok = true;
+
+  for (int it = 0; it < nC && ok; ++it) {
+    const int c = nC - 1 - it, t0 = c * L;
+    uint8_t* st = smem + (it & 1) * B_STAGE;
+    uint8_t *tU = st, *tB = st + TILE, *tC = st + 3 * TILE, *tDY = st + 5 * TILE, *tZ = st + 6 * TILE;
+    if (tid == 0 && it + 1 < nC) issue_loads(c - 1, it + 1);
+    if (warp == 0) chunk_scalars(sc, Mb, Kb, t0, T, lane);
+    __syncthreads();
+    // ---- dWv tile: dz rotated by the unit phase of Pi_end:  (a,b) -> (ur a - ui b, ui a + ur b) ----
+    {
+      const float ur = sc[10 * 64 + 2], ui = sc[10 * 64 + 3];
+      if (tid < 64) sc[11 * 64 + tid] = __expf(fminf(sc[63] - sc[tid], 0.f));
+      uint8_t* dw = smem + B_OFF_DW + hf * TILE;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = dz[8 * ch + 2 * e], bq = dz[8 * ch + 2 * e + 1];
+          const float na = ur * a - ui * bq, nb = ui * a + ur * bq;
+          dz[8 * ch + 2 * e] = na; dz[8 * ch + 2 * e + 1] = nb;
+          w[e] = PK::pack(na, nb);
+        }
+        *reinterpret_cast<uint4*>(dw + sw128(row, ch)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    ok = mbar_wait(&bar_tma[it & 1], (it >> 1) & 1);
+    if (!ok) { report_timeout(11); s_abort = 1; }
+    __syncthreads();
+    if (s_abort) { ok = false; break; }
+
+    // ---- pass 1 over dY, U: sigma_t = <dy_t, u_t>, dYoff = e^{l_t} dY -------------------------------
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int item = tid + 128 * k, r = item >> 3, ch = item & 7;
+      const uint32_t off = sw128(r, ch);
+      const uint4 dv = *reinterpret_cast<const uint4*>(tDY + off);
+      const uint4 uv = *reinterpret_cast<const uint4*>(tU + off);
+      const uint32_t dw_[4] = {dv.x, dv.y, dv.z, dv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      const float et = sc[1 * 64 + r];
+      uint32_t o[4];
+      float sg = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 d2 = PK::unpack(dw_[e]), u2 = PK::unpack(uw[e]);
+        sg += d2.x * u2.x + d2.y * u2.y;
+        o[e] = PK::pack(et * d2.x, et * d2.y);
+      }
+      *reinterpret_cast<uint4*>(smem + B_OFF_DYO + off) = make_uint4(o[0], o[1], o[2], o[3]);
+      sg += __shfl_xor_sync(0xffffffffu, sg, 4);
+      sg += __shfl_xor_sync(0xffffffffu, sg, 2);
+      sg += __shfl_xor_sync(0xffffffffu, sg, 1);
+      if (ch == 0) sc[12 * 64 + r] = sg;
+    }
+    // ---- pass 2 over B, C: Q, K', diagonal pieces ------------------------------------------------------
+    {
+      const uint32_t half = rcol >> 3, ch = rcol & 7;
+#pragma unroll 2
+      for (int k = 0; k < 8; ++k) {
+        const int r = rrow0 + 8 * k;
+        const uint32_t off = half * TILE + sw128(r, ch);
+        const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
+        const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
+        const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
+        const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
+        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t qo[4], ko[4];
+        float dg = 0.f, cbr = 0.f, cbi = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
+          qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
+          ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
+          const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
+          dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
+          cbr += cc.x * bb.x + cc.y * bb.y;                                       // c conj(b)
+          cbi += cc.y * bb.x - cc.x * bb.y;
+        }
+        *reinterpret_cast<uint4*>(smem + B_OFF_Q + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+        *reinterpret_cast<uint4*>(smem + B_OFF_KP + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+          dg += __shfl_xor_sync(0xffffffffu, dg, o);
+          cbr += __shfl_xor_sync(0xffffffffu, cbr, o);
+          cbi += __shfl_xor_sync(0xffffffffu, cbi, o);
+        }
+        if (rcol == 0) { sc[13 * 64 + r] = dg; sc[14 * 64 + r] = cbr; sc[15 * 64 + r] = cbi; }
+      }
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    // ---- MMA group 1: P~ = Q K'^T, dS = dY U^T ----------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t aU = smem_u32(tU), aDY = smem_u32(tDY);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t dP_ = tmem + ((16u * q) << 16), dS_ = dP_ + 32;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+          umma(dP_, make_desc(aQ + ko, 16, 1024), make_desc(aKP + 4096 * q + ko, 16, 1024), ID_KK32, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma(dS_, make_desc(aDY + 32 * k, 16, 1024), make_desc(aU + 4096 * q + 32 * k, 16, 1024), ID_KK32,
+               k > 0);
+      }
+      umma_commit(&bar_mma[0]);
+    }
+    ok = mbar_wait(&bar_mma[0], it & 1);
+    if (!ok) { report_timeout(12); s_abort = 1; }
+    tc_fence_after_sync();
+
+    // ---- epilogue 1: decayed, strictly causal Pdec and dP as 16-bit tiles -------------------------------
+    {
+      uint32_t pr[32], ds[32];
+      tmem_ld32(tmem + lane_base + 0, pr);
+      tmem_ld32(tmem + lane_base + 32, ds);
+      tmem_ld_wait();
+      const float lt = sc[row];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t wp[4], wd[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float vp[2], vd[2];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int j = 8 * ch + 2 * e + q, s = 32 * hf + j;
+            const float dec = s < row ? __expf(fminf(lt - sc[s], 0.f)) : 0.f;
+            vp[q] = dec * __uint_as_float(pr[j]);
+            vd[q] = dec * __uint_as_float(ds[j]);
+          }
+          wp[e] = PK::pack(vp[0], vp[1]);
+          wd[e] = PK::pack(vd[0], vd[1]);
+        }
+        const uint32_t off = sw128(row, 4 * hf + ch);
+        *reinterpret_cast<uint4*>(smem + B_OFF_PD + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+        *reinterpret_cast<uint4*>(smem + B_OFF_DP + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (s_abort) { ok = false; break; }
+
+    // ---- MMA group 2 ----------------------------------------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t aU = smem_u32(tU), aDY = smem_u32(tDY), aZ = smem_u32(tZ);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t mk = 2048 * k, kk = 32 * k;
+          // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
+          umma(lb + 64, make_desc(aDP + kk, 16, 1024), make_desc(aKP + TILE * q + mk, 8192, 1024), ID_KM64, k > 0);
+          // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
+          umma(lb + 128, make_desc(aDY + kk, 16, 1024), make_desc(aZ + TILE * q + mk, 8192, 1024), ID_KM64, k > 0);
+          // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
+          umma(lb + 192, make_desc(aDP + mk, 8192, 1024), make_desc(aQ + TILE * q + mk, 8192, 1024), ID_MM64, k > 0);
+          // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
+          umma(lb + 256, make_desc(aU + kk, 16, 1024), make_desc(aDW + TILE * q + mk, 8192, 1024), ID_KM64, k > 0);
+          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
+          umma(lb + 320, make_desc(aPD + mk, 8192, 1024), make_desc(aDY + 64 * q + mk, 8192, 1024), ID_MM32, k > 0);
+          // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
+          umma(lb + 384, make_desc(aDYO + mk, 8192, 1024), make_desc(aQ + TILE * q + mk, 8192, 1024), ID_MM64, k > 0);
+        }
+        // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p (N = 32 half)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+          umma(lb + 352, make_desc(aKP + ko, 16, 1024), make_desc(aDW + 4096 * q + ko, 16, 1024), ID_KK32, k > 0);
+        }
+      }
+      umma_commit(&bar_mma[1]);
+    }
+    ok = mbar_wait(&bar_mma[1], it & 1);
+    if (!ok) { report_timeout(13); s_abort = 1; }
+    tc_fence_after_sync();
+
+    const bool tok_valid = t0 + row < T;
+    const float sig = sc[12 * 64 + row];
+    // ---- epilogue 2: dQ -> dC, <q,dq> ------------------------------------------------------------------
+    {
+      const float et = sc[1 * 64 + row], phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
+      const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
+      float ar = 0.f, ai = 0.f;
+      TIn* dst = reinterpret_cast<TIn*>(p.dC) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t qa[32], qb[32];
+        tmem_ld32(tmem + lane_base + 64 + 32 * part, qa);
+        tmem_ld32(tmem + lane_base + 128 + 32 * part, qb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t off = hf * TILE + sw128(row, 4 * part + ch);
+          const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
+          const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+          const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = 8 * ch + 2 * e;
+            const float dqr = __uint_as_float(qa[j]) + et * __uint_as_float(qb[j]);
+            const float dqi = __uint_as_float(qa[j + 1]) + et * __uint_as_float(qb[j + 1]);
+            const float2 q = PK::unpack(qw[e]), bb = PK::unpack(bw[e]);
+            ar += q.x * dqr + q.y * dqi;          // conj(q) dq
+            ai += q.x * dqi - q.y * dqr;
+            // dc = conj(dq) phi + sigma kc b
+            const float dcr = dqr * phr + dqi * phi + (skr * bb.x - ski * bb.y);
+            const float dci = dqr * phi - dqi * phr + (skr * bb.y + ski * bb.x);
+            o[e] = PK::pack(dcr, dci);
+          }
+          if (tok_valid) *reinterpret_cast<uint4*>(dst + 32 * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      sc[(16 + hf) * 64 + row] = ar;
+      sc[(18 + hf) * 64 + row] = ai;
+    }
+    // ---- epilogue 3: dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
+    {
+      const float ee = sc[11 * 64 + row], wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
+      const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];
+      float rr = 0.f, ri = 0.f;
+      TIn* dst = reinterpret_cast<TIn*>(p.dB) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t xa[32], xb[32];
+        tmem_ld32(tmem + lane_base + 192 + 32 * part, xa);
+        tmem_ld32(tmem + lane_base + 256 + 32 * part, xb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t off = hf * TILE + sw128(row, 4 * part + ch);
+          const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
+          const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+          const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = 8 * ch + 2 * e;
+            const float ga = __uint_as_float(xa[j]) + ee * __uint_as_float(xb[j]);
+            const float gb = __uint_as_float(xa[j + 1]) + ee * __uint_as_float(xb[j + 1]);
+            const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
+            // dX = ga - i gb ; R += conj(b) dX
+            rr += bb.x * ga - bb.y * gb;
+            ri += -bb.x * gb - bb.y * ga;
+            // db = conj(w) dX + sigma conj(kc) c
+            const float dbr = wr * ga - wi * gb + (skr * cc.x + ski * cc.y);
+            const float dbi = -wr * gb - wi * ga + (skr * cc.y - ski * cc.x);
+            o[e] = PK::pack(dbr, dbi);
+          }
+          if (tok_valid) *reinterpret_cast<uint4*>(dst + 32 * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      sc[(20 + hf) * 64 + row] = rr;
+      sc[(22 + hf) * 64 + row] = ri;
+    }
+    // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
+    {
+      uint32_t ua[32], ub[32];
+      tmem_ld32(tmem + lane_base + 320, ua);
+      tmem_ld32(tmem + lane_base + 352, ub);
+      tmem_ld_wait();
+      const float ee = sc[11 * 64 + row], dgv = sc[13 * 64 + row];
+      TIn* dst = reinterpret_cast<TIn*>(p.dU) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        const uint4 dv = *reinterpret_cast<const uint4*>(tDY + sw128(row, 4 * hf + ch));
+        const uint32_t dw_[4] = {dv.x, dv.y, dv.z, dv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 8 * ch + 2 * e;
+          const float2 d2 = PK::unpack(dw_[e]);
+          o[e] = PK::pack(__uint_as_float(ua[j]) + ee * __uint_as_float(ub[j]) + dgv * d2.x,
+                          __uint_as_float(ua[j + 1]) + ee * __uint_as_float(ub[j + 1]) + dgv * d2.y);
+        }
+        if (tok_valid) *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    // ---- epilogue 5: dz <- e^{l_end} dWv + dZ ; anchor of the boundary below ----------------------------------
+    {
+      const float em = sc[1 * 64 + 63];
+      float ar = 0.f, ai = 0.f;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t zi[32];
+        tmem_ld32(tmem + lane_base + 384 + 32 * part, zi);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint4 zv4 = *reinterpret_cast<const uint4*>(tZ + hf * TILE + sw128(row, 4 * part + ch));
+          const uint32_t zw[4] = {zv4.x, zv4.y, zv4.z, zv4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = 8 * ch + 2 * e, jj = 32 * part + j;
+            const float da = em * dz[jj] + __uint_as_float(zi[j]);
+            const float db = em * dz[jj + 1] + __uint_as_float(zi[j + 1]);
+            dz[jj] = da; dz[jj + 1] = db;
+            const float2 z = PK::unpack(zw[e]);   // (a, b): z = a - i b ; dz = da - i db
+            ar += da * z.x + db * z.y;            // dz conj(z)
+            ai += da * z.y - db * z.x;
+          }
+        }
+      }
+      float sr, si;
+      block_sum2(ar, ai, sr, si);   // contains two barriers: also orders the table writes above
+      if (tid == 0 && c > 0) p.anchor[(size_t)bh * nC + c - 1] = make_float2(sr, si);
+    }
+    // ---- per-token scalars of this chunk ---------------------------------------------------------------------
+    if (tid < 64 && t0 + tid < T) {
+      const int t = tid;
+      const float Ar = sc[16 * 64 + t] + sc[17 * 64 + t], Ai = sc[18 * 64 + t] + sc[19 * 64 + t];
+      const float Rr = sc[20 * 64 + t] + sc[21 * 64 + t], Ri = sc[22 * 64 + t] + sc[23 * 64 + t];
+      const float phr = sc[2 * 64 + t], phi = sc[3 * 64 + t], wr = sc[4 * 64 + t], wi = sc[5 * 64 + t];
+      const size_t o = (size_t)bh * T + t0 + t;
+      p.dg[o] = make_float2(phr * Rr - phi * Ri, phr * Ri + phi * Rr);                 // phi R
+      p.sterm[o] = make_float2(Ar - (wr * Rr + wi * Ri), Ai - (wr * Ri - wi * Rr));   // A - conj(w) R
+      const float sg = sc[12 * 64 + t];
+      p.dkcd[o] = make_float2(sg * sc[14 * 64 + t], sg * sc[15 * 64 + t]);
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (s_abort) { ok = false; break; }
+  }
+
+  if (ok && p.dinit) {
+    float* dst = p.dinit + ((size_t)bh * 64 + row) * 128 + 64 * hf;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      *reinterpret_cast<float4*>(dst + 4 * j) =
+          make_float4(dz[4 * j], -dz[4 * j + 1], dz[4 * j + 2], -dz[4 * j + 3]);
+  }
+  if (!ok && tid == 0) {
+    for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, B_TMEM_COLS);
+}
+
+// dM and dK from the per-token scalars.  One warp per chunk (two tokens per lane).
+__global__ void __launch_bounds__(128) scan_tc_bwd_finish_kernel(const float* __restrict__ M,
+                                                                 const float* __restrict__ K,
+                                                                 const float2* __restrict__ dg,
+                                                                 const float2* __restrict__ sterm,
+                                                                 const float2* __restrict__ dkcd,
+                                                                 const float2* __restrict__ anchor,
+                                                                 float* __restrict__ dM,
+                                                                 float* __restrict__ dK, int T, int nC) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t bh = blockIdx.x;
+  for (int c = warp; c < nC; c += 4) {
+    const int tA = c * 64 + 2 * lane, tB = tA + 1;
+    float2 sA = make_float2(0.f, 0.f), sB = sA;
+    if (tA < T) sA = sterm[bh * T + tA];
+    if (tB < T) sB = sterm[bh * T + tB];
+    // inclusive suffix sums over the chunk
+    float xr = sA.x + sB.x, xi = sA.y + sB.y;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float yr = __shfl_down_sync(0xffffffffu, xr, o), yi = __shfl_down_sync(0xffffffffu, xi, o);
+      if (lane + o < 32) { xr += yr; xi += yi; }
+    }
+    const float2 an = anchor[bh * nC + c];
+    const float SAr = an.x + xr, SAi = an.y + xi;            // S at token tA
+    const float SBr = SAr - sA.x, SBi = SAi - sA.y;          // S at token tB
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int t = q ? tB : tA;
+      if (t >= T) continue;
+      const float Sr = q ? SBr : SAr, Si = q ? SBi : SAi;
+      const float mr = M[(bh * T + t) * 2], mi = M[(bh * T + t) * 2 + 1];
+      const float den = mr * mr + mi * mi;
+      const float4 k4 = *reinterpret_cast<const float4*>(K + (bh * T + t) * 4);
+      float2 gp = make_float2(0.f, 0.f);
+      if (t > 0) gp = dg[bh * T + t - 1];
+      const float2 gc = dg[bh * T + t], kd = dkcd[bh * T + t];
+      // x / conj(m) = x m / |m|^2
+      const float dmr = (Sr * mr - Si * mi) / den, dmi = (Sr * mi + Si * mr) / den;
+      const float dkpr = (gp.x * mr - gp.y * mi) / den, dkpi = (gp.x * mi + gp.y * mr) / den;
+      // q = kp / m ; dm -= conj(q) dkp
+      const float qr = (k4.x * mr + k4.y * mi) / den, qi = (k4.y * mr - k4.x * mi) / den;
+      float2* dMo = reinterpret_cast<float2*>(dM) + bh * T + t;
+      *dMo = make_float2(dmr - (qr * dkpr + qi * dkpi), dmi - (qr * dkpi - qi * dkpr));
+      *reinterpret_cast<float4*>(dK + (bh * T + t) * 4) = make_float4(dkpr, dkpi, gc.x + kd.x, gc.y + kd.y);
+    }
+  }
+}

@@ -246,3 +246,58 @@ def test_auto_path_prefers_tensor_cores_and_falls_back_for_float32():
         _run(case, 64, "tc")
     Y = _run(case, 64, "auto")[0]
     assert rel(Y, _oracle_fwd(case)[0]) <= 1e-5
+
+
+TC_BWD_SHAPES = [
+    (1, 1, 64, False, False),
+    (1, 2, 1, True, True),
+    (2, 2, 63, False, True),
+    (1, 3, 65, True, True),
+    (2, 4, 200, True, False),
+    (1, 2, 333, False, False),
+    (1, 2, 1024, True, True),
+]
+
+
+@pytest.mark.parametrize("shape", TC_BWD_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_backward_tensor_core_path(shape, dtype):
+    from slinoss_b200 import _C
+    b, h, T, init, with_dfinal = shape
+    case = make_scan_case(b, h, T, 64, 64, dtype=dtype, seed=11 * T + h, with_init=init)
+    c = case.to(DEV)
+    names = ["U", "M", "K", "B", "C"] + (["initial_states"] if init else [])
+    leaves = {k: getattr(c, k).clone().requires_grad_(True) for k in names}
+    out = v2x2ssd(leaves["U"], leaves["M"], leaves["K"], leaves["B"], leaves["C"], chunk_size=64,
+                  initial_states=leaves.get("initial_states"), path="tc")
+    gen = torch.Generator().manual_seed(5)
+    d_final = torch.randn(out[1].shape, generator=gen).to(dtype) if with_dfinal else None
+    outs, cots = [out[0]], [c.dY]
+    if with_dfinal:
+        outs.append(out[1]); cots.append(d_final.to(DEV))
+    grads = torch.autograd.grad(outs, list(leaves.values()), cots)
+    assert _C.device_status() == 0
+    want = scan_np.v2x2ssd_bwd(*[n64(t) for t in case.tensors()], n64(case.dY),
+                               d_final_state=n64(d_final), initial_states=n64(case.initial_states))
+    for name, gr in zip(names, grads):
+        assert torch.isfinite(gr).all(), name
+        assert rel(gr, want[name]) <= 2e-2, (name, rel(gr, want[name]))
+
+
+def test_backward_tensor_core_agrees_with_exact_path_at_strong_decay():
+    import math
+    gen = torch.Generator().manual_seed(1)
+    b, h, T = 1, 2, 300
+    radius = 0.6 + 0.35 * torch.rand(b, h, T, generator=gen)
+    angle = (2 * torch.rand(b, h, T, generator=gen) - 1) * math.pi
+    M = torch.stack((radius * torch.cos(angle), radius * torch.sin(angle)), -1).to(DEV)
+    K = (0.1 * torch.randn(b, h, T, 2, 2, generator=gen)).to(DEV)
+    mk = lambda *s: torch.randn(*s, generator=gen).to(torch.bfloat16).to(DEV)
+    U, B, C, dY = mk(b, h, T, 64), 0.1 * mk(b, h, T, 128), 0.1 * mk(b, h, T, 128), mk(b, h, T, 64)
+    res = {}
+    for path in ("tc", "simt"):
+        lv = [x.clone().requires_grad_(True) for x in (U, M, K, B, C)]
+        Y = v2x2ssd_cute(*lv, chunk_size=64, path=path)
+        res[path] = torch.autograd.grad(Y, lv, dY)
+    for name, a, e in zip("UMKBC", res["tc"], res["simt"]):
+        assert rel(a, e) <= 2e-2, (name, rel(a, e))
