@@ -169,6 +169,7 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="T=512 variant for profiler captures")
+    ap.add_argument("--tc-warps", type=int, default=0, help="development knob: warps per TMEM quadrant")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -192,6 +193,8 @@ def main():
     from slinoss_b200.ops.v2x2ssd import v2x2ssd_cute
     from slinoss_b200.synthetic import make_scan_case
 
+    if args.tc_warps:
+        _C.lib().sl_tune_tc_warps(args.tc_warps)
     c = CFG
     case_h = make_scan_case(c["batch"], c["heads"], c["T"], c["P"], c["N"], dtype=torch.bfloat16,
                             seed=rank)

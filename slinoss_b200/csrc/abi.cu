@@ -23,6 +23,7 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
                 int dy_dtype, void* ws, size_t ws_bytes, cudaStream_t st);
 
 int scan_tc_device_status();
+void scan_tc_set_warps(int nw);
 
 namespace {
 
@@ -52,6 +53,10 @@ extern "C" int sl_version(void) { return 100; }
 extern "C" unsigned long long sl_kernel_launches(void) {
   return sl::g_launches.load(std::memory_order_relaxed);
 }
+
+// Development knob (not part of the documented ABI): warps per TMEM lane quadrant of the
+// tensor-core scan kernels.
+extern "C" SL_API void sl_tune_tc_warps(int nw) { sl::scan_tc_set_warps(nw); }
 
 extern "C" int sl_device_status(void) { return sl::scan_tc_device_status(); }
 

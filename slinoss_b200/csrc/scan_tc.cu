@@ -46,10 +46,13 @@ constexpr uint32_t OFF_S = OFF_KPP + 2 * TILE;
 constexpr uint32_t OFF_ZV = OFF_S + TILE; // Zv (2 tiles)
 constexpr uint32_t OFF_SCAL = OFF_ZV + 2 * TILE;
 constexpr int NSCAL = 12;                 // per-token float arrays
-constexpr uint32_t SMEM_BYTES = OFF_SCAL + NSCAL * 64 * 4 + 64 + 1024;
+constexpr uint32_t SMEM_BYTES = OFF_SCAL + 2 * NSCAL * 64 * 4 + 64 + 1024;
 constexpr uint32_t TMEM_COLS = 256;       // S 0..31 | Yoff 32..63 | Ydiag 64..95 | Inc 128..191
 
-__device__ int g_tc_status = 0;           // first device-side error (bounded wait expired)
+__device__ int g_tc_status = 0;
+#ifdef SL_TC_TIMING
+__device__ long long g_tc_timing[16];
+#endif           // first device-side error (bounded wait expired)
 
 struct alignas(64) TcFwdParams {
   CUtensorMap tmU, tmB, tmC;
@@ -163,315 +166,7 @@ __device__ void chunk_scalars(float* sc, const float* __restrict__ Mb, const flo
   }
 }
 
-// STATES_ONLY: the state pre-sweep of the backward pass (no C, no scores, no Y).
-template <typename TIn, typename TY, bool STATES_ONLY>
-__global__ void __launch_bounds__(128, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ uint64_t bar_tma[2], bar_mma[2];
-  __shared__ uint32_t tmem_slot;
-  __shared__ int s_abort;
-  float* sc = reinterpret_cast<float*>(smem + OFF_SCAL);
-  float* s_diag = sc + 11 * 64;
-  using PK = Pack2<TIn>;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row = 16 * warp + (lane & 15), hf = lane >> 4;   // epilogue identity
-  const int rcol = tid & 15, rrow0 = tid >> 4;               // rotation identity
-  const int bh = blockIdx.x, b = bh / p.heads, h = bh % p.heads;
-  const int bg = b * p.groups + h / (p.heads / p.groups);
-  const int T = p.T;
-  const float* Mb = p.M + (size_t)bh * T * 2;
-  const float* Kb = p.K + (size_t)bh * T * 4;
-
-  if (tid == 0) {
-    mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
-    mbar_init(&bar_mma[0], 1); mbar_init(&bar_mma[1], 1);
-    fence_barrier_init();
-    s_abort = 0;
-    tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
-  }
-  if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_slot;
-
-  auto issue_loads = [&](int c) {   // one thread
-    uint8_t* st = smem + (c & 1) * STAGE;
-    uint64_t* bar = &bar_tma[c & 1];
-    mbar_expect_tx(bar, STATES_ONLY ? 3 * TILE : STAGE);
-    tma_load_3d(st, &p.tmU, bar, 0, c * L, bh);
-    tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bg);
-    tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bg);
-    if (!STATES_ONLY) {
-      tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bg);
-      tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bg);
-    }
-  };
-  if (tid == 0) issue_loads(0);
-
-  // ---- carried state in conjugated form: zv[2j], zv[2j+1] = (re, -im) of column pair j ------
-  float zv[64];
-  {
-    const TIn* Bp = reinterpret_cast<const TIn*>(p.Bprev);
-    const TIn* Up = reinterpret_cast<const TIn*>(p.Uprev);
-    float cr = 0.f, ci = 0.f, up = 0.f;
-    if (Bp) {  // pending prev-tap of the token before the sequence: u_prev (x) (kp_0 / m_0) b_prev
-      const float mr = Mb[0], mi = Mb[1], kr = Kb[0], ki = Kb[1];
-      const float den = mr * mr + mi * mi;
-      cr = (kr * mr + ki * mi) / den; ci = (ki * mr - kr * mi) / den;
-      up = to_f32(Up[(size_t)bh * 64 + row]);
-    }
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int d = 64 * hf + 2 * j;
-      float re = 0.f, im = 0.f;
-      if (p.z0) {
-        const float2 z = *reinterpret_cast<const float2*>(p.z0 + ((size_t)bh * 64 + row) * 128 + d);
-        re = z.x; im = z.y;
-      }
-      if (Bp) {
-        const float br = to_f32(Bp[(size_t)bg * 128 + d]), bi = to_f32(Bp[(size_t)bg * 128 + d + 1]);
-        re += up * (cr * br - ci * bi);
-        im += up * (cr * bi + ci * br);
-      }
-      zv[2 * j] = re; zv[2 * j + 1] = -im;
-    }
-  }
-  auto store_zv_tile = [&]() {   // bf16 copy of the state: rows p, K-major along d
-    uint8_t* zt = smem + OFF_ZV + hf * TILE;
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      uint4 v;
-      v.x = PK::pack(zv[8 * ch + 0], zv[8 * ch + 1]); v.y = PK::pack(zv[8 * ch + 2], zv[8 * ch + 3]);
-      v.z = PK::pack(zv[8 * ch + 4], zv[8 * ch + 5]); v.w = PK::pack(zv[8 * ch + 6], zv[8 * ch + 7]);
-      *reinterpret_cast<uint4*>(zt + sw128(row, ch)) = v;
-    }
-  };
-  auto store_chunk_state = [&](int c) {   // conjugated form, 16-bit, row-major [p][128]
-    if (!p.states16) return;
-    TIn* dst = reinterpret_cast<TIn*>(p.states16) + (((size_t)bh * p.nchunks + c) * 64 + row) * 128 + 64 * hf;
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      uint4 v;
-      v.x = PK::pack(zv[8 * ch + 0], zv[8 * ch + 1]); v.y = PK::pack(zv[8 * ch + 2], zv[8 * ch + 3]);
-      v.z = PK::pack(zv[8 * ch + 4], zv[8 * ch + 5]); v.w = PK::pack(zv[8 * ch + 6], zv[8 * ch + 7]);
-      *reinterpret_cast<uint4*>(dst + 8 * ch) = v;
-    }
-  };
-  store_zv_tile();
-
-  constexpr uint32_t ID_S = make_idesc(64, 32, PK::fmt, 0, 0);     // K-major x K-major
-  constexpr uint32_t ID_Y = make_idesc(64, 32, PK::fmt, 0, 1);     // K-major x MN-major
-  constexpr uint32_t ID_Z = make_idesc(64, 64, PK::fmt, 1, 1);     // MN-major x MN-major
-  const uint32_t aKPP = smem_u32(smem + OFF_KPP), aS = smem_u32(smem + OFF_S),
-                 aZV = smem_u32(smem + OFF_ZV);
-  bool ok = true;
-
-  for (int c = 0; c < p.nchunks && ok; ++c) {
-    const int t0 = c * L;
-    uint8_t* st = smem + (c & 1) * STAGE;
-    if (tid == 0 && c + 1 < p.nchunks) issue_loads(c + 1);
-    if (warp == 0) chunk_scalars(sc, Mb, Kb, t0, T, lane);
-    store_chunk_state(c);
-    ok = mbar_wait(&bar_tma[c & 1], (c >> 1) & 1);
-    if (!ok) { report_timeout(1); s_abort = 1; }
-    __syncthreads();
-    if (s_abort) { ok = false; break; }
-
-    // ---- rotation: C -> Q, B -> K' (both in place), K'' ; diagonal scores --------------------
-    {
-      const uint32_t half = rcol >> 3, ch = rcol & 7;
-      uint8_t* tB = st + TILE + half * TILE;
-      uint8_t* tC = st + 3 * TILE + half * TILE;
-      uint8_t* tK = smem + OFF_KPP + half * TILE;
-#pragma unroll 2
-      for (int k = 0; k < 8; ++k) {
-        const int r = rrow0 + 8 * k;
-        const uint32_t off = sw128(r, ch);
-        const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
-        const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
-        const float vr = sc[6 * 64 + r], vi = sc[7 * 64 + r];
-        const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
-        uint4 cv = make_uint4(0u, 0u, 0u, 0u);
-        if (!STATES_ONLY) cv = *reinterpret_cast<const uint4*>(tC + off);
-        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
-        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-        uint32_t qo[4], ko[4], vo[4];
-        float dg = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
-          qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
-          ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
-          vo[e] = PK::pack(vr * bb.x - vi * bb.y, -(vr * bb.y + vi * bb.x));      // conj(v b)
-          const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
-          dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
-        }
-        *reinterpret_cast<uint4*>(tK + off) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
-        if (!STATES_ONLY) {
-          *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
-          *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
-          if (rcol == 0) s_diag[r] = dg;
-        }
-      }
-    }
-    fence_async_smem();
-    __syncthreads();
-
-    if (!STATES_ONLY) {
-    // ---- MMA group 1: scores and off-term ------------------------------------------------------
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t aB = smem_u32(st + TILE), aC = smem_u32(st + 3 * TILE);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const uint32_t dS = tmem + ((16u * q) << 16), dO = dS + 32;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          const uint64_t da = make_desc(aC + ko, 16, 1024);
-          umma(dS, da, make_desc(aB + 4096 * q + ko, 16, 1024), ID_S, k > 0);
-          umma(dO, da, make_desc(aZV + 4096 * q + ko, 16, 1024), ID_S, k > 0);
-        }
-      }
-      umma_commit(&bar_mma[0]);
-    }
-    ok = mbar_wait(&bar_mma[0], c & 1);
-    if (!ok) { report_timeout(2); s_abort = 1; }
-    tc_fence_after_sync();
-
-    // ---- scores epilogue: decay, causal mask, diagonal -> 16-bit S tile ----------------------------
-    {
-      uint32_t r32[32];
-      tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 0, r32);
-      tmem_ld_wait();
-      const float lt = sc[row];
-      const float dgv = s_diag[row];
-      uint8_t* tS = smem + OFF_S;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float v2[2];
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int j = 8 * ch + 2 * e + q, s = 32 * hf + j;
-            float v = __uint_as_float(r32[j]) * __expf(fminf(lt - sc[s], 0.f));
-            v = s < row ? v : (s == row ? dgv : 0.f);
-            v2[q] = v;
-          }
-          w[e] = PK::pack(v2[0], v2[1]);
-        }
-        *reinterpret_cast<uint4*>(tS + sw128(row, 4 * hf + ch)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (s_abort) { ok = false; break; }
-    }  // !STATES_ONLY
-
-    // ---- MMA group 2: Y_diag = S U, Inc = U^T K'' ------------------------------------------------------
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t aU = smem_u32(st);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const uint32_t dY = tmem + ((16u * q) << 16) + 64, dZ = tmem + ((16u * q) << 16) + 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (!STATES_ONLY)
-            umma(dY, make_desc(aS + 32 * k, 16, 1024), make_desc(aU + 64 * q + 2048 * k, 8192, 1024), ID_Y,
-                 k > 0);
-          umma(dZ, make_desc(aU + 2048 * k, 8192, 1024), make_desc(aKPP + TILE * q + 2048 * k, 8192, 1024),
-               ID_Z, k > 0);
-        }
-      }
-      umma_commit(&bar_mma[1]);
-    }
-    ok = mbar_wait(&bar_mma[1], c & 1);
-    if (!ok) { report_timeout(3); s_abort = 1; }
-    tc_fence_after_sync();
-
-    // ---- output epilogue: y = Y_diag + exp(l_t) Y_off ---------------------------------------------------
-    if (!STATES_ONLY) {
-      uint32_t yd[32], yo[32];
-      tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 64, yd);
-      tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 32, yo);
-      tmem_ld_wait();
-      const float et = sc[1 * 64 + row];
-      if (t0 + row < T) {
-        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf;
-        if constexpr (sizeof(TY) == 2) {
-          using PY = Pack2<TY>;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 8 * v + 2 * e;
-              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
-                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
-            }
-            *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        } else {
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            float4 o;
-            o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
-            o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
-            o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
-            o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
-          }
-        }
-      }
-    }
-    // ---- state update: zv = conj(Pi_end) zv + Inc -------------------------------------------------------
-    {
-      const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t inc[32];
-        tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 128 + 32 * part, inc);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float a = zv[32 * part + 2 * j], bq = zv[32 * part + 2 * j + 1];
-          zv[32 * part + 2 * j] = pr * a + pi * bq + __uint_as_float(inc[2 * j]);
-          zv[32 * part + 2 * j + 1] = pr * bq - pi * a + __uint_as_float(inc[2 * j + 1]);
-        }
-      }
-      store_zv_tile();
-    }
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (s_abort) { ok = false; break; }
-  }
-
-  if (ok && p.zfinal) {
-    float* dst = p.zfinal + ((size_t)bh * 64 + row) * 128 + 64 * hf;
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-      *reinterpret_cast<float4*>(dst + 4 * j) =
-          make_float4(zv[4 * j], -zv[4 * j + 1], zv[4 * j + 2], -zv[4 * j + 3]);
-  }
-  // unwind: nothing of ours may still be in flight when shared memory / TMEM are released
-  if (!ok && tid == 0) {
-    for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);   // bounded; best effort drain
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
-}
-
+#include "scan_tc_fwd.cuh"
 #include "scan_tc_bwd.cuh"
 
 }  // namespace
@@ -505,14 +200,24 @@ size_t scan_tc_bwd_workspace(const ScanDims& d) {
   return std::max(scan_simt_bwd_workspace(d), tc_bwd_layout(d).total);
 }
 
-template <typename TIn, typename TY, bool STATES_ONLY>
-static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
-  auto k = scan_tc_fwd_kernel<TIn, TY, STATES_ONLY>;
+int g_tc_nw = 4;   // warps per TMEM lane quadrant (tuning knob: 1, 2 or 4)
+
+template <typename TIn, typename TY, bool STATES_ONLY, int NW>
+static int launch_tc_fwd_nw(const TcFwdParams& p, int grid, cudaStream_t st) {
+  auto k = scan_tc_fwd_kernel<TIn, TY, STATES_ONLY, NW>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess)
     return SL_ERR_LAUNCH_FAILED;
-  k<<<grid, 128, SMEM_BYTES, st>>>(p);
+  k<<<grid, 128 * NW + 32, SMEM_BYTES, st>>>(p);
   note_launches(1);
   return launch_status();
+}
+template <typename TIn, typename TY, bool STATES_ONLY>
+static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
+  switch (g_tc_nw) {
+    case 1: return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 1>(p, grid, st);
+    case 2: return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 2>(p, grid, st);
+    default: return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 4>(p, grid, st);
+  }
 }
 
 // Y == nullptr runs the state pre-sweep only (chunk-start states + final state).
@@ -548,6 +253,15 @@ int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, co
   return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, nullptr, d, io_dtype, y_dtype, st);
 }
 
+template <typename TIn, int NW>
+static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
+  auto k = scan_tc_bwd_kernel<TIn, NW>;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
+    return SL_ERR_LAUNCH_FAILED;
+  k<<<grid, 128 * NW + 32, B_SMEM_BYTES, st>>>(p);
+  return launch_status();
+}
+
 // Tensor-core backward: state pre-sweep, reverse sweep, scalar finish.  Cases it does not
 // cover (grouped B/C, carried B_prev/U_prev, dY of another dtype or absent) take the exact
 // float32 sweeps.
@@ -578,21 +292,29 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
   p.dkcd = reinterpret_cast<float2*>(w + lay.dkcd); p.anchor = reinterpret_cast<float2*>(w + lay.anchor);
   p.dinit = dinit; p.T = d.T; p.nchunks = nC;
+  int rc = SL_ERR_UNSUPPORTED;
   if (bf) {
-    auto k = scan_tc_bwd_kernel<__nv_bfloat16>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
-      return SL_ERR_LAUNCH_FAILED;
-    k<<<(int)BH, 128, B_SMEM_BYTES, st>>>(p);
+    rc = g_tc_nw == 1 ? launch_tc_bwd<__nv_bfloat16, 1>(p, (int)BH, st)
+       : g_tc_nw == 2 ? launch_tc_bwd<__nv_bfloat16, 2>(p, (int)BH, st)
+                      : launch_tc_bwd<__nv_bfloat16, 4>(p, (int)BH, st);
   } else {
-    auto k = scan_tc_bwd_kernel<__half>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
-      return SL_ERR_LAUNCH_FAILED;
-    k<<<(int)BH, 128, B_SMEM_BYTES, st>>>(p);
+    rc = g_tc_nw == 1 ? launch_tc_bwd<__half, 1>(p, (int)BH, st)
+       : g_tc_nw == 2 ? launch_tc_bwd<__half, 2>(p, (int)BH, st)
+                      : launch_tc_bwd<__half, 4>(p, (int)BH, st);
   }
+  if (rc != SL_OK) return rc;
   scan_tc_bwd_finish_kernel<<<(int)BH, 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
   note_launches(2);
   return launch_status();
 }
+
+#ifdef SL_TC_TIMING
+extern "C" __attribute__((visibility("default"))) void sl_dbg_timing(long long* out) {
+  cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(long long) * 16);
+}
+#endif
+
+void scan_tc_set_warps(int nw) { g_tc_nw = (nw == 1 || nw == 2) ? nw : 4; }
 
 int scan_tc_device_status() {
   int v = 0;

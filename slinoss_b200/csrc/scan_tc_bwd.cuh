@@ -24,7 +24,7 @@ constexpr uint32_t B_OFF_PD = B_OFF_DYO + TILE;        // Pdec (1)
 constexpr uint32_t B_OFF_DP = B_OFF_PD + TILE;         // dP (1)
 constexpr uint32_t B_OFF_DW = B_OFF_DP + TILE;         // dWv (2)
 constexpr uint32_t B_OFF_SCAL = B_OFF_DW + 2 * TILE;
-constexpr int B_NSCAL = 24;
+constexpr int B_NSCAL = 2 * 11 + 5 + 32;   // 2 x 11 look-ahead rows, 5 worker rows, 4 x 8 partial sums
 constexpr uint32_t B_SMEM_BYTES = B_OFF_SCAL + B_NSCAL * 64 * 4 + 1024;
 // TMEM columns: P~ 0 | dS 32 | dQa 64 | dQb 128 | dXa 192 | dXb 256 | dUa 320 | dUb 352 | dZ 384
 constexpr uint32_t B_TMEM_COLS = 512;
@@ -43,26 +43,37 @@ struct alignas(64) TcBwdParams {
 
 // Per-token table: rows 0..10 as written by chunk_scalars, then
 //  11 e^{l_end-l_t}   12 sigma_t = <dy_t,u_t>   13 diag_t   14,15 sum_n c conj(b)
-//  16,17 / 18,19  re / im of <q,dq> per column half     20,21 / 22,23  re / im of sum conj(b) dX
-template <typename TIn>
-__global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
+//  s_acc (after row 15): partial sums per (column group, half): re/im of <q,dq>, re/im of sum conj(b) dX
+// NW = warps per TMEM lane quadrant (same thread-to-data mapping as the forward kernel).
+template <typename TIn, int NW>
+__global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
+  constexpr int NT = 128 * NW;               // worker threads; one more warp prepares the scalars
+  constexpr int ZC = 64 / NW;                // columns per thread of a 64-wide accumulator half
+  constexpr int SC = 32 / NW;                // columns per thread of a 32-wide accumulator half
+  constexpr int PC = ZC > 32 ? 32 : ZC;      // columns handled per TMEM load in the wide epilogues
+  constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t bar_tma[2], bar_mma[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
-  __shared__ float s_red[8];
-  float* sc = reinterpret_cast<float*>(smem + B_OFF_SCAL);
+  __shared__ float s_red[8 * NW + 2];
+  float* sc_tab = reinterpret_cast<float*>(smem + B_OFF_SCAL);   // two tables of 11 rows (chunk parity)
+  float* sw = sc_tab + 22 * 64;  // rows written by the workers: e^{l_end-l_t}, sigma, diag, c conj(b)
+  float* s_acc = sw + 5 * 64;    // [4 quantities][8 = column group x half][64 rows]
   using PK = Pack2<TIn>;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row = 16 * warp + (lane & 15), hf = lane >> 4;
+  const bool worker = warp < 4 * NW;
+  const int quad = warp & 3, cg = worker ? (warp >> 2) : 0;
+  const int row = 16 * quad + (lane & 15), hf = lane >> 4;
   const int rcol = tid & 15, rrow0 = tid >> 4;
+  const int d0 = cg * ZC;                    // first column (inside the half) of this thread
   const int bh = blockIdx.x;
   const int T = p.T, nC = p.nchunks;
   const float* Mb = p.M + (size_t)bh * T * 2;
   const float* Kb = p.K + (size_t)bh * T * 4;
-  const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+  const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
 
   if (tid == 0) {
     mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
@@ -94,23 +105,24 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
   if (tid == 0) issue_loads(nC - 1, 0);
 
   auto block_sum2 = [&](float a, float b, float& oa, float& ob) {
-    a = warp_sum(a); b = warp_sum(b);
-    __syncthreads();
+    a = warp_sum(a); b = warp_sum(b);   // workers only
+    bar_sync(1, NT);
     if (lane == 0) { s_red[2 * warp] = a; s_red[2 * warp + 1] = b; }
-    __syncthreads();
-    oa = s_red[0] + s_red[2] + s_red[4] + s_red[6];
-    ob = s_red[1] + s_red[3] + s_red[5] + s_red[7];
+    bar_sync(1, NT);
+    oa = 0.f; ob = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4 * NW; ++k) { oa += s_red[2 * k]; ob += s_red[2 * k + 1]; }
   };
 
   // adjoint state, conjugated pairs (da, db):  dz = da - i db
-  float dz[64];
+  float dz[ZC];
   {
     float ar = 0.f, ai = 0.f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < ZC / 2; ++j) {
       float re = 0.f, im = 0.f;
-      if (p.dfinal) {
-        const size_t o = ((size_t)bh * 64 + row) * 128 + 64 * hf + 2 * j;
+      if (p.dfinal && worker) {
+        const size_t o = ((size_t)bh * 64 + row) * 128 + 64 * hf + d0 + 2 * j;
         const float2 g = *reinterpret_cast<const float2*>(p.dfinal + o);
         const float2 z = *reinterpret_cast<const float2*>(p.zfinal + o);
         re = g.x; im = g.y;
@@ -119,10 +131,14 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
       }
       dz[2 * j] = re; dz[2 * j + 1] = -im;
     }
-    float sr, si;
-    block_sum2(ar, ai, sr, si);
-    if (tid == 0) p.anchor[(size_t)bh * nC + nC - 1] = make_float2(sr, si);
+    if (worker) {
+      float sr, si;
+      block_sum2(ar, ai, sr, si);
+      if (tid == 0) p.anchor[(size_t)bh * nC + nC - 1] = make_float2(sr, si);
+    }
   }
+  if (!worker) chunk_scalars(sc_tab, Mb, Kb, (nC - 1) * L, T, lane);
+  __syncthreads();
 
   constexpr uint32_t ID_KK32 = make_idesc(64, 32, PK::fmt, 0, 0);
   constexpr uint32_t ID_KM64 = make_idesc(64, 64, PK::fmt, 0, 1);
@@ -132,21 +148,32 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
                  aDYO = smem_u32(smem + B_OFF_DYO), aPD = smem_u32(smem + B_OFF_PD),
                  aDP = smem_u32(smem + B_OFF_DP), aDW = smem_u32(smem + B_OFF_DW);
   bool ok = true;
+#ifdef SL_TC_TIMING
+#define SL_TOCK(i) if (bh == 0 && tid == 0 && it == 8) g_tc_timing[i] = clock64();
+#else
+#define SL_TOCK(i)
+#endif
 
   for (int it = 0; it < nC && ok; ++it) {
     const int c = nC - 1 - it, t0 = c * L;
+    SL_TOCK(0)
     uint8_t* st = smem + (it & 1) * B_STAGE;
     uint8_t *tU = st, *tB = st + TILE, *tC = st + 3 * TILE, *tDY = st + 5 * TILE, *tZ = st + 6 * TILE;
+    float* sc = sc_tab + (it & 1) * (11 * 64);
     if (tid == 0 && it + 1 < nC) issue_loads(c - 1, it + 1);
-    if (warp == 0) chunk_scalars(sc, Mb, Kb, t0, T, lane);
-    __syncthreads();
+    if (!worker) {
+      // scalars of the next (earlier) chunk; this warp meets the others only at the barrier
+      // that ends the iteration
+      if (it + 1 < nC) chunk_scalars(sc_tab + ((it + 1) & 1) * (11 * 64), Mb, Kb, t0 - L, T, lane);
+    } else {
+    bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
     // ---- dWv tile: dz rotated by the unit phase of Pi_end:  (a,b) -> (ur a - ui b, ui a + ur b) ----
     {
       const float ur = sc[10 * 64 + 2], ui = sc[10 * 64 + 3];
-      if (tid < 64) sc[11 * 64 + tid] = __expf(fminf(sc[63] - sc[tid], 0.f));
+      if (tid < 64) sw[0 * 64 + tid] = __expf(fminf(sc[63] - sc[tid], 0.f));
       uint8_t* dw = smem + B_OFF_DW + hf * TILE;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < ZC / 8; ++ch) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -155,18 +182,20 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
           dz[8 * ch + 2 * e] = na; dz[8 * ch + 2 * e + 1] = nb;
           w[e] = PK::pack(na, nb);
         }
-        *reinterpret_cast<uint4*>(dw + sw128(row, ch)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(dw + sw128(row, d0 / 8 + ch)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    ok = mbar_wait(&bar_tma[it & 1], (it >> 1) & 1);
-    if (!ok) { report_timeout(11); s_abort = 1; }
-    __syncthreads();
-    if (s_abort) { ok = false; break; }
+    if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(11); s_abort = 1; }
+    SL_TOCK(1)
+    bar_sync(1, NT);
+    live = s_abort == 0;
+    SL_TOCK(2)
 
     // ---- pass 1 over dY, U: sigma_t = <dy_t, u_t>, dYoff = e^{l_t} dY -------------------------------
+    if (live) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int item = tid + 128 * k, r = item >> 3, ch = item & 7;
+    for (int k = 0; k < 512 / NT; ++k) {
+      const int item = tid + NT * k, r = item >> 3, ch = item & 7;
       const uint32_t off = sw128(r, ch);
       const uint4 dv = *reinterpret_cast<const uint4*>(tDY + off);
       const uint4 uv = *reinterpret_cast<const uint4*>(tU + off);
@@ -184,14 +213,16 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
       sg += __shfl_xor_sync(0xffffffffu, sg, 4);
       sg += __shfl_xor_sync(0xffffffffu, sg, 2);
       sg += __shfl_xor_sync(0xffffffffu, sg, 1);
-      if (ch == 0) sc[12 * 64 + r] = sg;
+      if (ch == 0) sw[1 * 64 + r] = sg;
     }
+    }
+    SL_TOCK(3)
     // ---- pass 2 over B, C: Q, K', diagonal pieces ------------------------------------------------------
-    {
+    if (live) {
       const uint32_t half = rcol >> 3, ch = rcol & 7;
-#pragma unroll 2
-      for (int k = 0; k < 8; ++k) {
-        const int r = rrow0 + 8 * k;
+#pragma unroll
+      for (int k = 0; k < 64 / RSTEP; ++k) {
+        const int r = rrow0 + RSTEP * k;
         const uint32_t off = half * TILE + sw128(r, ch);
         const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
         const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
@@ -219,51 +250,62 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
           cbr += __shfl_xor_sync(0xffffffffu, cbr, o);
           cbi += __shfl_xor_sync(0xffffffffu, cbi, o);
         }
-        if (rcol == 0) { sc[13 * 64 + r] = dg; sc[14 * 64 + r] = cbr; sc[15 * 64 + r] = cbi; }
+        if (rcol == 0) { sw[2 * 64 + r] = dg; sw[3 * 64 + r] = cbr; sw[4 * 64 + r] = cbi; }
       }
     }
+    SL_TOCK(4)
     fence_async_smem();
-    __syncthreads();
+    bar_sync(1, NT);
+    SL_TOCK(5)
+
+    // K-major (kX) and MN-major (mX) base descriptors of every operand tile of this chunk
+    const uint64_t kQ = make_desc(aQ, 16, 1024), mQ = make_desc(aQ, 8192, 1024);
+    const uint64_t kKP = make_desc(aKP, 16, 1024), mKP = make_desc(aKP, 8192, 1024);
+    const uint64_t kU = make_desc(smem_u32(tU), 16, 1024);
+    const uint64_t kDY = make_desc(smem_u32(tDY), 16, 1024), mDY = make_desc(smem_u32(tDY), 8192, 1024);
+    const uint64_t mZ = make_desc(smem_u32(tZ), 8192, 1024);
+    const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
+    const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024);
+    const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
 
     // ---- MMA group 1: P~ = Q K'^T, dS = dY U^T ----------------------------------------------------------
-    if (tid == 0) {
+    if (tid == 0 && live) {
       tc_fence_after_sync();
-      const uint32_t aU = smem_u32(tU), aDY = smem_u32(tDY);
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const uint32_t dP_ = tmem + ((16u * q) << 16), dS_ = dP_ + 32;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          umma(dP_, make_desc(aQ + ko, 16, 1024), make_desc(aKP + 4096 * q + ko, 16, 1024), ID_KK32, k > 0);
+          umma(dP_, desc_adv(kQ, ko), desc_adv(kKP, 4096 * q + ko), ID_KK32, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma(dS_, make_desc(aDY + 32 * k, 16, 1024), make_desc(aU + 4096 * q + 32 * k, 16, 1024), ID_KK32,
-               k > 0);
+          umma(dS_, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
       }
       umma_commit(&bar_mma[0]);
+      SL_TOCK(6)
     }
-    ok = mbar_wait(&bar_mma[0], it & 1);
-    if (!ok) { report_timeout(12); s_abort = 1; }
+    if (live && !mbar_wait(&bar_mma[0], it & 1)) { report_timeout(12); s_abort = 1; live = false; }
     tc_fence_after_sync();
+    SL_TOCK(7)
 
     // ---- epilogue 1: decayed, strictly causal Pdec and dP as 16-bit tiles -------------------------------
-    {
-      uint32_t pr[32], ds[32];
-      tmem_ld32(tmem + lane_base + 0, pr);
-      tmem_ld32(tmem + lane_base + 32, ds);
+    if (live) {
+      uint32_t pr[SC], ds[SC];
+      tmem_ld<SC>(tmem + lane_base + 0 + cg * SC, pr);
+      tmem_ld<SC>(tmem + lane_base + 32 + cg * SC, ds);
       tmem_ld_wait();
       const float lt = sc[row];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < SC / 8; ++ch) {
         uint32_t wp[4], wd[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float vp[2], vd[2];
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
-            const int j = 8 * ch + 2 * e + q, s = 32 * hf + j;
+            const int j = 8 * ch + 2 * e + q, s = 32 * hf + cg * SC + j;
             const float dec = s < row ? __expf(fminf(lt - sc[s], 0.f)) : 0.f;
             vp[q] = dec * __uint_as_float(pr[j]);
             vd[q] = dec * __uint_as_float(ds[j]);
@@ -271,20 +313,20 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
           wp[e] = PK::pack(vp[0], vp[1]);
           wd[e] = PK::pack(vd[0], vd[1]);
         }
-        const uint32_t off = sw128(row, 4 * hf + ch);
+        const uint32_t off = sw128(row, 4 * hf + cg * (SC / 8) + ch);
         *reinterpret_cast<uint4*>(smem + B_OFF_PD + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
         *reinterpret_cast<uint4*>(smem + B_OFF_DP + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
       }
     }
     fence_async_smem();
     tc_fence_before_sync();
-    __syncthreads();
-    if (s_abort) { ok = false; break; }
+    bar_sync(1, NT);
+    live = s_abort == 0;
+    SL_TOCK(8)
 
     // ---- MMA group 2 ----------------------------------------------------------------------------------------
-    if (tid == 0) {
+    if (tid == 0 && live) {
       tc_fence_after_sync();
-      const uint32_t aU = smem_u32(tU), aDY = smem_u32(tDY), aZ = smem_u32(tZ);
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const uint32_t lb = tmem + ((16u * q) << 16);
@@ -292,48 +334,49 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
         for (int k = 0; k < 4; ++k) {
           const uint32_t mk = 2048 * k, kk = 32 * k;
           // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
-          umma(lb + 64, make_desc(aDP + kk, 16, 1024), make_desc(aKP + TILE * q + mk, 8192, 1024), ID_KM64, k > 0);
+          umma(lb + 64, desc_adv(kDP, kk), desc_adv(mKP, TILE * q + mk), ID_KM64, k > 0);
           // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
-          umma(lb + 128, make_desc(aDY + kk, 16, 1024), make_desc(aZ + TILE * q + mk, 8192, 1024), ID_KM64, k > 0);
+          umma(lb + 128, desc_adv(kDY, kk), desc_adv(mZ, TILE * q + mk), ID_KM64, k > 0);
           // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
-          umma(lb + 192, make_desc(aDP + mk, 8192, 1024), make_desc(aQ + TILE * q + mk, 8192, 1024), ID_MM64, k > 0);
+          umma(lb + 192, desc_adv(mDP, mk), desc_adv(mQ, TILE * q + mk), ID_MM64, k > 0);
           // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
-          umma(lb + 256, make_desc(aU + kk, 16, 1024), make_desc(aDW + TILE * q + mk, 8192, 1024), ID_KM64, k > 0);
+          umma(lb + 256, desc_adv(kU, kk), desc_adv(mDW, TILE * q + mk), ID_KM64, k > 0);
           // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
-          umma(lb + 320, make_desc(aPD + mk, 8192, 1024), make_desc(aDY + 64 * q + mk, 8192, 1024), ID_MM32, k > 0);
+          umma(lb + 320, desc_adv(mPD, mk), desc_adv(mDY, 64 * q + mk), ID_MM32, k > 0);
           // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
-          umma(lb + 384, make_desc(aDYO + mk, 8192, 1024), make_desc(aQ + TILE * q + mk, 8192, 1024), ID_MM64, k > 0);
+          umma(lb + 384, desc_adv(mDYO, mk), desc_adv(mQ, TILE * q + mk), ID_MM64, k > 0);
         }
         // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p (N = 32 half)
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          umma(lb + 352, make_desc(aKP + ko, 16, 1024), make_desc(aDW + 4096 * q + ko, 16, 1024), ID_KK32, k > 0);
+          umma(lb + 352, desc_adv(kKP, ko), desc_adv(kDW, 4096 * q + ko), ID_KK32, k > 0);
         }
       }
       umma_commit(&bar_mma[1]);
+      SL_TOCK(9)
     }
-    ok = mbar_wait(&bar_mma[1], it & 1);
-    if (!ok) { report_timeout(13); s_abort = 1; }
+    if (live && !mbar_wait(&bar_mma[1], it & 1)) { report_timeout(13); s_abort = 1; live = false; }
     tc_fence_after_sync();
+    SL_TOCK(10)
 
     const bool tok_valid = t0 + row < T;
-    const float sig = sc[12 * 64 + row];
+    const float sig = sw[1 * 64 + row];
     // ---- epilogue 2: dQ -> dC, <q,dq> ------------------------------------------------------------------
-    {
+    if (live) {
       const float et = sc[1 * 64 + row], phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
       const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
       float ar = 0.f, ai = 0.f;
-      TIn* dst = reinterpret_cast<TIn*>(p.dC) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf;
+      TIn* dst = reinterpret_cast<TIn*>(p.dC) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf + d0;
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t qa[32], qb[32];
-        tmem_ld32(tmem + lane_base + 64 + 32 * part, qa);
-        tmem_ld32(tmem + lane_base + 128 + 32 * part, qb);
+      for (int part = 0; part < ZC / PC; ++part) {
+        uint32_t qa[PC], qb[PC];
+        tmem_ld<PC>(tmem + lane_base + 64 + d0 + PC * part, qa);
+        tmem_ld<PC>(tmem + lane_base + 128 + d0 + PC * part, qb);
         tmem_ld_wait();
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t off = hf * TILE + sw128(row, 4 * part + ch);
+        for (int ch = 0; ch < PC / 8; ++ch) {
+          const uint32_t off = hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch);
           const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
           const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
           const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -351,27 +394,28 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
             const float dci = dqr * phi - dqi * phr + (skr * bb.y + ski * bb.x);
             o[e] = PK::pack(dcr, dci);
           }
-          if (tok_valid) *reinterpret_cast<uint4*>(dst + 32 * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+          if (tok_valid) *reinterpret_cast<uint4*>(dst + PC * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
-      sc[(16 + hf) * 64 + row] = ar;
-      sc[(18 + hf) * 64 + row] = ai;
+      s_acc[(0 * 8 + 2 * cg + hf) * 64 + row] = ar;
+      s_acc[(1 * 8 + 2 * cg + hf) * 64 + row] = ai;
     }
+    SL_TOCK(11)
     // ---- epilogue 3: dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
-    {
-      const float ee = sc[11 * 64 + row], wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
+    if (live) {
+      const float ee = sw[0 * 64 + row], wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
       const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];
       float rr = 0.f, ri = 0.f;
-      TIn* dst = reinterpret_cast<TIn*>(p.dB) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf;
+      TIn* dst = reinterpret_cast<TIn*>(p.dB) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf + d0;
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t xa[32], xb[32];
-        tmem_ld32(tmem + lane_base + 192 + 32 * part, xa);
-        tmem_ld32(tmem + lane_base + 256 + 32 * part, xb);
+      for (int part = 0; part < ZC / PC; ++part) {
+        uint32_t xa[PC], xb[PC];
+        tmem_ld<PC>(tmem + lane_base + 192 + d0 + PC * part, xa);
+        tmem_ld<PC>(tmem + lane_base + 256 + d0 + PC * part, xb);
         tmem_ld_wait();
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t off = hf * TILE + sw128(row, 4 * part + ch);
+        for (int ch = 0; ch < PC / 8; ++ch) {
+          const uint32_t off = hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch);
           const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
           const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
           const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -390,23 +434,24 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
             const float dbi = -wr * gb - wi * ga + (skr * cc.y - ski * cc.x);
             o[e] = PK::pack(dbr, dbi);
           }
-          if (tok_valid) *reinterpret_cast<uint4*>(dst + 32 * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+          if (tok_valid) *reinterpret_cast<uint4*>(dst + PC * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
-      sc[(20 + hf) * 64 + row] = rr;
-      sc[(22 + hf) * 64 + row] = ri;
+      s_acc[(2 * 8 + 2 * cg + hf) * 64 + row] = rr;
+      s_acc[(3 * 8 + 2 * cg + hf) * 64 + row] = ri;
     }
+    SL_TOCK(12)
     // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
-    {
-      uint32_t ua[32], ub[32];
-      tmem_ld32(tmem + lane_base + 320, ua);
-      tmem_ld32(tmem + lane_base + 352, ub);
+    if (live) {
+      uint32_t ua[SC], ub[SC];
+      tmem_ld<SC>(tmem + lane_base + 320 + cg * SC, ua);
+      tmem_ld<SC>(tmem + lane_base + 352 + cg * SC, ub);
       tmem_ld_wait();
-      const float ee = sc[11 * 64 + row], dgv = sc[13 * 64 + row];
-      TIn* dst = reinterpret_cast<TIn*>(p.dU) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf;
+      const float ee = sw[0 * 64 + row], dgv = sw[2 * 64 + row];
+      TIn* dst = reinterpret_cast<TIn*>(p.dU) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf + cg * SC;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const uint4 dv = *reinterpret_cast<const uint4*>(tDY + sw128(row, 4 * hf + ch));
+      for (int ch = 0; ch < SC / 8; ++ch) {
+        const uint4 dv = *reinterpret_cast<const uint4*>(tDY + sw128(row, 4 * hf + cg * (SC / 8) + ch));
         const uint32_t dw_[4] = {dv.x, dv.y, dv.z, dv.w};
         uint32_t o[4];
 #pragma unroll
@@ -419,22 +464,24 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
         if (tok_valid) *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
+    SL_TOCK(13)
     // ---- epilogue 5: dz <- e^{l_end} dWv + dZ ; anchor of the boundary below ----------------------------------
     {
       const float em = sc[1 * 64 + 63];
       float ar = 0.f, ai = 0.f;
+      if (live) {
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t zi[32];
-        tmem_ld32(tmem + lane_base + 384 + 32 * part, zi);
+      for (int part = 0; part < ZC / PC; ++part) {
+        uint32_t zi[PC];
+        tmem_ld<PC>(tmem + lane_base + 384 + d0 + PC * part, zi);
         tmem_ld_wait();
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint4 zv4 = *reinterpret_cast<const uint4*>(tZ + hf * TILE + sw128(row, 4 * part + ch));
+        for (int ch = 0; ch < PC / 8; ++ch) {
+          const uint4 zv4 = *reinterpret_cast<const uint4*>(tZ + hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch));
           const uint32_t zw[4] = {zv4.x, zv4.y, zv4.z, zv4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int j = 8 * ch + 2 * e, jj = 32 * part + j;
+            const int j = 8 * ch + 2 * e, jj = PC * part + j;
             const float da = em * dz[jj] + __uint_as_float(zi[j]);
             const float db = em * dz[jj + 1] + __uint_as_float(zi[j + 1]);
             dz[jj] = da; dz[jj + 1] = db;
@@ -444,32 +491,40 @@ __global__ void __launch_bounds__(128, 1) scan_tc_bwd_kernel(const __grid_consta
           }
         }
       }
+      }
       float sr, si;
       block_sum2(ar, ai, sr, si);   // contains two barriers: also orders the table writes above
       if (tid == 0 && c > 0) p.anchor[(size_t)bh * nC + c - 1] = make_float2(sr, si);
     }
+    SL_TOCK(14)
     // ---- per-token scalars of this chunk ---------------------------------------------------------------------
-    if (tid < 64 && t0 + tid < T) {
+    if (live && tid < 64 && t0 + tid < T) {
       const int t = tid;
-      const float Ar = sc[16 * 64 + t] + sc[17 * 64 + t], Ai = sc[18 * 64 + t] + sc[19 * 64 + t];
-      const float Rr = sc[20 * 64 + t] + sc[21 * 64 + t], Ri = sc[22 * 64 + t] + sc[23 * 64 + t];
+      float Ar = 0.f, Ai = 0.f, Rr = 0.f, Ri = 0.f;
+#pragma unroll
+      for (int k = 0; k < 2 * NW; ++k) {
+        Ar += s_acc[(0 * 8 + k) * 64 + t]; Ai += s_acc[(1 * 8 + k) * 64 + t];
+        Rr += s_acc[(2 * 8 + k) * 64 + t]; Ri += s_acc[(3 * 8 + k) * 64 + t];
+      }
       const float phr = sc[2 * 64 + t], phi = sc[3 * 64 + t], wr = sc[4 * 64 + t], wi = sc[5 * 64 + t];
       const size_t o = (size_t)bh * T + t0 + t;
       p.dg[o] = make_float2(phr * Rr - phi * Ri, phr * Ri + phi * Rr);                 // phi R
       p.sterm[o] = make_float2(Ar - (wr * Rr + wi * Ri), Ai - (wr * Ri - wi * Rr));   // A - conj(w) R
-      const float sg = sc[12 * 64 + t];
-      p.dkcd[o] = make_float2(sg * sc[14 * 64 + t], sg * sc[15 * 64 + t]);
+      const float sg = sw[1 * 64 + t];
+      p.dkcd[o] = make_float2(sg * sw[3 * 64 + t], sg * sw[4 * 64 + t]);
     }
     fence_async_smem();
     tc_fence_before_sync();
+    }  // worker
     __syncthreads();
+    SL_TOCK(15)
     if (s_abort) { ok = false; break; }
   }
 
-  if (ok && p.dinit) {
-    float* dst = p.dinit + ((size_t)bh * 64 + row) * 128 + 64 * hf;
+  if (ok && p.dinit && worker) {
+    float* dst = p.dinit + ((size_t)bh * 64 + row) * 128 + 64 * hf + d0;
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
+    for (int j = 0; j < ZC / 4; ++j)
       *reinterpret_cast<float4*>(dst + 4 * j) =
           make_float4(dz[4 * j], -dz[4 * j + 1], dz[4 * j + 2], -dz[4 * j + 3]);
   }

@@ -1,0 +1,343 @@
+// Forward kernel of the chunked scan on tcgen05 (included by scan_tc.cu inside its namespaces).
+//
+// NW = warps per TMEM lane quadrant.  The CTA has 4*NW warps; warp w works on TMEM lanes
+// 32*(w & 3) .. +31 (a hardware rule) and, inside every accumulator, on the column group
+// (w >> 2) of NW.  Thread (quad, cg, lane) therefore owns row 16*quad + (lane & 15), the
+// column half (lane >> 4) and 1/NW of that half's columns of every result matrix.
+//
+// STATES_ONLY: the state pre-sweep of the backward pass (no C, no scores, no Y).
+template <typename TIn, typename TY, bool STATES_ONLY, int NW>
+__global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
+  constexpr int NT = 128 * NW;  // worker threads; one more warp prepares the per-chunk scalars
+  constexpr int ZC = 64 / NW;   // state columns per thread (pairs stay inside a thread)
+  constexpr int SC = 32 / NW;   // score / output columns per thread
+  constexpr int RSTEP = NT / 16;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ uint64_t bar_tma[2], bar_mma[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  float* sc_tab = reinterpret_cast<float*>(smem + OFF_SCAL);   // two tables: chunk parity
+  using PK = Pack2<TIn>;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool worker = warp < 4 * NW;     // the last warp only runs chunk_scalars one chunk ahead
+  const int quad = warp & 3, cg = worker ? (warp >> 2) : 0;
+  const int row = 16 * quad + (lane & 15), hf = lane >> 4;   // epilogue identity
+  const int rcol = tid & 15, rrow0 = tid >> 4;               // rotation identity
+  const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
+  const int bh = blockIdx.x, b = bh / p.heads, h = bh % p.heads;
+  const int bg = b * p.groups + h / (p.heads / p.groups);
+  const int T = p.T;
+  const float* Mb = p.M + (size_t)bh * T * 2;
+  const float* Kb = p.K + (size_t)bh * T * 4;
+
+  if (tid == 0) {
+    mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
+    mbar_init(&bar_mma[0], 1); mbar_init(&bar_mma[1], 1);
+    fence_barrier_init();
+    s_abort = 0;
+    tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  auto issue_loads = [&](int c) {   // one thread
+    uint8_t* st = smem + (c & 1) * STAGE;
+    uint64_t* bar = &bar_tma[c & 1];
+    mbar_expect_tx(bar, STATES_ONLY ? 3 * TILE : STAGE);
+    tma_load_3d(st, &p.tmU, bar, 0, c * L, bh);
+    tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bg);
+    tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bg);
+    if (!STATES_ONLY) {
+      tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bg);
+      tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bg);
+    }
+  };
+  if (tid == 0) issue_loads(0);
+
+  // ---- carried state, conjugated: zv[2j], zv[2j+1] = (re, -im) of column pair j of this thread ----
+  const int d0 = 64 * hf + cg * ZC;   // first state column of this thread
+  float zv[ZC];
+#pragma unroll
+  for (int j = 0; j < ZC; ++j) zv[j] = 0.f;
+  if (worker) {
+    const TIn* Bp = reinterpret_cast<const TIn*>(p.Bprev);
+    const TIn* Up = reinterpret_cast<const TIn*>(p.Uprev);
+    float cr = 0.f, ci = 0.f, up = 0.f;
+    if (Bp) {  // pending prev-tap of the token before the sequence: u_prev (x) (kp_0 / m_0) b_prev
+      const float mr = Mb[0], mi = Mb[1], kr = Kb[0], ki = Kb[1];
+      const float den = mr * mr + mi * mi;
+      cr = (kr * mr + ki * mi) / den; ci = (ki * mr - kr * mi) / den;
+      up = to_f32(Up[(size_t)bh * 64 + row]);
+    }
+#pragma unroll
+    for (int j = 0; j < ZC / 2; ++j) {
+      const int d = d0 + 2 * j;
+      float re = 0.f, im = 0.f;
+      if (p.z0) {
+        const float2 z = *reinterpret_cast<const float2*>(p.z0 + ((size_t)bh * 64 + row) * 128 + d);
+        re = z.x; im = z.y;
+      }
+      if (Bp) {
+        const float br = to_f32(Bp[(size_t)bg * 128 + d]), bi = to_f32(Bp[(size_t)bg * 128 + d + 1]);
+        re += up * (cr * br - ci * bi);
+        im += up * (cr * bi + ci * br);
+      }
+      zv[2 * j] = re; zv[2 * j + 1] = -im;
+    }
+  }
+  auto pack8 = [&](int ch) {
+    uint4 v;
+    v.x = PK::pack(zv[8 * ch + 0], zv[8 * ch + 1]); v.y = PK::pack(zv[8 * ch + 2], zv[8 * ch + 3]);
+    v.z = PK::pack(zv[8 * ch + 4], zv[8 * ch + 5]); v.w = PK::pack(zv[8 * ch + 6], zv[8 * ch + 7]);
+    return v;
+  };
+  auto store_zv_tile = [&]() {   // 16-bit copy of the state: rows p, K-major along d
+    uint8_t* zt = smem + OFF_ZV + hf * TILE;
+#pragma unroll
+    for (int ch = 0; ch < ZC / 8; ++ch)
+      *reinterpret_cast<uint4*>(zt + sw128(row, cg * (ZC / 8) + ch)) = pack8(ch);
+  };
+  auto store_chunk_state = [&](int c) {   // conjugated form, 16-bit, row-major [p][128]
+    if (!p.states16) return;
+    TIn* dst = reinterpret_cast<TIn*>(p.states16) + (((size_t)bh * p.nchunks + c) * 64 + row) * 128 + d0;
+#pragma unroll
+    for (int ch = 0; ch < ZC / 8; ++ch) *reinterpret_cast<uint4*>(dst + 8 * ch) = pack8(ch);
+  };
+  if (worker) store_zv_tile();
+  else chunk_scalars(sc_tab, Mb, Kb, 0, T, lane);
+  __syncthreads();
+
+  constexpr uint32_t ID_S = make_idesc(64, 32, PK::fmt, 0, 0);     // K-major x K-major
+  constexpr uint32_t ID_Y = make_idesc(64, 32, PK::fmt, 0, 1);     // K-major x MN-major
+  constexpr uint32_t ID_Z = make_idesc(64, 64, PK::fmt, 1, 1);     // MN-major x MN-major
+  const uint32_t aKPP = smem_u32(smem + OFF_KPP), aS = smem_u32(smem + OFF_S),
+                 aZV = smem_u32(smem + OFF_ZV);
+  bool ok = true;
+#ifdef SL_TC_TIMING
+#define SL_TICK(i) if (bh == 0 && tid == 0 && c == 8) g_tc_timing[i] = clock64();
+#else
+#define SL_TICK(i)
+#endif
+
+  for (int c = 0; c < p.nchunks && ok; ++c) {
+    SL_TICK(0)
+    const int t0 = c * L;
+    uint8_t* st = smem + (c & 1) * STAGE;
+    float* sc = sc_tab + (c & 1) * (NSCAL * 64);
+    float* s_diag = sc + 11 * 64;
+    if (tid == 0 && c + 1 < p.nchunks) issue_loads(c + 1);
+    if (!worker) {
+      // scalars of the NEXT chunk; this warp only meets the others at the barrier that ends the
+      // iteration, so its global loads and scans overlap the whole chunk
+      if (c + 1 < p.nchunks) chunk_scalars(sc_tab + ((c + 1) & 1) * (NSCAL * 64), Mb, Kb, t0 + L, T, lane);
+    } else {
+    bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
+    store_chunk_state(c);
+    if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1)) { report_timeout(1); s_abort = 1; }
+    bar_sync(1, NT);
+    live = s_abort == 0;
+    SL_TICK(1)
+
+    // ---- rotation: C -> Q, B -> K' (both in place), K'' ; diagonal scores --------------------
+    if (live) {
+      const uint32_t half = rcol >> 3, ch = rcol & 7;
+      uint8_t* tB = st + TILE + half * TILE;
+      uint8_t* tC = st + 3 * TILE + half * TILE;
+      uint8_t* tK = smem + OFF_KPP + half * TILE;
+#pragma unroll
+      for (int k = 0; k < 64 / RSTEP; ++k) {
+        const int r = rrow0 + RSTEP * k;
+        const uint32_t off = sw128(r, ch);
+        const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
+        const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
+        const float vr = sc[6 * 64 + r], vi = sc[7 * 64 + r];
+        const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
+        uint4 cv = make_uint4(0u, 0u, 0u, 0u);
+        if (!STATES_ONLY) cv = *reinterpret_cast<const uint4*>(tC + off);
+        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t qo[4], ko[4], vo[4];
+        float dg = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
+          qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
+          ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
+          vo[e] = PK::pack(vr * bb.x - vi * bb.y, -(vr * bb.y + vi * bb.x));      // conj(v b)
+          const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
+          dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
+        }
+        *reinterpret_cast<uint4*>(tK + off) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
+        if (!STATES_ONLY) {
+          *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+          *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
+          if (rcol == 0) s_diag[r] = dg;
+        }
+      }
+    }
+    fence_async_smem();
+    bar_sync(1, NT);
+    SL_TICK(2)
+
+    if (!STATES_ONLY) {
+      // ---- MMA group 1: scores and off-term --------------------------------------------------
+      if (tid == 0 && live) {
+        tc_fence_after_sync();
+        const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);
+        const uint64_t bC = make_desc(smem_u32(st + 3 * TILE), 16, 1024);
+        const uint64_t bZ = make_desc(aZV, 16, 1024);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t dS = tmem + ((16u * q) << 16), dO = dS + 32;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+            const uint64_t da = desc_adv(bC, ko);
+            umma(dS, da, desc_adv(bB, 4096 * q + ko), ID_S, k > 0);
+            umma(dO, da, desc_adv(bZ, 4096 * q + ko), ID_S, k > 0);
+          }
+        }
+        umma_commit(&bar_mma[0]);
+        SL_TICK(3)
+      }
+      if (live && !mbar_wait(&bar_mma[0], c & 1)) { report_timeout(2); s_abort = 1; live = false; }
+      tc_fence_after_sync();
+      SL_TICK(4)
+
+      // ---- scores epilogue: decay, causal mask, diagonal -> 16-bit S tile ------------------------
+      if (live) {
+        uint32_t r[SC];
+        tmem_ld<SC>(tmem + lane_base + cg * SC, r);
+        tmem_ld_wait();
+        const float lt = sc[row];
+        const float dgv = s_diag[row];
+        uint8_t* tS = smem + OFF_S;
+#pragma unroll
+        for (int ch = 0; ch < SC / 8; ++ch) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float v2[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int j = 8 * ch + 2 * e + q, s = 32 * hf + cg * SC + j;
+              float v = __uint_as_float(r[j]) * __expf(fminf(lt - sc[s], 0.f));
+              v = s < row ? v : (s == row ? dgv : 0.f);
+              v2[q] = v;
+            }
+            w[e] = PK::pack(v2[0], v2[1]);
+          }
+          *reinterpret_cast<uint4*>(tS + sw128(row, 4 * hf + cg * (SC / 8) + ch)) =
+              make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before_sync();
+      bar_sync(1, NT);
+      live = s_abort == 0;
+      SL_TICK(5)
+    }
+
+    // ---- MMA group 2: Y_diag = S U, Inc = U^T K'' --------------------------------------------------
+    if (tid == 0 && live) {
+      tc_fence_after_sync();
+      const uint64_t bS = make_desc(aS, 16, 1024);
+      const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
+      const uint64_t bK = make_desc(aKPP, 8192, 1024);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t dY = tmem + ((16u * q) << 16) + 64, dZ = tmem + ((16u * q) << 16) + 128;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (!STATES_ONLY) umma(dY, desc_adv(bS, 32 * k), desc_adv(bU, 64 * q + 2048 * k), ID_Y, k > 0);
+          umma(dZ, desc_adv(bU, 2048 * k), desc_adv(bK, TILE * q + 2048 * k), ID_Z, k > 0);
+        }
+      }
+      umma_commit(&bar_mma[1]);
+      SL_TICK(6)
+    }
+    if (live && !mbar_wait(&bar_mma[1], c & 1)) { report_timeout(3); s_abort = 1; live = false; }
+    tc_fence_after_sync();
+    SL_TICK(7)
+
+    // ---- output epilogue: y = Y_diag + exp(l_t) Y_off -----------------------------------------------
+    if (!STATES_ONLY && live) {
+      uint32_t yd[SC], yo[SC];
+      tmem_ld<SC>(tmem + lane_base + 64 + cg * SC, yd);
+      tmem_ld<SC>(tmem + lane_base + 32 + cg * SC, yo);
+      tmem_ld_wait();
+      const float et = sc[1 * 64 + row];
+      if (t0 + row < T) {
+        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf + cg * SC;
+        if constexpr (sizeof(TY) == 2) {
+          using PY = Pack2<TY>;
+#pragma unroll
+          for (int v = 0; v < SC / 8; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = 8 * v + 2 * e;
+              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
+                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < SC / 4; ++v) {
+            float4 o;
+            o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
+            o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
+            o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
+            o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
+          }
+        }
+      }
+    }
+    SL_TICK(8)
+    // ---- state update: zv = conj(Pi_end) zv + Inc ---------------------------------------------------
+    if (live) {
+      const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
+      uint32_t inc[ZC];
+      tmem_ld<ZC>(tmem + lane_base + 128 + cg * ZC, inc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < ZC / 2; ++j) {
+        const float a = zv[2 * j], bq = zv[2 * j + 1];
+        zv[2 * j] = pr * a + pi * bq + __uint_as_float(inc[2 * j]);
+        zv[2 * j + 1] = pr * bq - pi * a + __uint_as_float(inc[2 * j + 1]);
+      }
+      store_zv_tile();
+    }
+    SL_TICK(9)
+    fence_async_smem();
+    tc_fence_before_sync();
+    }  // worker
+    __syncthreads();
+    if (s_abort) { ok = false; break; }
+    SL_TICK(10)
+  }
+
+  if (ok && p.zfinal && worker) {
+    float* dst = p.zfinal + ((size_t)bh * 64 + row) * 128 + d0;
+#pragma unroll
+    for (int j = 0; j < ZC / 4; ++j)
+      *reinterpret_cast<float4*>(dst + 4 * j) =
+          make_float4(zv[4 * j], -zv[4 * j + 1], zv[4 * j + 2], -zv[4 * j + 3]);
+  }
+  // unwind: nothing of ours may still be in flight when shared memory / TMEM are released
+  if (!ok && tid == 0) {
+    for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);   // bounded; best effort drain
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}

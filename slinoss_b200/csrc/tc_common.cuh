@@ -120,6 +120,17 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int fmt, int a_m
          ((uint32_t)b_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// A descriptor advanced by a byte offset inside the same tile stack: only the 14-bit start
+// address field changes and it cannot carry (shared memory is < 256 KB), so a 32-bit add on
+// the low word is enough.  Keeps the per-MMA work of the issuing thread to two adds.
+__device__ __forceinline__ uint64_t desc_adv(uint64_t base, uint32_t byte_off) {
+  return base + (uint64_t)(byte_off >> 4);
+}
+// named barrier among the first `nthreads` threads of the CTA (id 1..15)
+__device__ __forceinline__ void bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                      uint32_t accumulate) {
@@ -152,6 +163,36 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// Narrower variants: 16 and 8 consecutive columns.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
+// N consecutive columns, N in {8, 16, 32, 64}
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16 || N == 32 || N == 64, "unsupported TMEM load width");
+  if constexpr (N == 8) tmem_ld8(taddr, r);
+  else if constexpr (N == 16) tmem_ld16(taddr, r);
+  else if constexpr (N == 32) tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r));
+  else {
+    tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_ld32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
+  }
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
