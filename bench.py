@@ -202,9 +202,12 @@ def main():
     U, M, K, B, C, dY = case.U, case.M, case.K, case.B, case.C, case.dY
 
     def step_device():
-        _C.scan_fwd(U, M, K, B, C, None, None, None, chunk_size=c["chunk"], y_dtype=torch.bfloat16,
-                    want_final=False, path=args.path)
-        _C.scan_bwd(U, M, K, B, C, None, None, None, dY, None, chunk_size=c["chunk"], path=args.path)
+        # what autograd does: the forward keeps its chunk-start states for the backward
+        _, fin, st = _C.scan_fwd(U, M, K, B, C, None, None, None, chunk_size=c["chunk"],
+                                 y_dtype=torch.bfloat16, want_final=False, path=args.path,
+                                 save_states=True)
+        _C.scan_bwd(U, M, K, B, C, None, None, None, dY, None, chunk_size=c["chunk"], path=args.path,
+                    saved=(st, fin))
 
     def barrier():
         if dist is not None:
@@ -233,10 +236,12 @@ def main():
     # per-phase split (separate short loop so that the events do not perturb the headline)
     for _ in range(min(args.steps, 5)):
         e0.record()
-        _C.scan_fwd(U, M, K, B, C, None, None, None, chunk_size=c["chunk"], y_dtype=torch.bfloat16,
-                    want_final=False, path=args.path)
+        _, fin, st = _C.scan_fwd(U, M, K, B, C, None, None, None, chunk_size=c["chunk"],
+                                 y_dtype=torch.bfloat16, want_final=False, path=args.path,
+                                 save_states=True)
         e1.record()
-        _C.scan_bwd(U, M, K, B, C, None, None, None, dY, None, chunk_size=c["chunk"], path=args.path)
+        _C.scan_bwd(U, M, K, B, C, None, None, None, dY, None, chunk_size=c["chunk"], path=args.path,
+                    saved=(st, fin))
         e2.record()
         torch.cuda.synchronize()
         fwd_ms += e0.elapsed_time(e1)

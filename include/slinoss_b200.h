@@ -64,7 +64,8 @@ enum {
   SL_WS_SCAN_FWD = 0,
   SL_WS_SCAN_BWD = 1,
   SL_WS_SCANPREP_BWD = 2,
-  SL_WS_TAIL_BWD = 3
+  SL_WS_TAIL_BWD = 3,
+  SL_WS_SCAN_STATES = 4 /* optional chunk-state buffer handed from forward to backward */
 };
 
 /* Library version, major*10000 + minor*100 + patch. */
@@ -96,12 +97,16 @@ SL_API size_t sl_workspace_bytes(int kind, int batch, int heads, int groups, int
  *   U, B, C, B_prev, U_prev : io_dtype;  Y : y_dtype;  M, K, states : float32.
  *   initial_states, B_prev, U_prev, final_state may be NULL (B_prev and U_prev
  *   together).  T must be >= 1 (T == 0 is answered by the host wrapper).
+ *   chunk_states (optional, sl_workspace_bytes(SL_WS_SCAN_STATES, ...) bytes): when given
+ *   together with final_state, the tensor-core path stores the state at the start of every
+ *   64-token chunk there; handing both to sl_v2x2ssd_bwd saves its state pre-sweep.  The
+ *   reference recomputes instead (it saves only the inputs); passing NULL does the same.
  */
 SL_API int sl_v2x2ssd_fwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                    const float* initial_states, const void* B_prev, const void* U_prev,
-                   void* Y, float* final_state, int batch, int heads, int groups, int T, int P,
-                   int N, int chunk, int io_dtype, int y_dtype, int path, void* workspace,
-                   size_t workspace_bytes, void* stream);
+                   void* Y, float* final_state, void* chunk_states, int batch, int heads,
+                   int groups, int T, int P, int N, int chunk, int io_dtype, int y_dtype, int path,
+                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Scan backward.  Replaces _V2x2SSDCuTeTrainingFn.backward
@@ -110,9 +115,12 @@ SL_API int sl_v2x2ssd_fwd(const void* U, const float* M, const float* K, const v
  *   dU, dB, dC, dB_prev, dU_prev : io_dtype;  dM, dK, d_initial : float32.
  *   d_initial, dB_prev, dU_prev may be NULL.  Grouped dB/dC/dB_prev are summed
  *   over the heads of a group in float32 before the cast.
+ *   chunk_states / final_state: both as filled by sl_v2x2ssd_fwd for the same inputs,
+ *   or both NULL (then the backward recomputes them).
  */
 SL_API int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                    const float* initial_states, const void* B_prev, const void* U_prev,
+                   const void* chunk_states, const float* final_state,
                    const void* dY, const float* d_final_state, void* dU, float* dM, float* dK,
                    void* dB, void* dC, float* d_initial, void* dB_prev, void* dU_prev,
                    int batch, int heads, int groups, int T, int P, int N, int chunk,

@@ -25,7 +25,7 @@ _lib = None
 
 SL_F32, SL_BF16, SL_F16 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
-WS_SCAN_FWD, WS_SCAN_BWD = 0, 1
+WS_SCAN_FWD, WS_SCAN_BWD, WS_SCAN_STATES = 0, 1, 4
 
 _DTYPE_CODE = {torch.float32: SL_F32, torch.bfloat16: SL_BF16, torch.float16: SL_F16}
 _PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tc": PATH_TC}
@@ -44,8 +44,8 @@ _PROTOTYPES = {
     "sl_device_status": (c_int, []),
     "sl_status_string": (ctypes.c_char_p, [c_int]),
     "sl_workspace_bytes": (c_size_t, [c_int] * 10),
-    "sl_v2x2ssd_fwd": (c_int, [_P] * 10 + [c_int] * 10 + [_P, c_size_t, _P]),
-    "sl_v2x2ssd_bwd": (c_int, [_P] * 18 + [c_int] * 10 + [_P, c_size_t, _P]),
+    "sl_v2x2ssd_fwd": (c_int, [_P] * 11 + [c_int] * 10 + [_P, c_size_t, _P]),
+    "sl_v2x2ssd_bwd": (c_int, [_P] * 20 + [c_int] * 10 + [_P, c_size_t, _P]),
     "sl_static_scratch_bytes": (c_size_t, []),
     "sl_v2x2ssd_bwd_static": (c_int, [_P] * 18 + [c_int] * 8 + [_P]),
     "sl_v2x2ssd_decode": (c_int, [_P] * 10 + [c_int] * 7 + [_P]),
@@ -145,29 +145,42 @@ def workspace_bytes(kind, batch, heads, groups, T, P, N, chunk, io_dtype, path="
 # ---------------------------------------------------------------------------------
 # scan
 # ---------------------------------------------------------------------------------
-def scan_fwd(U, M, K, B, C, z0, B_prev, U_prev, *, chunk_size, y_dtype, want_final, path="auto"):
+def scan_fwd(U, M, K, B, C, z0, B_prev, U_prev, *, chunk_size, y_dtype, want_final, path="auto",
+             save_states=False):
     """Launch ``sl_v2x2ssd_fwd``.  ``U,B,C,B_prev,U_prev`` share one dtype; ``M,K,z0``
-    are float32.  Returns ``(Y, final_state or None)``."""
+    are float32.  Returns ``(Y, final_state or None)``; with ``save_states`` a third item:
+    the chunk-state buffer for ``scan_bwd`` (None when the chosen path keeps none)."""
     dev = require_cuda(U, M, K, B, C, z0, B_prev, U_prev)
     batch, heads, T, P = U.shape
     groups, N = B.shape[1], B.shape[3] // 2
     io, pcode = dtype_code(U.dtype), _PATHS[path]
     Y = torch.empty((batch, heads, T, P), dtype=y_dtype, device=dev)
-    final = torch.empty((batch, heads, P, 2 * N), dtype=torch.float32, device=dev) \
-        if want_final else None
+    states = None
     with torch.cuda.device(dev):
+        if save_states and B_prev is None and groups == heads:
+            sbytes = lib().sl_workspace_bytes(WS_SCAN_STATES, batch, heads, groups, T, P, N,
+                                              chunk_size, io, pcode)
+            if sbytes:
+                states = torch.empty(sbytes, dtype=torch.uint8, device=dev)
+        final = torch.empty((batch, heads, P, 2 * N), dtype=torch.float32, device=dev) \
+            if (want_final or states is not None) else None
         ws, nbytes = _workspace(WS_SCAN_FWD, dev, batch, heads, groups, T, P, N, chunk_size, io, pcode)
         check(lib().sl_v2x2ssd_fwd(
             _ptr(U), _ptr(M), _ptr(K), _ptr(B), _ptr(C), _ptr(z0), _ptr(B_prev), _ptr(U_prev),
-            _ptr(Y), _ptr(final), batch, heads, groups, T, P, N, chunk_size, io,
+            _ptr(Y), _ptr(final), _ptr(states), batch, heads, groups, T, P, N, chunk_size, io,
             dtype_code(y_dtype), pcode, _ptr(ws), nbytes, _stream(dev)), "sl_v2x2ssd_fwd")
+    if save_states:
+        return Y, final, states
     return Y, final
 
 
-def scan_bwd(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *, chunk_size, path="auto"):
+def scan_bwd(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *, chunk_size, path="auto",
+             saved=None):
     """Launch ``sl_v2x2ssd_bwd``.  Returns ``(dU, dM, dK, dB, dC, d_initial, dB_prev,
-    dU_prev)``; the last three are None when the matching input is absent."""
+    dU_prev)``; the last three are None when the matching input is absent.  ``saved`` is
+    ``(chunk_states, final_state)`` from ``scan_fwd(..., save_states=True)`` or None."""
     dev = require_cuda(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final)
+    states, zfinal = saved if (saved is not None and saved[0] is not None) else (None, None)
     batch, heads, T, P = U.shape
     groups, N = B.shape[1], B.shape[3] // 2
     io, pcode = dtype_code(U.dtype), _PATHS[path]
@@ -185,9 +198,10 @@ def scan_bwd(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *, chunk_size, path
         ws, nbytes = _workspace(WS_SCAN_BWD, dev, batch, heads, groups, T, P, N, chunk_size, io, pcode)
         check(lib().sl_v2x2ssd_bwd(
             _ptr(U), _ptr(M), _ptr(K), _ptr(B), _ptr(C), _ptr(z0), _ptr(B_prev), _ptr(U_prev),
-            _ptr(dY), _ptr(d_final), _ptr(dU), _ptr(dM), _ptr(dK), _ptr(dB), _ptr(dC),
-            _ptr(d_init), _ptr(dB_prev), _ptr(dU_prev), batch, heads, groups, T, P, N,
-            chunk_size, io, dy_code, pcode, _ptr(ws), nbytes, _stream(dev)), "sl_v2x2ssd_bwd")
+            _ptr(states), _ptr(zfinal), _ptr(dY), _ptr(d_final), _ptr(dU), _ptr(dM), _ptr(dK),
+            _ptr(dB), _ptr(dC), _ptr(d_init), _ptr(dB_prev), _ptr(dU_prev), batch, heads, groups,
+            T, P, N, chunk_size, io, dy_code, pcode, _ptr(ws), nbytes, _stream(dev)),
+            "sl_v2x2ssd_bwd")
     return dU, dM, dK, dB, dC, d_init, dB_prev, dU_prev
 
 

@@ -12,12 +12,14 @@ void note_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::mem
 bool scan_tc_supported(const ScanDims& d, int io_dtype);
 size_t scan_tc_fwd_workspace(const ScanDims& d);
 size_t scan_tc_bwd_workspace(const ScanDims& d);
+size_t scan_tc_states_bytes(const ScanDims& d);
 int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                 const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
-                const ScanDims& d, int io_dtype, int y_dtype, void* ws, size_t ws_bytes,
-                cudaStream_t st);
+                void* states_out, const ScanDims& d, int io_dtype, int y_dtype, void* ws,
+                size_t ws_bytes, cudaStream_t st);
 int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
-                const float* z0, const void* Bprev, const void* Uprev, const void* dY,
+                const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
+                const float* zfinal_in, const void* dY,
                 const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC,
                 float* dinit, void* dBprev, void* dUprev, const ScanDims& d, int io_dtype,
                 int dy_dtype, void* ws, size_t ws_bytes, cudaStream_t st);
@@ -86,6 +88,8 @@ extern "C" size_t sl_workspace_bytes(int kind, int batch, int heads, int groups,
       return use_tc(path, d, io_dtype) ? scan_tc_fwd_workspace(d) : 0;
     case SL_WS_SCAN_BWD:
       return use_tc(path, d, io_dtype) ? scan_tc_bwd_workspace(d) : scan_simt_bwd_workspace(d);
+    case SL_WS_SCAN_STATES:
+      return use_tc(path, d, io_dtype) ? scan_tc_states_bytes(d) : 0;
     default:
       return 0;
   }
@@ -93,10 +97,10 @@ extern "C" size_t sl_workspace_bytes(int kind, int batch, int heads, int groups,
 
 extern "C" int sl_v2x2ssd_fwd(const void* U, const float* M, const float* K, const void* B,
                               const void* C, const float* initial_states, const void* B_prev,
-                              const void* U_prev, void* Y, float* final_state, int batch,
-                              int heads, int groups, int T, int P, int N, int chunk,
-                              int io_dtype, int y_dtype, int path, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+                              const void* U_prev, void* Y, float* final_state,
+                              void* chunk_states, int batch, int heads, int groups, int T, int P,
+                              int N, int chunk, int io_dtype, int y_dtype, int path,
+                              void* workspace, size_t workspace_bytes, void* stream) {
   using namespace sl;
   const ScanDims d{batch, heads, groups, T, P, N, chunk};
   if (int e = check_scan(U, M, K, B, C, B_prev, U_prev, d, io_dtype)) return e;
@@ -105,16 +109,19 @@ extern "C" int sl_v2x2ssd_fwd(const void* U, const float* M, const float* K, con
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == SL_PATH_TC && !scan_tc_supported(d, io_dtype)) return SL_ERR_UNSUPPORTED;
   if (use_tc(path, d, io_dtype))
-    return scan_tc_fwd(U, M, K, B, C, initial_states, B_prev, U_prev, Y, final_state, d,
-                       io_dtype, y_dtype, workspace, workspace_bytes, st);
+    return scan_tc_fwd(U, M, K, B, C, initial_states, B_prev, U_prev, Y, final_state,
+                       final_state ? chunk_states : nullptr, d, io_dtype, y_dtype, workspace,
+                       workspace_bytes, st);
   return scan_simt_fwd(U, M, K, B, C, initial_states, B_prev, U_prev, Y, final_state, d,
                        io_dtype, y_dtype, st);
 }
 
 extern "C" int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, const void* B,
                               const void* C, const float* initial_states, const void* B_prev,
-                              const void* U_prev, const void* dY, const float* d_final_state,
-                              void* dU, float* dM, float* dK, void* dB, void* dC,
+                              const void* U_prev, const void* chunk_states,
+                              const float* final_state, const void* dY,
+                              const float* d_final_state, void* dU, float* dM, float* dK,
+                              void* dB, void* dC,
                               float* d_initial, void* dB_prev, void* dU_prev, int batch,
                               int heads, int groups, int T, int P, int N, int chunk,
                               int io_dtype, int dy_dtype, int path, void* workspace,
@@ -127,7 +134,9 @@ extern "C" int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, con
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == SL_PATH_TC && !scan_tc_supported(d, io_dtype)) return SL_ERR_UNSUPPORTED;
   if (use_tc(path, d, io_dtype))
-    return scan_tc_bwd(U, M, K, B, C, initial_states, B_prev, U_prev, dY, d_final_state, dU, dM,
+    return scan_tc_bwd(U, M, K, B, C, initial_states, B_prev, U_prev,
+                       final_state ? chunk_states : nullptr, chunk_states ? final_state : nullptr, dY,
+                       d_final_state, dU, dM,
                        dK, dB, dC, d_initial, dB_prev, dU_prev, d, io_dtype, dy_dtype, workspace,
                        workspace_bytes, st);
   return scan_simt_bwd(U, M, K, B, C, initial_states, B_prev, U_prev, dY, d_final_state, dU, dM,

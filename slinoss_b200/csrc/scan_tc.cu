@@ -40,14 +40,13 @@ using namespace tc;
 
 constexpr int L = 64;
 constexpr uint32_t TILE = 8192;           // one [64][128 B] tile
-constexpr uint32_t STAGE = 5 * TILE;      // U | B(2) | C(2)
+constexpr uint32_t STAGE = 7 * TILE;      // U | B0 | Zv0 | B1 | Zv1 | C0 | C1  (Zv written by the CTA)
 constexpr uint32_t OFF_KPP = 2 * STAGE;   // K'' (2 tiles)
 constexpr uint32_t OFF_S = OFF_KPP + 2 * TILE;
-constexpr uint32_t OFF_ZV = OFF_S + TILE; // Zv (2 tiles)
-constexpr uint32_t OFF_SCAL = OFF_ZV + 2 * TILE;
+constexpr uint32_t OFF_SCAL = OFF_S + TILE;
 constexpr int NSCAL = 12;                 // per-token float arrays
 constexpr uint32_t SMEM_BYTES = OFF_SCAL + 2 * NSCAL * 64 * 4 + 64 + 1024;
-constexpr uint32_t TMEM_COLS = 256;       // S 0..31 | Yoff 32..63 | Ydiag 64..95 | Inc 128..191
+constexpr uint32_t TMEM_COLS = 512;       // S 0..63 | Yoff 64..127 | Ydiag 128..191 | Inc 192..319
 
 __device__ int g_tc_status = 0;
 #ifdef SL_TC_TIMING
@@ -213,11 +212,8 @@ static int launch_tc_fwd_nw(const TcFwdParams& p, int grid, cudaStream_t st) {
 }
 template <typename TIn, typename TY, bool STATES_ONLY>
 static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
-  switch (g_tc_nw) {
-    case 1: return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 1>(p, grid, st);
-    case 2: return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 2>(p, grid, st);
-    default: return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 4>(p, grid, st);
-  }
+  if (g_tc_nw == 2) return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 2>(p, grid, st);
+  return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 4>(p, grid, st);
 }
 
 // Y == nullptr runs the state pre-sweep only (chunk-start states + final state).
@@ -247,10 +243,17 @@ int scan_tc_fwd_impl(const void* U, const float* M, const float* K, const void* 
   return rc;
 }
 
+size_t scan_tc_states_bytes(const ScanDims& d) {
+  return (size_t)d.batch * d.heads * ((d.T + L - 1) / L) * 64 * 128 * 2;
+}
+
 int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                 const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
-                const ScanDims& d, int io_dtype, int y_dtype, void*, size_t, cudaStream_t st) {
-  return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, nullptr, d, io_dtype, y_dtype, st);
+                void* states_out, const ScanDims& d, int io_dtype, int y_dtype, void*, size_t,
+                cudaStream_t st) {
+  // chunk states are only meaningful for the cases the tensor-core backward covers
+  if (Bprev || d.groups != d.heads) states_out = nullptr;
+  return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, states_out, d, io_dtype, y_dtype, st);
 }
 
 template <typename TIn, int NW>
@@ -266,7 +269,8 @@ static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
 // cover (grouped B/C, carried B_prev/U_prev, dY of another dtype or absent) take the exact
 // float32 sweeps.
 int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
-                const float* z0, const void* Bprev, const void* Uprev, const void* dY,
+                const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
+                const float* zfinal_in, const void* dY,
                 const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC, float* dinit,
                 void* dBprev, void* dUprev, const ScanDims& d, int io_dtype, int dy_dtype, void* ws,
                 size_t ws_bytes, cudaStream_t st) {
@@ -279,14 +283,20 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   const bool bf = io_dtype == SL_BF16;
   const uint64_t BH = (uint64_t)d.batch * d.heads;
   const int nC = (d.T + L - 1) / L;
-  float* zfinal = reinterpret_cast<float*>(w + lay.zfinal);
-  if (int e = scan_tc_fwd_impl(U, M, K, B, nullptr, z0, nullptr, nullptr, nullptr, zfinal, w + lay.states, d,
-                               io_dtype, SL_F32, st))
-    return e;
+  const float* zfinal = zfinal_in;
+  const void* states = states_in;
+  if (!states || !zfinal) {   // nothing saved by the forward: recompute with the state pre-sweep
+    float* zf = reinterpret_cast<float*>(w + lay.zfinal);
+    if (int e = scan_tc_fwd_impl(U, M, K, B, nullptr, z0, nullptr, nullptr, nullptr, zf, w + lay.states, d,
+                                 io_dtype, SL_F32, st))
+      return e;
+    zfinal = zf;
+    states = w + lay.states;
+  }
   TcBwdParams p{};
   if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BH, 64, bf) ||
       !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmZ, w + lay.states, 128, (uint64_t)nC * 64, BH, 64, bf))
+      !tc::make_tmap_3d(&p.tmZ, states, 128, (uint64_t)nC * 64, BH, 64, bf))
     return SL_ERR_LAUNCH_FAILED;
   p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal; p.dU = dU; p.dB = dB; p.dC = dC;
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);

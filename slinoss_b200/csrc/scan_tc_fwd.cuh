@@ -1,16 +1,20 @@
 // Forward kernel of the chunked scan on tcgen05 (included by scan_tc.cu inside its namespaces).
 //
-// NW = warps per TMEM lane quadrant.  The CTA has 4*NW warps; warp w works on TMEM lanes
-// 32*(w & 3) .. +31 (a hardware rule) and, inside every accumulator, on the column group
-// (w >> 2) of NW.  Thread (quad, cg, lane) therefore owns row 16*quad + (lane & 15), the
-// column half (lane >> 4) and 1/NW of that half's columns of every result matrix.
+// NW = warps per TMEM lane quadrant (2 or 4).  The CTA has 4*NW worker warps; warp w reads TMEM
+// lanes 32*(w & 3) .. +31 (a hardware rule) and, inside every accumulator, the column group
+// (w >> 2) of NW.  All MMAs have M = 64, whose rows live in lanes 0..15 of every quadrant, so in
+// the epilogues lane i < 16 of warp (quad, cg) owns row 16*quad + i and 1/NW of the columns;
+// the upper half-warp only takes part in the rotation pass.  Every tcgen05.mma costs the issuing
+// thread ~50 cycles whatever its N, so operands are laid out for few, wide instructions:
+// [K' ; Zv] is one 128-row B operand (scores and off-term in one MMA per k-step) and K'' is one
+// 128-column MN-major operand.
 //
 // STATES_ONLY: the state pre-sweep of the backward pass (no C, no scores, no Y).
 template <typename TIn, typename TY, bool STATES_ONLY, int NW>
 __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
   constexpr int NT = 128 * NW;  // worker threads; one more warp prepares the per-chunk scalars
-  constexpr int ZC = 64 / NW;   // state columns per thread (pairs stay inside a thread)
-  constexpr int SC = 32 / NW;   // score / output columns per thread
+  constexpr int ZC = 128 / NW;  // state columns per active thread (pairs stay inside a thread)
+  constexpr int SC = 64 / NW;   // score / output columns per active thread
   constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -23,7 +27,8 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool worker = warp < 4 * NW;     // the last warp only runs chunk_scalars one chunk ahead
   const int quad = warp & 3, cg = worker ? (warp >> 2) : 0;
-  const int row = 16 * quad + (lane & 15), hf = lane >> 4;   // epilogue identity
+  const int row = 16 * quad + (lane & 15);                   // epilogue identity
+  const bool act = worker && lane < 16;                      // rows of M = 64 accumulators
   const int rcol = tid & 15, rrow0 = tid >> 4;               // rotation identity
   const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
   const int bh = blockIdx.x, b = bh / p.heads, h = bh % p.heads;
@@ -48,23 +53,23 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
   auto issue_loads = [&](int c) {   // one thread
     uint8_t* st = smem + (c & 1) * STAGE;
     uint64_t* bar = &bar_tma[c & 1];
-    mbar_expect_tx(bar, STATES_ONLY ? 3 * TILE : STAGE);
+    mbar_expect_tx(bar, (STATES_ONLY ? 3 : 5) * TILE);
     tma_load_3d(st, &p.tmU, bar, 0, c * L, bh);
     tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bg);
-    tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bg);
+    tma_load_3d(st + 3 * TILE, &p.tmB, bar, 64, c * L, bg);
     if (!STATES_ONLY) {
-      tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bg);
-      tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bg);
+      tma_load_3d(st + 5 * TILE, &p.tmC, bar, 0, c * L, bg);
+      tma_load_3d(st + 6 * TILE, &p.tmC, bar, 64, c * L, bg);
     }
   };
   if (tid == 0) issue_loads(0);
 
   // ---- carried state, conjugated: zv[2j], zv[2j+1] = (re, -im) of column pair j of this thread ----
-  const int d0 = 64 * hf + cg * ZC;   // first state column of this thread
+  const int d0 = cg * ZC;             // first state column (0..127) of this thread
   float zv[ZC];
 #pragma unroll
   for (int j = 0; j < ZC; ++j) zv[j] = 0.f;
-  if (worker) {
+  if (act) {
     const TIn* Bp = reinterpret_cast<const TIn*>(p.Bprev);
     const TIn* Up = reinterpret_cast<const TIn*>(p.Uprev);
     float cr = 0.f, ci = 0.f, up = 0.f;
@@ -96,11 +101,15 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
     v.z = PK::pack(zv[8 * ch + 4], zv[8 * ch + 5]); v.w = PK::pack(zv[8 * ch + 6], zv[8 * ch + 7]);
     return v;
   };
-  auto store_zv_tile = [&]() {   // 16-bit copy of the state: rows p, K-major along d
-    uint8_t* zt = smem + OFF_ZV + hf * TILE;
+  // 16-bit copy of the state for chunk c: rows p, K-major along d, in the Zv slots of stage c & 1
+  // (directly below the K' rows, so that [K' ; Zv] is one 128-row operand)
+  auto store_zv_tile = [&](int c) {
+    uint8_t* stg = smem + (c & 1) * STAGE;
 #pragma unroll
-    for (int ch = 0; ch < ZC / 8; ++ch)
-      *reinterpret_cast<uint4*>(zt + sw128(row, cg * (ZC / 8) + ch)) = pack8(ch);
+    for (int ch = 0; ch < ZC / 8; ++ch) {
+      const int ci = d0 / 8 + ch;   // 16-byte chunk index along d (0..15)
+      *reinterpret_cast<uint4*>(stg + (2 + 2 * (ci >> 3)) * TILE + sw128(row, ci & 7)) = pack8(ch);
+    }
   };
   auto store_chunk_state = [&](int c) {   // conjugated form, 16-bit, row-major [p][128]
     if (!p.states16) return;
@@ -108,15 +117,14 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
 #pragma unroll
     for (int ch = 0; ch < ZC / 8; ++ch) *reinterpret_cast<uint4*>(dst + 8 * ch) = pack8(ch);
   };
-  if (worker) store_zv_tile();
-  else chunk_scalars(sc_tab, Mb, Kb, 0, T, lane);
+  if (act) store_zv_tile(0);
+  if (!worker) chunk_scalars(sc_tab, Mb, Kb, 0, T, lane);
   __syncthreads();
 
-  constexpr uint32_t ID_S = make_idesc(64, 32, PK::fmt, 0, 0);     // K-major x K-major
-  constexpr uint32_t ID_Y = make_idesc(64, 32, PK::fmt, 0, 1);     // K-major x MN-major
-  constexpr uint32_t ID_Z = make_idesc(64, 64, PK::fmt, 1, 1);     // MN-major x MN-major
-  const uint32_t aKPP = smem_u32(smem + OFF_KPP), aS = smem_u32(smem + OFF_S),
-                 aZV = smem_u32(smem + OFF_ZV);
+  constexpr uint32_t ID_S = make_idesc(64, 128, PK::fmt, 0, 0);    // K-major x K-major   [S | Yoff]
+  constexpr uint32_t ID_Y = make_idesc(64, 64, PK::fmt, 0, 1);     // K-major x MN-major  Ydiag
+  constexpr uint32_t ID_Z = make_idesc(64, 128, PK::fmt, 1, 1);    // MN-major x MN-major Inc
+  const uint32_t aKPP = smem_u32(smem + OFF_KPP), aS = smem_u32(smem + OFF_S);
   bool ok = true;
 #ifdef SL_TC_TIMING
 #define SL_TICK(i) if (bh == 0 && tid == 0 && c == 8) g_tc_timing[i] = clock64();
@@ -137,7 +145,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
       if (c + 1 < p.nchunks) chunk_scalars(sc_tab + ((c + 1) & 1) * (NSCAL * 64), Mb, Kb, t0 + L, T, lane);
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
-    store_chunk_state(c);
+    if (act) store_chunk_state(c);
     if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1)) { report_timeout(1); s_abort = 1; }
     bar_sync(1, NT);
     live = s_abort == 0;
@@ -146,8 +154,8 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
     // ---- rotation: C -> Q, B -> K' (both in place), K'' ; diagonal scores --------------------
     if (live) {
       const uint32_t half = rcol >> 3, ch = rcol & 7;
-      uint8_t* tB = st + TILE + half * TILE;
-      uint8_t* tC = st + 3 * TILE + half * TILE;
+      uint8_t* tB = st + (1 + 2 * half) * TILE;
+      uint8_t* tC = st + (5 + half) * TILE;
       uint8_t* tK = smem + OFF_KPP + half * TILE;
 #pragma unroll
       for (int k = 0; k < 64 / RSTEP; ++k) {
@@ -190,20 +198,12 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
       // ---- MMA group 1: scores and off-term --------------------------------------------------
       if (tid == 0 && live) {
         tc_fence_after_sync();
-        const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);
-        const uint64_t bC = make_desc(smem_u32(st + 3 * TILE), 16, 1024);
-        const uint64_t bZ = make_desc(aZV, 16, 1024);
+        const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);       // [K'_h ; Zv_h], h = k >> 2
+        const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t dS = tmem + ((16u * q) << 16), dO = dS + 32;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-            const uint64_t da = desc_adv(bC, ko);
-            umma(dS, da, desc_adv(bB, 4096 * q + ko), ID_S, k > 0);
-            umma(dO, da, desc_adv(bZ, 4096 * q + ko), ID_S, k > 0);
-          }
-        }
+        for (int k = 0; k < 8; ++k)
+          umma(tmem, desc_adv(bC, (k >> 2) * TILE + (k & 3) * 32),
+               desc_adv(bB, (k >> 2) * 2 * TILE + (k & 3) * 32), ID_S, k > 0);
         umma_commit(&bar_mma[0]);
         SL_TICK(3)
       }
@@ -216,6 +216,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
         uint32_t r[SC];
         tmem_ld<SC>(tmem + lane_base + cg * SC, r);
         tmem_ld_wait();
+        if (act) {
         const float lt = sc[row];
         const float dgv = s_diag[row];
         uint8_t* tS = smem + OFF_S;
@@ -227,15 +228,16 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
             float v2[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-              const int j = 8 * ch + 2 * e + q, s = 32 * hf + cg * SC + j;
+              const int j = 8 * ch + 2 * e + q, s = cg * SC + j;
               float v = __uint_as_float(r[j]) * __expf(fminf(lt - sc[s], 0.f));
               v = s < row ? v : (s == row ? dgv : 0.f);
               v2[q] = v;
             }
             w[e] = PK::pack(v2[0], v2[1]);
           }
-          *reinterpret_cast<uint4*>(tS + sw128(row, 4 * hf + cg * (SC / 8) + ch)) =
+          *reinterpret_cast<uint4*>(tS + sw128(row, cg * (SC / 8) + ch)) =
               make_uint4(w[0], w[1], w[2], w[3]);
+        }
         }
       }
       fence_async_smem();
@@ -252,13 +254,9 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
       const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
       const uint64_t bK = make_desc(aKPP, 8192, 1024);
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const uint32_t dY = tmem + ((16u * q) << 16) + 64, dZ = tmem + ((16u * q) << 16) + 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (!STATES_ONLY) umma(dY, desc_adv(bS, 32 * k), desc_adv(bU, 64 * q + 2048 * k), ID_Y, k > 0);
-          umma(dZ, desc_adv(bU, 2048 * k), desc_adv(bK, TILE * q + 2048 * k), ID_Z, k > 0);
-        }
+      for (int k = 0; k < 4; ++k) {
+        if (!STATES_ONLY) umma(tmem + 128, desc_adv(bS, 32 * k), desc_adv(bU, 2048 * k), ID_Y, k > 0);
+        umma(tmem + 192, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
       }
       umma_commit(&bar_mma[1]);
       SL_TICK(6)
@@ -270,12 +268,12 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
     // ---- output epilogue: y = Y_diag + exp(l_t) Y_off -----------------------------------------------
     if (!STATES_ONLY && live) {
       uint32_t yd[SC], yo[SC];
-      tmem_ld<SC>(tmem + lane_base + 64 + cg * SC, yd);
-      tmem_ld<SC>(tmem + lane_base + 32 + cg * SC, yo);
+      tmem_ld<SC>(tmem + lane_base + 128 + cg * SC, yd);
+      tmem_ld<SC>(tmem + lane_base + 64 + cg * SC, yo);
       tmem_ld_wait();
       const float et = sc[1 * 64 + row];
-      if (t0 + row < T) {
-        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf + cg * SC;
+      if (act && t0 + row < T) {
+        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + cg * SC;
         if constexpr (sizeof(TY) == 2) {
           using PY = Pack2<TY>;
 #pragma unroll
@@ -307,15 +305,17 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
     if (live) {
       const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
       uint32_t inc[ZC];
-      tmem_ld<ZC>(tmem + lane_base + 128 + cg * ZC, inc);
+      tmem_ld<ZC>(tmem + lane_base + 192 + cg * ZC, inc);
       tmem_ld_wait();
+      if (act) {
 #pragma unroll
-      for (int j = 0; j < ZC / 2; ++j) {
-        const float a = zv[2 * j], bq = zv[2 * j + 1];
-        zv[2 * j] = pr * a + pi * bq + __uint_as_float(inc[2 * j]);
-        zv[2 * j + 1] = pr * bq - pi * a + __uint_as_float(inc[2 * j + 1]);
+        for (int j = 0; j < ZC / 2; ++j) {
+          const float a = zv[2 * j], bq = zv[2 * j + 1];
+          zv[2 * j] = pr * a + pi * bq + __uint_as_float(inc[2 * j]);
+          zv[2 * j + 1] = pr * bq - pi * a + __uint_as_float(inc[2 * j + 1]);
+        }
+        store_zv_tile(c + 1);
       }
-      store_zv_tile();
     }
     SL_TICK(9)
     fence_async_smem();
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
     SL_TICK(10)
   }
 
-  if (ok && p.zfinal && worker) {
+  if (ok && p.zfinal && act) {
     float* dst = p.zfinal + ((size_t)bh * 64 + row) * 128 + d0;
 #pragma unroll
     for (int j = 0; j < ZC / 4; ++j)

@@ -124,17 +124,22 @@ def _prep(U, M, K, B, C, initial_states, B_prev, U_prev):
 
 
 class _ScanFn(torch.autograd.Function):
-    """Saves only the inputs; the backward kernels recompute what they need
-    (same saved set as slinoss/ops/v2x2ssd/cute/autograd.py:110-118)."""
+    """Saves the inputs (same saved set as slinoss/ops/v2x2ssd/cute/autograd.py:110-118)
+    and, optionally, the 16-bit chunk-start states of the tensor-core path, which spare the
+    backward its state pre-sweep at the price of one more (batch,heads,T/64,64,128) tensor."""
 
     @staticmethod
     def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, chunk_size, odtype,
-                return_state, path):
+                return_state, path, save_states):
         args = _prep(U, M, K, B, C, initial_states, B_prev, U_prev)
         y_dtype = odtype if odtype in _IO_DTYPES else torch.float32
-        Y, final = _C.scan_fwd(*args, chunk_size=chunk_size, y_dtype=y_dtype,
-                               want_final=return_state, path=path)
-        ctx.save_for_backward(*[a for a in args if a is not None])
+        out = _C.scan_fwd(*args, chunk_size=chunk_size, y_dtype=y_dtype, want_final=return_state,
+                          path=path, save_states=save_states)
+        Y, final = out[0], out[1]
+        states = out[2] if len(out) > 2 else None
+        ctx.has_saved_states = states is not None
+        extra = [states, final] if states is not None else []
+        ctx.save_for_backward(*[a for a in args if a is not None], *extra)
         ctx.present = [a is not None for a in args]
         ctx.in_dtypes = [None if x is None else x.dtype
                          for x in (U, M, K, B, C, initial_states, B_prev, U_prev)]
@@ -149,6 +154,7 @@ class _ScanFn(torch.autograd.Function):
     def backward(ctx, *grads):
         it = iter(ctx.saved_tensors)
         U, M, K, B, C, z0, B_prev, U_prev = [next(it) if p else None for p in ctx.present]
+        saved = (next(it), next(it)) if ctx.has_saved_states else None
         dY = grads[0]
         d_final = dB_last = dU_last = None
         if ctx.return_state:
@@ -162,7 +168,7 @@ class _ScanFn(torch.autograd.Function):
             if d_final is not None:
                 d_final = d_final.to(torch.float32).contiguous()
             out = list(_C.scan_bwd(U, M, K, B, C, z0, B_prev, U_prev, dY, d_final,
-                                   chunk_size=ctx.chunk_size, path=ctx.path))
+                                   chunk_size=ctx.chunk_size, path=ctx.path, saved=saved))
         if dB_last is not None:
             if out[3] is None:
                 out[3] = torch.zeros_like(B)
@@ -174,15 +180,19 @@ class _ScanFn(torch.autograd.Function):
         res = []
         for g, dt, need in zip(out, ctx.in_dtypes, ctx.needs_input_grad[:8]):
             res.append(g.to(dtype=dt) if (g is not None and dt is not None and need) else None)
-        return (*res, None, None, None, None)
+        return (*res, None, None, None, None, None)
 
 
 def v2x2ssd_cute(U, M, K, B, C, *, chunk_size, initial_states=None, B_prev=None, U_prev=None,
-                 compute_dtype=None, output_dtype=None, return_state=False, path="auto"):
+                 compute_dtype=None, output_dtype=None, return_state=False, path="auto",
+                 save_chunk_states=True):
     """GPU scan.  Returns ``Y`` or ``(Y, final_state, B_last, U_last)``.
 
     ``path`` selects the kernel family: "auto" (tensor cores when the shape and dtype
-    allow, else the exact float32 recurrence), "simt" or "tc"."""
+    allow, else the exact float32 recurrence), "simt" or "tc".  ``save_chunk_states``
+    (training only) keeps the tensor-core path's 16-bit chunk-start states for the
+    backward instead of recomputing them there; False saves only the inputs, like the
+    reference."""
     batch, heads, T, N, P = validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
     _C.require_cuda(U)
     if chunk_size <= 0:
@@ -197,7 +207,7 @@ def v2x2ssd_cute(U, M, K, B, C, *, chunk_size, initial_states=None, B_prev=None,
         t is not None and t.requires_grad for t in (U, M, K, B, C, initial_states, B_prev, U_prev))
     if needs_grad:
         return _ScanFn.apply(U, M, K, B, C, initial_states, B_prev, U_prev, int(chunk_size),
-                             odtype, bool(return_state), path)
+                             odtype, bool(return_state), path, bool(save_chunk_states))
     args = _prep(U, M, K, B, C, initial_states, B_prev, U_prev)
     y_dtype = odtype if odtype in _IO_DTYPES else torch.float32
     Y, final = _C.scan_fwd(*args, chunk_size=int(chunk_size), y_dtype=y_dtype,

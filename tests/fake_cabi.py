@@ -43,16 +43,18 @@ class FakeCABI:
 
     # ---- scan ---------------------------------------------------------------------------
     def scan_fwd(self, U, M, K, B, C, z0, B_prev, U_prev, *, chunk_size, y_dtype, want_final,
-                 path="auto"):
+                 path="auto", save_states=False):
         self.calls.append(("scan_fwd", dict(chunk_size=chunk_size, path=path, io=U.dtype,
                                             shapes=[tuple(t.shape) for t in (U, M, K, B, C)],
                                             has_state=z0 is not None, has_prev=B_prev is not None)))
         assert M.dtype == K.dtype == torch.float32 and B.dtype == C.dtype == U.dtype
         Y, fin, _, _ = scan_np.v2x2ssd(_n(U), _n(M), _n(K), _n(B), _n(C), chunk_size=chunk_size,
                                        initial_states=_n(z0), B_prev=_n(B_prev), U_prev=_n(U_prev))
-        return _t(Y, y_dtype), (_t(fin, torch.float32) if want_final else None)
+        out = (_t(Y, y_dtype), (_t(fin, torch.float32) if want_final else None))
+        return out + (None,) if save_states else out
 
-    def scan_bwd(self, U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *, chunk_size, path="auto"):
+    def scan_bwd(self, U, M, K, B, C, z0, B_prev, U_prev, dY, d_final, *, chunk_size, path="auto",
+                 saved=None):
         self.calls.append(("scan_bwd", dict(chunk_size=chunk_size, path=path)))
         dYn = _n(dY) if dY is not None else np.zeros(U.shape)
         g = scan_np.v2x2ssd_bwd(_n(U), _n(M), _n(K), _n(B), _n(C), dYn, d_final_state=_n(d_final),

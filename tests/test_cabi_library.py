@@ -49,18 +49,19 @@ def test_arguments_are_validated_before_any_launch(lib):
     call = lambda *a: lib.sl_v2x2ssd_fwd(*a)
     dims = (1, 2, 2, 4, 4, 2, 4)
     # missing U
-    assert call(null, p, p, p, p, null, null, null, p, null, *dims, 0, 0, 0, null, 0, null) == 1
+    assert call(null, p, p, p, p, null, null, null, p, null, null, *dims, 0, 0, 0, null, 0, null) == 1
     # only one of B_prev / U_prev
-    assert call(p, p, p, p, p, null, p, null, p, null, *dims, 0, 0, 0, null, 0, null) == 1
+    assert call(p, p, p, p, p, null, p, null, p, null, null, *dims, 0, 0, 0, null, 0, null) == 1
     # groups do not divide heads
-    assert call(p, p, p, p, p, null, null, null, p, null, 1, 3, 2, 4, 4, 2, 4, 0, 0, 0, null, 0, null) == 2
+    assert call(p, p, p, p, p, null, null, null, p, null, null, 1, 3, 2, 4, 4, 2, 4, 0, 0, 0, null, 0,
+                null) == 2
     # unknown dtype code
-    assert call(p, p, p, p, p, null, null, null, p, null, *dims, 7, 0, 0, null, 0, null) == 4
+    assert call(p, p, p, p, p, null, null, null, p, null, null, *dims, 7, 0, 0, null, 0, null) == 4
     # misaligned K
-    assert call(p, p, p + 4, p, p, null, null, null, p, null, *dims, 0, 0, 0, null, 0, null) == 3
+    assert call(p, p, p + 4, p, p, null, null, null, p, null, null, *dims, 0, 0, 0, null, 0, null) == 3
     # backward without a workspace
-    assert lib.sl_v2x2ssd_bwd(p, p, p, p, p, null, null, null, p, null, p, p, p, p, p, null, null,
-                              null, *dims, 0, 0, 1, null, 0, null) == 5
+    assert lib.sl_v2x2ssd_bwd(p, p, p, p, p, null, null, null, null, null, p, null, p, p, p, p, p, null,
+                              null, null, *dims, 0, 0, 1, null, 0, null) == 5
     # decode / tail / scanprep null checks
     assert lib.sl_v2x2ssd_decode(null, p, p, p, p, p, null, null, p, p, 1, 2, 2, 4, 2, 0, 0, null) == 1
     assert lib.sl_mixer_tail_fwd(null, p, 8, null, null, p, 1e-5, p, 1, 2, 4, 4, 0, null) == 1

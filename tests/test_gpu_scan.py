@@ -301,3 +301,14 @@ def test_backward_tensor_core_agrees_with_exact_path_at_strong_decay():
         res[path] = torch.autograd.grad(Y, lv, dY)
     for name, a, e in zip("UMKBC", res["tc"], res["simt"]):
         assert rel(a, e) <= 2e-2, (name, rel(a, e))
+
+
+def test_saved_chunk_states_and_recompute_give_the_same_gradients():
+    case = make_scan_case(2, 2, 300, 64, 64, dtype=torch.bfloat16, seed=2, with_init=True).to(DEV)
+    res = []
+    for keep in (True, False):
+        lv = [x.clone().requires_grad_(True) for x in (*case.tensors(), case.initial_states)]
+        Y = v2x2ssd_cute(*lv[:5], chunk_size=64, initial_states=lv[5], path="tc", save_chunk_states=keep)
+        res.append(torch.autograd.grad(Y, lv, case.dY))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
