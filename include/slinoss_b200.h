@@ -84,6 +84,10 @@ SL_API int sl_device_status(void);
 /* Static, human readable text of a status code. */
 SL_API const char* sl_status_string(int status);
 
+/* The CUDA runtime's text for the error behind the most recent SL_ERR_LAUNCH_FAILED of this
+ * process ("no error" if there was none).  Diagnostics only; no reference counterpart. */
+SL_API const char* sl_last_cuda_error(void);
+
 /* Scratch bytes a call of the given kind needs for these dimensions
  * (0 when none).  `path` is one of SL_PATH_*.  For SL_WS_SCANPREP_BWD and
  * SL_WS_TAIL_BWD only batch, heads, groups, T, P, N are read. */

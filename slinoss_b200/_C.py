@@ -43,6 +43,7 @@ _PROTOTYPES = {
     "sl_kernel_launches": (ctypes.c_ulonglong, []),
     "sl_device_status": (c_int, []),
     "sl_status_string": (ctypes.c_char_p, [c_int]),
+    "sl_last_cuda_error": (ctypes.c_char_p, []),
     "sl_workspace_bytes": (c_size_t, [c_int] * 10),
     "sl_v2x2ssd_fwd": (c_int, [_P] * 11 + [c_int] * 10 + [_P, c_size_t, _P]),
     "sl_v2x2ssd_bwd": (c_int, [_P] * 20 + [c_int] * 10 + [_P, c_size_t, _P]),
@@ -97,6 +98,8 @@ def device_status() -> int:
 def check(status: int, what: str) -> None:
     if status != 0:
         text = lib().sl_status_string(status).decode()
+        if status == 6:   # SL_ERR_LAUNCH_FAILED: add the CUDA runtime's own words
+            text += f" ({lib().sl_last_cuda_error().decode()})"
         raise RuntimeError(f"slinoss_b200.{what} failed with status {status}: {text}")
 
 

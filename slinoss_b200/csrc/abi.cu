@@ -7,6 +7,8 @@ namespace sl {
 
 static std::atomic<unsigned long long> g_launches{0};
 void note_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+static std::atomic<int> g_cuda_error{0};
+void note_cuda_error(int code) { g_cuda_error.store(code, std::memory_order_relaxed); }
 
 // Implemented in scan_tc.cu (tcgen05 / TMEM chunked path).
 bool scan_tc_supported(const ScanDims& d, int io_dtype);
@@ -62,6 +64,10 @@ extern "C" SL_API void sl_tune_tc_warps(int nw) { sl::scan_tc_set_warps(nw); }
 
 extern "C" int sl_device_status(void) { return sl::scan_tc_device_status(); }
 
+extern "C" const char* sl_last_cuda_error(void) {
+  return cudaGetErrorString((cudaError_t)sl::g_cuda_error.load(std::memory_order_relaxed));
+}
+
 extern "C" const char* sl_status_string(int status) {
   switch (status) {
     case SL_OK: return "ok";
@@ -106,6 +112,7 @@ extern "C" int sl_v2x2ssd_fwd(const void* U, const float* M, const float* K, con
   if (int e = check_scan(U, M, K, B, C, B_prev, U_prev, d, io_dtype)) return e;
   if (!Y) return SL_ERR_NULL_POINTER;
   if (!dtype_ok(y_dtype)) return SL_ERR_UNSUPPORTED;
+  if (!aligned(Y, 16) || (chunk_states && !aligned(chunk_states, 16))) return SL_ERR_BAD_ALIGNMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == SL_PATH_TC && !scan_tc_supported(d, io_dtype)) return SL_ERR_UNSUPPORTED;
   if (use_tc(path, d, io_dtype))
@@ -130,6 +137,8 @@ extern "C" int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, con
   const ScanDims d{batch, heads, groups, T, P, N, chunk};
   if (int e = check_scan(U, M, K, B, C, B_prev, U_prev, d, io_dtype)) return e;
   if (!dU || !dM || !dK || !dB || !dC) return SL_ERR_NULL_POINTER;
+  if (!aligned(dU, 16) || !aligned(dB, 16) || !aligned(dC, 16) || (dY && !aligned(dY, 16)))
+    return SL_ERR_BAD_ALIGNMENT;
   if (!dtype_ok(dy_dtype)) return SL_ERR_UNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == SL_PATH_TC && !scan_tc_supported(d, io_dtype)) return SL_ERR_UNSUPPORTED;

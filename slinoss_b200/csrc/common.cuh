@@ -55,8 +55,14 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // process-wide count of kernels this library has launched (see sl_kernel_launches)
 void note_launches(int n);
 
+// remembers the CUDA error behind the last SL_ERR_LAUNCH_FAILED (see sl_last_cuda_error)
+void note_cuda_error(int code);
+
 inline int launch_status() {
-  return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_LAUNCH_FAILED;
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return SL_OK;
+  note_cuda_error((int)e);
+  return SL_ERR_LAUNCH_FAILED;
 }
 
 // Dispatch a callable templated on the io element type.

@@ -50,11 +50,13 @@ constexpr uint32_t TMEM_COLS = 512;       // S 0..63 | Yoff 64..127 | Ydiag 128.
 
 __device__ int g_tc_status = 0;
 #ifdef SL_TC_TIMING
-__device__ long long g_tc_timing[16];
+__device__ long long g_tc_timing[24];
+__device__ int g_tc_exp;   // timing experiments only
 #endif           // first device-side error (bounded wait expired)
 
 struct alignas(64) TcFwdParams {
   CUtensorMap tmU, tmB, tmC;
+  CUtensorMap tmY, tmS;   // 16-bit output and chunk-state tensors (TMA stores); unused ones stay zero
   const float* M;
   const float* K;
   const float* z0;
@@ -206,7 +208,7 @@ static int launch_tc_fwd_nw(const TcFwdParams& p, int grid, cudaStream_t st) {
   auto k = scan_tc_fwd_kernel<TIn, TY, STATES_ONLY, NW>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess)
     return SL_ERR_LAUNCH_FAILED;
-  k<<<grid, 128 * NW + 32, SMEM_BYTES, st>>>(p);
+  k<<<grid, 128 * NW + 64, SMEM_BYTES, st>>>(p);
   note_launches(1);
   return launch_status();
 }
@@ -230,6 +232,10 @@ int scan_tc_fwd_impl(const void* U, const float* M, const float* K, const void* 
   p.M = M; p.K = K; p.z0 = z0; p.Bprev = Bprev; p.Uprev = Uprev; p.Y = Y; p.zfinal = zfinal;
   p.states16 = states16;
   p.heads = d.heads; p.groups = d.groups; p.T = d.T; p.nchunks = (d.T + L - 1) / L;
+  if (Y && y_dtype != SL_F32 && !tc::make_tmap_3d(&p.tmY, Y, 64, d.T, BH, 64, y_dtype == SL_BF16))
+    return SL_ERR_LAUNCH_FAILED;
+  if (states16 && !tc::make_tmap_3d(&p.tmS, states16, 128, (uint64_t)p.nchunks * 64, BH, 64, bf))
+    return SL_ERR_LAUNCH_FAILED;
   const int grid = (int)BH;
   int rc = SL_ERR_UNSUPPORTED;
   if (!Y) {
@@ -261,7 +267,7 @@ static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
   auto k = scan_tc_bwd_kernel<TIn, NW>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
     return SL_ERR_LAUNCH_FAILED;
-  k<<<grid, 128 * NW + 32, B_SMEM_BYTES, st>>>(p);
+  k<<<grid, 128 * NW + 64, B_SMEM_BYTES, st>>>(p);
   return launch_status();
 }
 
@@ -296,9 +302,11 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   TcBwdParams p{};
   if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BH, 64, bf) ||
       !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmZ, states, 128, (uint64_t)nC * 64, BH, 64, bf))
+      !tc::make_tmap_3d(&p.tmZ, states, 128, (uint64_t)nC * 64, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmdU, dU, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdB, dB, 128, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmdC, dC, 128, d.T, BH, 64, bf))
     return SL_ERR_LAUNCH_FAILED;
-  p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal; p.dU = dU; p.dB = dB; p.dC = dC;
+  p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal;
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
   p.dkcd = reinterpret_cast<float2*>(w + lay.dkcd); p.anchor = reinterpret_cast<float2*>(w + lay.anchor);
   p.dinit = dinit; p.T = d.T; p.nchunks = nC;
@@ -319,8 +327,11 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
 }
 
 #ifdef SL_TC_TIMING
+extern "C" __attribute__((visibility("default"))) void sl_dbg_set_exp(int v) {
+  cudaMemcpyToSymbol(g_tc_exp, &v, sizeof(int));
+}
 extern "C" __attribute__((visibility("default"))) void sl_dbg_timing(long long* out) {
-  cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(long long) * 16);
+  cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(long long) * 24);
 }
 #endif
 

@@ -31,11 +31,11 @@ constexpr uint32_t B_TMEM_COLS = 512;
 
 struct alignas(64) TcBwdParams {
   CUtensorMap tmU, tmB, tmC, tmdY, tmZ;
+  CUtensorMap tmdU, tmdB, tmdC;   // outputs, written with TMA stores from shared memory
   const float* M;
   const float* K;
   const float* dfinal;   // (BH, 64, 128) or null
   const float* zfinal;   // forward final state (pre-sweep), read when dfinal is given
-  void *dU, *dB, *dC;
   float2 *dg, *sterm, *dkcd, *anchor;   // per token / per chunk scalars (workspace)
   float* dinit;          // (BH, 64, 128) adjoint of the carried start state, or null
   int T, nchunks;
@@ -46,15 +46,16 @@ struct alignas(64) TcBwdParams {
 //  s_acc (after row 15): partial sums per (column group, half): re/im of <q,dq>, re/im of sum conj(b) dX
 // NW = warps per TMEM lane quadrant (same thread-to-data mapping as the forward kernel).
 template <typename TIn, int NW>
-__global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
-  constexpr int NT = 128 * NW;               // worker threads; one more warp prepares the scalars
+__global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
+  constexpr int NT = 128 * NW;               // worker threads; two more warps: scalars, TMA + MMA issue
   constexpr int ZC = 64 / NW;                // columns per thread of a 64-wide accumulator half
   constexpr int SC = 32 / NW;                // columns per thread of a 32-wide accumulator half
   constexpr int PC = ZC > 32 ? 32 : ZC;      // columns handled per TMEM load in the wide epilogues
   constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ uint64_t bar_tma[2], bar_mma[2];
+  __shared__ uint64_t bar_tma[2], bar_mma[5];   // bar_mma: group 1 | dX | dQ | dU | dZ
+  __shared__ uint64_t bar_st[3];               // output tiles staged in shared memory: dB | dC | dU
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ float s_red[8 * NW + 2];
@@ -77,11 +78,13 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
 
   if (tid == 0) {
     mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
-    mbar_init(&bar_mma[0], 1); mbar_init(&bar_mma[1], 1);
+    for (int i = 0; i < 5; ++i) mbar_init(&bar_mma[i], 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_st[i], 4 * NW);   // one arrival per worker warp
     fence_barrier_init();
     s_abort = 0;
     tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
     tma_prefetch_desc(&p.tmdY); tma_prefetch_desc(&p.tmZ);
+    tma_prefetch_desc(&p.tmdU); tma_prefetch_desc(&p.tmdB); tma_prefetch_desc(&p.tmdC);
   }
   if (warp == 0) tmem_alloc(&tmem_slot, B_TMEM_COLS);
   tc_fence_before_sync();
@@ -137,7 +140,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
       if (tid == 0) p.anchor[(size_t)bh * nC + nC - 1] = make_float2(sr, si);
     }
   }
-  if (!worker) chunk_scalars(sc_tab, Mb, Kb, (nC - 1) * L, T, lane);
+  if (warp == 4 * NW) chunk_scalars(sc_tab, Mb, Kb, (nC - 1) * L, T, lane);
   __syncthreads();
 
   constexpr uint32_t ID_KK32 = make_idesc(64, 32, PK::fmt, 0, 0);
@@ -150,8 +153,10 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
   bool ok = true;
 #ifdef SL_TC_TIMING
 #define SL_TOCK(i) if (bh == 0 && tid == 0 && it == 8) g_tc_timing[i] = clock64();
+#define SL_TOCK_MMA(i) if (bh == 0 && it == 8) g_tc_timing[i] = clock64();
 #else
 #define SL_TOCK(i)
+#define SL_TOCK_MMA(i)
 #endif
 
   for (int it = 0; it < nC && ok; ++it) {
@@ -160,17 +165,128 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
     uint8_t* st = smem + (it & 1) * B_STAGE;
     uint8_t *tU = st, *tB = st + TILE, *tC = st + 3 * TILE, *tDY = st + 5 * TILE, *tZ = st + 6 * TILE;
     float* sc = sc_tab + (it & 1) * (11 * 64);
-    if (tid == 0 && it + 1 < nC) issue_loads(c - 1, it + 1);
-    if (!worker) {
-      // scalars of the next (earlier) chunk; this warp meets the others only at the barrier
-      // that ends the iteration
+    if (warp == 4 * NW) {
+      // scalars of the next (earlier) chunk; this warp meets the others only at the barrier that
+      // ends the iteration
+      // (it starts after the workers' first passes: global loads issued while every worker warp
+      // bursts shared-memory traffic at the top of the iteration stalled the whole SM for about a
+      // DRAM round trip)
+      bar_sync(2, NT + 64);
       if (it + 1 < nC) chunk_scalars(sc_tab + ((it + 1) & 1) * (11 * 64), Mb, Kb, t0 - L, T, lane);
+    } else if (!worker) {
+      // Issue warp: TMA loads of the next (earlier) chunk, then the MMAs of this chunk.  It meets
+      // the workers at the two "operands ready" barriers (id 2) and at the end of the iteration.
+      // K-major (kX) and MN-major (mX) base descriptors of every operand tile of this chunk
+      const uint64_t kQ = make_desc(aQ, 16, 1024), mQ = make_desc(aQ, 8192, 1024);
+      const uint64_t kKP = make_desc(aKP, 16, 1024), mKP = make_desc(aKP, 8192, 1024);
+      const uint64_t kU = make_desc(smem_u32(tU), 16, 1024);
+      const uint64_t kDY = make_desc(smem_u32(tDY), 16, 1024), mDY = make_desc(smem_u32(tDY), 8192, 1024);
+      const uint64_t mZ = make_desc(smem_u32(tZ), 8192, 1024);
+      const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
+      const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024);
+      const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
+      bar_sync(2, NT + 64);   // Q, K', dYoff, dWv written; U, dY, Zv landed
+      if (lane == 0 && s_abort == 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t dP_ = tmem + ((16u * q) << 16), dS_ = dP_ + 32;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+            umma(dP_, desc_adv(kQ, ko), desc_adv(kKP, 4096 * q + ko), ID_KK32, k > 0);
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma(dS_, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
+        }
+        umma_commit(&bar_mma[0]);
+        SL_TOCK_MMA(6)
+        if (it + 1 < nC) {   // next chunk's tiles, after the workers' burst
+          tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
+          issue_loads(c - 1, it + 1);
+        }
+        SL_TOCK_MMA(18)
+      }
+      __syncwarp();
+      bar_sync(3, NT + 32);   // Pdec, dP written
+      if (lane == 0 && s_abort == 0) {
+        tc_fence_after_sync();
+        // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
+        // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma(lb + 192, desc_adv(mDP, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
+            umma(lb + 256, desc_adv(kU, 32 * k), desc_adv(mDW, TILE * q + 2048 * k), ID_KM64, k > 0);
+          }
+        }
+        umma_commit(&bar_mma[1]);
+        // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
+        // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma(lb + 64, desc_adv(kDP, 32 * k), desc_adv(mKP, TILE * q + 2048 * k), ID_KM64, k > 0);
+            umma(lb + 128, desc_adv(kDY, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
+          }
+        }
+        umma_commit(&bar_mma[2]);
+        // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
+        // dUb[s][p] = sum_d K'[s][d] dWv[p][d]       A: K' K-major, B: dWv K-major rows p (N = 32 half)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma(lb + 320, desc_adv(mPD, 2048 * k), desc_adv(mDY, 64 * q + 2048 * k), ID_MM32, k > 0);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+            umma(lb + 352, desc_adv(kKP, ko), desc_adv(kDW, 4096 * q + ko), ID_KK32, k > 0);
+          }
+        }
+        umma_commit(&bar_mma[3]);
+        // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma(lb + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
+        }
+        umma_commit(&bar_mma[4]);
+        SL_TOCK_MMA(9)
+        // Output tiles: the workers overwrite dead operand tiles of this stage in place (C with dB,
+        // B with dC, dY with dU) and signal; one TMA store per tile writes full 128-byte rows.
+        if (mbar_wait(&bar_st[0], it & 1)) {
+          tma_store_3d(&p.tmdB, tC, 0, t0, bh); tma_store_3d(&p.tmdB, tC + TILE, 64, t0, bh);
+          tma_store_commit();
+        } else { report_timeout(17); s_abort = 1; }
+        if (mbar_wait(&bar_st[1], it & 1)) {
+          tma_store_3d(&p.tmdC, tB, 0, t0, bh); tma_store_3d(&p.tmdC, tB + TILE, 64, t0, bh);
+          tma_store_commit();
+        } else { report_timeout(18); s_abort = 1; }
+        if (mbar_wait(&bar_st[2], it & 1)) {
+          tma_store_3d(&p.tmdU, tDY, 0, t0, bh);
+          tma_store_commit();
+        } else { report_timeout(19); s_abort = 1; }
+      }
+      __syncwarp();
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
     // ---- dWv tile: dz rotated by the unit phase of Pi_end:  (a,b) -> (ur a - ui b, ui a + ur b) ----
     {
       const float ur = sc[10 * 64 + 2], ui = sc[10 * 64 + 3];
+#ifdef SL_TC_TIMING
+      if (bh == 0 && tid == 0 && it == 8) { g_tc_timing[19] = clock64() + (ur + ui == 123.f); }
+#endif
       if (tid < 64) sw[0 * 64 + tid] = __expf(fminf(sc[63] - sc[tid], 0.f));
+      SL_TOCK(20)
       uint8_t* dw = smem + B_OFF_DW + hf * TILE;
 #pragma unroll
       for (int ch = 0; ch < ZC / 8; ++ch) {
@@ -185,10 +301,9 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
         *reinterpret_cast<uint4*>(dw + sw128(row, d0 / 8 + ch)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(11); s_abort = 1; }
+    SL_TOCK(16)
+    if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(11); s_abort = 1; live = false; }
     SL_TOCK(1)
-    bar_sync(1, NT);
-    live = s_abort == 0;
     SL_TOCK(2)
 
     // ---- pass 1 over dY, U: sigma_t = <dy_t, u_t>, dYoff = e^{l_t} dY -------------------------------
@@ -220,7 +335,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
     // ---- pass 2 over B, C: Q, K', diagonal pieces ------------------------------------------------------
     if (live) {
       const uint32_t half = rcol >> 3, ch = rcol & 7;
-#pragma unroll
+#pragma unroll 1
       for (int k = 0; k < 64 / RSTEP; ++k) {
         const int r = rrow0 + RSTEP * k;
         const uint32_t off = half * TILE + sw128(r, ch);
@@ -255,37 +370,12 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
     }
     SL_TOCK(4)
     fence_async_smem();
-    bar_sync(1, NT);
+    tc_fence_before_sync();
+    bar_sync(2, NT + 64);
+    live = s_abort == 0;
     SL_TOCK(5)
 
-    // K-major (kX) and MN-major (mX) base descriptors of every operand tile of this chunk
-    const uint64_t kQ = make_desc(aQ, 16, 1024), mQ = make_desc(aQ, 8192, 1024);
-    const uint64_t kKP = make_desc(aKP, 16, 1024), mKP = make_desc(aKP, 8192, 1024);
-    const uint64_t kU = make_desc(smem_u32(tU), 16, 1024);
-    const uint64_t kDY = make_desc(smem_u32(tDY), 16, 1024), mDY = make_desc(smem_u32(tDY), 8192, 1024);
-    const uint64_t mZ = make_desc(smem_u32(tZ), 8192, 1024);
-    const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
-    const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024);
-    const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
-
-    // ---- MMA group 1: P~ = Q K'^T, dS = dY U^T ----------------------------------------------------------
-    if (tid == 0 && live) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const uint32_t dP_ = tmem + ((16u * q) << 16), dS_ = dP_ + 32;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          umma(dP_, desc_adv(kQ, ko), desc_adv(kKP, 4096 * q + ko), ID_KK32, k > 0);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma(dS_, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
-      }
-      umma_commit(&bar_mma[0]);
-      SL_TOCK(6)
-    }
+    // ---- MMA group 1 (issued by the look-ahead warp): P~ = Q K'^T, dS = dY U^T ------------------------
     if (live && !mbar_wait(&bar_mma[0], it & 1)) { report_timeout(12); s_abort = 1; live = false; }
     tc_fence_after_sync();
     SL_TOCK(7)
@@ -320,127 +410,99 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
     }
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(1, NT);
+    bar_sync(3, NT + 32);
     live = s_abort == 0;
     SL_TOCK(8)
 
-    // ---- MMA group 2 ----------------------------------------------------------------------------------------
-    if (tid == 0 && live) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t mk = 2048 * k, kk = 32 * k;
-          // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
-          umma(lb + 64, desc_adv(kDP, kk), desc_adv(mKP, TILE * q + mk), ID_KM64, k > 0);
-          // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
-          umma(lb + 128, desc_adv(kDY, kk), desc_adv(mZ, TILE * q + mk), ID_KM64, k > 0);
-          // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
-          umma(lb + 192, desc_adv(mDP, mk), desc_adv(mQ, TILE * q + mk), ID_MM64, k > 0);
-          // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
-          umma(lb + 256, desc_adv(kU, kk), desc_adv(mDW, TILE * q + mk), ID_KM64, k > 0);
-          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
-          umma(lb + 320, desc_adv(mPD, mk), desc_adv(mDY, 64 * q + mk), ID_MM32, k > 0);
-          // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
-          umma(lb + 384, desc_adv(mDYO, mk), desc_adv(mQ, TILE * q + mk), ID_MM64, k > 0);
-        }
-        // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p (N = 32 half)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          umma(lb + 352, desc_adv(kKP, ko), desc_adv(kDW, 4096 * q + ko), ID_KK32, k > 0);
-        }
-      }
-      umma_commit(&bar_mma[1]);
-      SL_TOCK(9)
-    }
+    // ---- MMA group 2 (issued by the look-ahead warp, one commit per accumulator set) ------------------
     if (live && !mbar_wait(&bar_mma[1], it & 1)) { report_timeout(13); s_abort = 1; live = false; }
     tc_fence_after_sync();
     SL_TOCK(10)
 
-    const bool tok_valid = t0 + row < T;
     const float sig = sw[1 * 64 + row];
+    // ---- epilogue 3 (first): dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
+    if (live) {
+      const float ee = sw[0 * 64 + row], wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
+      const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];
+      float rr = 0.f, ri = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < ZC / 8; ++ch) {
+        uint32_t xa[8], xb[8];
+        tmem_ld<8>(tmem + lane_base + 192 + d0 + 8 * ch, xa);
+        tmem_ld<8>(tmem + lane_base + 256 + d0 + 8 * ch, xb);
+        tmem_ld_wait();
+        const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
+        const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
+        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 2 * e;
+          const float ga = __uint_as_float(xa[j]) + ee * __uint_as_float(xb[j]);
+          const float gb = __uint_as_float(xa[j + 1]) + ee * __uint_as_float(xb[j + 1]);
+          const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
+          // dX = ga - i gb ; R += conj(b) dX
+          rr += bb.x * ga - bb.y * gb;
+          ri += -bb.x * gb - bb.y * ga;
+          // db = conj(w) dX + sigma conj(kc) c
+          const float dbr = wr * ga - wi * gb + (skr * cc.x + ski * cc.y);
+          const float dbi = -wr * gb - wi * ga + (skr * cc.y - ski * cc.x);
+          o[e] = PK::pack(dbr, dbi);
+        }
+        *reinterpret_cast<uint4*>(tC + off) = make_uint4(o[0], o[1], o[2], o[3]);   // dB over C, in place
+      }
+      s_acc[(2 * 8 + 2 * cg + hf) * 64 + row] = rr;
+      s_acc[(3 * 8 + 2 * cg + hf) * 64 + row] = ri;
+    }
+    // the tile is complete once every worker warp has arrived; the issue warp then stores it
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bar_st[0]);
+    SL_TOCK(11)
+    if (live && !mbar_wait(&bar_mma[2], it & 1)) { report_timeout(14); s_abort = 1; live = false; }
+    tc_fence_after_sync();
     // ---- epilogue 2: dQ -> dC, <q,dq> ------------------------------------------------------------------
     if (live) {
       const float et = sc[1 * 64 + row], phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
       const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
       float ar = 0.f, ai = 0.f;
-      TIn* dst = reinterpret_cast<TIn*>(p.dC) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf + d0;
-#pragma unroll
-      for (int part = 0; part < ZC / PC; ++part) {
-        uint32_t qa[PC], qb[PC];
-        tmem_ld<PC>(tmem + lane_base + 64 + d0 + PC * part, qa);
-        tmem_ld<PC>(tmem + lane_base + 128 + d0 + PC * part, qb);
+#pragma unroll 1
+      for (int ch = 0; ch < ZC / 8; ++ch) {   // a real loop: keeps the kernel's code inside the instruction cache
+        uint32_t qa[8], qb[8];
+        tmem_ld<8>(tmem + lane_base + 64 + d0 + 8 * ch, qa);
+        tmem_ld<8>(tmem + lane_base + 128 + d0 + 8 * ch, qb);
         tmem_ld_wait();
+        const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
+        const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
+        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t o[4];
 #pragma unroll
-        for (int ch = 0; ch < PC / 8; ++ch) {
-          const uint32_t off = hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch);
-          const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
-          const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
-          const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-          uint32_t o[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = 8 * ch + 2 * e;
-            const float dqr = __uint_as_float(qa[j]) + et * __uint_as_float(qb[j]);
-            const float dqi = __uint_as_float(qa[j + 1]) + et * __uint_as_float(qb[j + 1]);
-            const float2 q = PK::unpack(qw[e]), bb = PK::unpack(bw[e]);
-            ar += q.x * dqr + q.y * dqi;          // conj(q) dq
-            ai += q.x * dqi - q.y * dqr;
-            // dc = conj(dq) phi + sigma kc b
-            const float dcr = dqr * phr + dqi * phi + (skr * bb.x - ski * bb.y);
-            const float dci = dqr * phi - dqi * phr + (skr * bb.y + ski * bb.x);
-            o[e] = PK::pack(dcr, dci);
-          }
-          if (tok_valid) *reinterpret_cast<uint4*>(dst + PC * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int e = 0; e < 4; ++e) {
+          const int j = 2 * e;
+          const float dqr = __uint_as_float(qa[j]) + et * __uint_as_float(qb[j]);
+          const float dqi = __uint_as_float(qa[j + 1]) + et * __uint_as_float(qb[j + 1]);
+          const float2 q = PK::unpack(qw[e]), bb = PK::unpack(bw[e]);
+          ar += q.x * dqr + q.y * dqi;          // conj(q) dq
+          ai += q.x * dqi - q.y * dqr;
+          // dc = conj(dq) phi + sigma kc b
+          const float dcr = dqr * phr + dqi * phi + (skr * bb.x - ski * bb.y);
+          const float dci = dqr * phi - dqi * phr + (skr * bb.y + ski * bb.x);
+          o[e] = PK::pack(dcr, dci);
         }
+        *reinterpret_cast<uint4*>(tB + off) = make_uint4(o[0], o[1], o[2], o[3]);   // dC over B, in place
       }
       s_acc[(0 * 8 + 2 * cg + hf) * 64 + row] = ar;
       s_acc[(1 * 8 + 2 * cg + hf) * 64 + row] = ai;
     }
-    SL_TOCK(11)
-    // ---- epilogue 3: dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
-    if (live) {
-      const float ee = sw[0 * 64 + row], wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
-      const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];
-      float rr = 0.f, ri = 0.f;
-      TIn* dst = reinterpret_cast<TIn*>(p.dB) + ((size_t)bh * T + t0 + row) * 128 + 64 * hf + d0;
-#pragma unroll
-      for (int part = 0; part < ZC / PC; ++part) {
-        uint32_t xa[PC], xb[PC];
-        tmem_ld<PC>(tmem + lane_base + 192 + d0 + PC * part, xa);
-        tmem_ld<PC>(tmem + lane_base + 256 + d0 + PC * part, xb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int ch = 0; ch < PC / 8; ++ch) {
-          const uint32_t off = hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch);
-          const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
-          const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
-          const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-          uint32_t o[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = 8 * ch + 2 * e;
-            const float ga = __uint_as_float(xa[j]) + ee * __uint_as_float(xb[j]);
-            const float gb = __uint_as_float(xa[j + 1]) + ee * __uint_as_float(xb[j + 1]);
-            const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
-            // dX = ga - i gb ; R += conj(b) dX
-            rr += bb.x * ga - bb.y * gb;
-            ri += -bb.x * gb - bb.y * ga;
-            // db = conj(w) dX + sigma conj(kc) c
-            const float dbr = wr * ga - wi * gb + (skr * cc.x + ski * cc.y);
-            const float dbi = -wr * gb - wi * ga + (skr * cc.y - ski * cc.x);
-            o[e] = PK::pack(dbr, dbi);
-          }
-          if (tok_valid) *reinterpret_cast<uint4*>(dst + PC * part + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-      }
-      s_acc[(2 * 8 + 2 * cg + hf) * 64 + row] = rr;
-      s_acc[(3 * 8 + 2 * cg + hf) * 64 + row] = ri;
-    }
+    // the tile is complete once every worker warp has arrived; the issue warp then stores it
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bar_st[1]);
     SL_TOCK(12)
+    if (live && !mbar_wait(&bar_mma[3], it & 1)) { report_timeout(15); s_abort = 1; live = false; }
+    tc_fence_after_sync();
     // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
     if (live) {
       uint32_t ua[SC], ub[SC];
@@ -448,10 +510,10 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
       tmem_ld<SC>(tmem + lane_base + 352 + cg * SC, ub);
       tmem_ld_wait();
       const float ee = sw[0 * 64 + row], dgv = sw[2 * 64 + row];
-      TIn* dst = reinterpret_cast<TIn*>(p.dU) + ((size_t)bh * T + t0 + row) * 64 + 32 * hf + cg * SC;
 #pragma unroll
       for (int ch = 0; ch < SC / 8; ++ch) {
-        const uint4 dv = *reinterpret_cast<const uint4*>(tDY + sw128(row, 4 * hf + cg * (SC / 8) + ch));
+        const uint32_t off = sw128(row, 4 * hf + cg * (SC / 8) + ch);
+        const uint4 dv = *reinterpret_cast<const uint4*>(tDY + off);
         const uint32_t dw_[4] = {dv.x, dv.y, dv.z, dv.w};
         uint32_t o[4];
 #pragma unroll
@@ -461,10 +523,16 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
           o[e] = PK::pack(__uint_as_float(ua[j]) + ee * __uint_as_float(ub[j]) + dgv * d2.x,
                           __uint_as_float(ua[j + 1]) + ee * __uint_as_float(ub[j + 1]) + dgv * d2.y);
         }
-        if (tok_valid) *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(tDY + off) = make_uint4(o[0], o[1], o[2], o[3]);   // dU over dY, in place
       }
     }
+    // the tile is complete once every worker warp has arrived; the issue warp then stores it
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bar_st[2]);
     SL_TOCK(13)
+    if (live && !mbar_wait(&bar_mma[4], it & 1)) { report_timeout(16); s_abort = 1; live = false; }
+    tc_fence_after_sync();
     // ---- epilogue 5: dz <- e^{l_end} dWv + dZ ; anchor of the boundary below ----------------------------------
     {
       const float em = sc[1 * 64 + 63];
@@ -531,6 +599,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_bwd_kernel(const __g
   if (!ok && tid == 0) {
     for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);
   }
+  if (warp == 4 * NW + 1 && lane == 0) tma_store_wait_all();   // output stores of the issue thread
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, B_TMEM_COLS);

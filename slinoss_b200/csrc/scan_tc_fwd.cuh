@@ -11,21 +11,23 @@
 //
 // STATES_ONLY: the state pre-sweep of the backward pass (no C, no scores, no Y).
 template <typename TIn, typename TY, bool STATES_ONLY, int NW>
-__global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
-  constexpr int NT = 128 * NW;  // worker threads; one more warp prepares the per-chunk scalars
+__global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
+  constexpr int NT = 128 * NW;  // worker threads; two more warps: per-chunk scalars, TMA + MMA issue
   constexpr int ZC = 128 / NW;  // state columns per active thread (pairs stay inside a thread)
   constexpr int SC = 64 / NW;   // score / output columns per active thread
   constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ uint64_t bar_tma[2], bar_mma[2];
+  __shared__ uint64_t bar_tma[2], bar_mma[3];   // bar_mma: [S|Yoff] | Inc | Ydiag
+  __shared__ uint64_t bar_st;                  // Y tile staged in shared memory (16-bit outputs)
+  constexpr bool Y_TMA = !STATES_ONLY && sizeof(TY) == 2;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   float* sc_tab = reinterpret_cast<float*>(smem + OFF_SCAL);   // two tables: chunk parity
   using PK = Pack2<TIn>;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool worker = warp < 4 * NW;     // the last warp only runs chunk_scalars one chunk ahead
+  const bool worker = warp < 4 * NW;     // warp 4 NW runs chunk_scalars one chunk ahead, warp 4 NW + 1 issues
   const int quad = warp & 3, cg = worker ? (warp >> 2) : 0;
   const int row = 16 * quad + (lane & 15);                   // epilogue identity
   const bool act = worker && lane < 16;                      // rows of M = 64 accumulators
@@ -39,10 +41,13 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
 
   if (tid == 0) {
     mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
-    mbar_init(&bar_mma[0], 1); mbar_init(&bar_mma[1], 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_mma[i], 1);
+    mbar_init(&bar_st, 4 * NW);   // one arrival per worker warp
     fence_barrier_init();
     s_abort = 0;
     tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
+    if (Y_TMA) tma_prefetch_desc(&p.tmY);
+    if (p.states16) tma_prefetch_desc(&p.tmS);
   }
   if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
   tc_fence_before_sync();
@@ -111,14 +116,8 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
       *reinterpret_cast<uint4*>(stg + (2 + 2 * (ci >> 3)) * TILE + sw128(row, ci & 7)) = pack8(ch);
     }
   };
-  auto store_chunk_state = [&](int c) {   // conjugated form, 16-bit, row-major [p][128]
-    if (!p.states16) return;
-    TIn* dst = reinterpret_cast<TIn*>(p.states16) + (((size_t)bh * p.nchunks + c) * 64 + row) * 128 + d0;
-#pragma unroll
-    for (int ch = 0; ch < ZC / 8; ++ch) *reinterpret_cast<uint4*>(dst + 8 * ch) = pack8(ch);
-  };
   if (act) store_zv_tile(0);
-  if (!worker) chunk_scalars(sc_tab, Mb, Kb, 0, T, lane);
+  if (warp == 4 * NW) chunk_scalars(sc_tab, Mb, Kb, 0, T, lane);
   __syncthreads();
 
   constexpr uint32_t ID_S = make_idesc(64, 128, PK::fmt, 0, 0);    // K-major x K-major   [S | Yoff]
@@ -128,8 +127,10 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
   bool ok = true;
 #ifdef SL_TC_TIMING
 #define SL_TICK(i) if (bh == 0 && tid == 0 && c == 8) g_tc_timing[i] = clock64();
+#define SL_TICK_MMA(i) if (bh == 0 && c == 8) g_tc_timing[i] = clock64();
 #else
 #define SL_TICK(i)
+#define SL_TICK_MMA(i)
 #endif
 
   for (int c = 0; c < p.nchunks && ok; ++c) {
@@ -138,17 +139,69 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
     uint8_t* st = smem + (c & 1) * STAGE;
     float* sc = sc_tab + (c & 1) * (NSCAL * 64);
     float* s_diag = sc + 11 * 64;
-    if (tid == 0 && c + 1 < p.nchunks) issue_loads(c + 1);
-    if (!worker) {
-      // scalars of the NEXT chunk; this warp only meets the others at the barrier that ends the
-      // iteration, so its global loads and scans overlap the whole chunk
+    if (warp == 4 * NW) {
+      // scalars of the NEXT chunk, started once the workers are through the rotation pass (global
+      // loads issued during the workers' shared-memory burst at the top of the iteration stalled
+      // the whole SM for about a DRAM round trip)
+      bar_sync(2, NT + 64);
       if (c + 1 < p.nchunks) chunk_scalars(sc_tab + ((c + 1) & 1) * (NSCAL * 64), Mb, Kb, t0 + L, T, lane);
+    } else if (!worker) {
+      // Issue warp: the MMAs of this chunk and the TMA loads of the NEXT one.  It meets the workers
+      // at the "operands ready" barriers (id 2) and at the end of the iteration.
+      const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
+      // the stores of the previous chunk (its Y tile, its state tiles) must have read shared memory
+      // before the workers overwrite the state tiles and before the stage is refilled below
+      if (lane == 0) tma_store_wait_read();
+      bar_sync(2, NT + 64);   // Q, K', K'' written; U landed; Zv tile stored by the previous chunk
+      if (lane == 0 && s_abort == 0) {
+        tc_fence_after_sync();
+        if (!STATES_ONLY) {
+          // scores and off-term: [S | Yoff] = Q [K' ; Zv]^T
+          const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);       // [K'_h ; Zv_h], h = k >> 2
+          const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma(tmem, desc_adv(bC, (k >> 2) * TILE + (k & 3) * 32),
+                 desc_adv(bB, (k >> 2) * 2 * TILE + (k & 3) * 32), ID_S, k > 0);
+          umma_commit(&bar_mma[0]);
+        }
+        // Inc = U^T K''
+        const uint64_t bK = make_desc(aKPP, 8192, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma(tmem + 192, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
+        umma_commit(&bar_mma[1]);
+        SL_TICK_MMA(3)
+        if (c + 1 < p.nchunks) issue_loads(c + 1);   // next chunk's tiles, after the workers' burst
+        if (p.states16) {   // the 16-bit state tile of this chunk is exactly what the backward wants
+          tma_store_3d(&p.tmS, st + 2 * TILE, 0, c * 64, bh);
+          tma_store_3d(&p.tmS, st + 4 * TILE, 64, c * 64, bh);
+          tma_store_commit();
+        }
+      }
+      __syncwarp();
+      if (!STATES_ONLY) {
+        bar_sync(3, NT + 32);   // S tile written
+        if (lane == 0 && s_abort == 0) {
+          tc_fence_after_sync();
+          const uint64_t bS = make_desc(aS, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)   // Y_diag = S U
+            umma(tmem + 128, desc_adv(bS, 32 * k), desc_adv(bU, 2048 * k), ID_Y, k > 0);
+          umma_commit(&bar_mma[2]);
+          SL_TICK_MMA(6)
+          if (Y_TMA) {   // the workers put the 16-bit Y tile over the (dead) U tile and signal
+            if (mbar_wait(&bar_st, c & 1)) {
+              tma_store_3d(&p.tmY, st, 0, t0, bh);
+              tma_store_commit();
+            } else { report_timeout(5); s_abort = 1; }
+          }
+        }
+        __syncwarp();
+      }
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
-    if (act) store_chunk_state(c);
-    if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1)) { report_timeout(1); s_abort = 1; }
-    bar_sync(1, NT);
-    live = s_abort == 0;
+    if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1)) { report_timeout(1); s_abort = 1; live = false; }
     SL_TICK(1)
 
     // ---- rotation: C -> Q, B -> K' (both in place), K'' ; diagonal scores --------------------
@@ -191,22 +244,13 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
       }
     }
     fence_async_smem();
-    bar_sync(1, NT);
+    tc_fence_before_sync();
+    bar_sync(2, NT + 64);
+    live = s_abort == 0;
     SL_TICK(2)
 
     if (!STATES_ONLY) {
-      // ---- MMA group 1: scores and off-term --------------------------------------------------
-      if (tid == 0 && live) {
-        tc_fence_after_sync();
-        const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);       // [K'_h ; Zv_h], h = k >> 2
-        const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma(tmem, desc_adv(bC, (k >> 2) * TILE + (k & 3) * 32),
-               desc_adv(bB, (k >> 2) * 2 * TILE + (k & 3) * 32), ID_S, k > 0);
-        umma_commit(&bar_mma[0]);
-        SL_TICK(3)
-      }
+      // ---- [S | Yoff] and Inc MMAs are issued by the look-ahead warp --------------------------------
       if (live && !mbar_wait(&bar_mma[0], c & 1)) { report_timeout(2); s_abort = 1; live = false; }
       tc_fence_after_sync();
       SL_TICK(4)
@@ -242,65 +286,15 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
       }
       fence_async_smem();
       tc_fence_before_sync();
-      bar_sync(1, NT);
+      bar_sync(3, NT + 32);   // the issue warp now issues Y_diag = S U
       live = s_abort == 0;
       SL_TICK(5)
     }
 
-    // ---- MMA group 2: Y_diag = S U, Inc = U^T K'' --------------------------------------------------
-    if (tid == 0 && live) {
-      tc_fence_after_sync();
-      const uint64_t bS = make_desc(aS, 16, 1024);
-      const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
-      const uint64_t bK = make_desc(aKPP, 8192, 1024);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (!STATES_ONLY) umma(tmem + 128, desc_adv(bS, 32 * k), desc_adv(bU, 2048 * k), ID_Y, k > 0);
-        umma(tmem + 192, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
-      }
-      umma_commit(&bar_mma[1]);
-      SL_TICK(6)
-    }
+    // ---- state update first (Inc does not depend on the scores), the output epilogue after it ------
     if (live && !mbar_wait(&bar_mma[1], c & 1)) { report_timeout(3); s_abort = 1; live = false; }
     tc_fence_after_sync();
     SL_TICK(7)
-
-    // ---- output epilogue: y = Y_diag + exp(l_t) Y_off -----------------------------------------------
-    if (!STATES_ONLY && live) {
-      uint32_t yd[SC], yo[SC];
-      tmem_ld<SC>(tmem + lane_base + 128 + cg * SC, yd);
-      tmem_ld<SC>(tmem + lane_base + 64 + cg * SC, yo);
-      tmem_ld_wait();
-      const float et = sc[1 * 64 + row];
-      if (act && t0 + row < T) {
-        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + cg * SC;
-        if constexpr (sizeof(TY) == 2) {
-          using PY = Pack2<TY>;
-#pragma unroll
-          for (int v = 0; v < SC / 8; ++v) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 8 * v + 2 * e;
-              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
-                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
-            }
-            *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        } else {
-#pragma unroll
-          for (int v = 0; v < SC / 4; ++v) {
-            float4 o;
-            o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
-            o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
-            o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
-            o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
-          }
-        }
-      }
-    }
-    SL_TICK(8)
     // ---- state update: zv = conj(Pi_end) zv + Inc ---------------------------------------------------
     if (live) {
       const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
@@ -316,6 +310,51 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
         }
         store_zv_tile(c + 1);
       }
+    }
+    SL_TICK(8)
+    if (!STATES_ONLY && live && !mbar_wait(&bar_mma[2], c & 1)) { report_timeout(4); s_abort = 1; live = false; }
+    tc_fence_after_sync();
+    // ---- output epilogue: y = Y_diag + exp(l_t) Y_off -----------------------------------------------
+    if (!STATES_ONLY && live) {
+      uint32_t yd[SC], yo[SC];
+      tmem_ld<SC>(tmem + lane_base + 128 + cg * SC, yd);
+      tmem_ld<SC>(tmem + lane_base + 64 + cg * SC, yo);
+      tmem_ld_wait();
+      const float et = sc[1 * 64 + row];
+      if constexpr (sizeof(TY) == 2) {
+        if (act) {   // into the U tile (dead once Y_diag and Inc are done); rows beyond T are clipped by the store
+          using PY = Pack2<TY>;
+#pragma unroll
+          for (int v = 0; v < SC / 8; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = 8 * v + 2 * e;
+              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
+                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
+            }
+            *reinterpret_cast<uint4*>(st + sw128(row, cg * (SC / 8) + v)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      } else if (act && t0 + row < T) {
+        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + cg * SC;
+        {
+#pragma unroll
+          for (int v = 0; v < SC / 4; ++v) {
+            float4 o;
+            o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
+            o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
+            o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
+            o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
+          }
+        }
+      }
+    }
+    if (Y_TMA) {   // the Y tile is complete once every worker warp has arrived
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_st);
     }
     SL_TICK(9)
     fence_async_smem();
@@ -337,6 +376,7 @@ __global__ void __launch_bounds__(128 * NW + 32, 1) scan_tc_fwd_kernel(const __g
   if (!ok && tid == 0) {
     for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);   // bounded; best effort drain
   }
+  if (warp == 4 * NW + 1 && lane == 0) tma_store_wait_all();   // Y / state stores of the issue thread
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
