@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ uint64_t bar_tma[2], bar_mma[5];   // bar_mma: group 1 | dX | dQ | dU | dZ
+  __shared__ uint64_t bar_tma[2], bar_mma[5];   // bar_mma: P~,dS | dX | dQ | dU | dZ (all earlier MMAs)
   __shared__ uint64_t bar_st[3];               // output tiles staged in shared memory: dB | dC | dU
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -185,23 +185,51 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
       const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024);
       const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
-      bar_sync(2, NT + 64);   // Q, K', dYoff, dWv written; U, dY, Zv landed
+      // MMAs on raw tiles go out as soon as the stage has landed, those on rotated tiles after the
+      // workers' passes, and only the three products of the masked tiles (dP, Pdec) wait for epilogue 1.
+      if (lane == 0 && s_abort == 0) {
+        if (mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              // dS[t][s] = sum_p dY[t][p] U[s][p]          A: dY K-major, B: U K-major rows s (N = 32 half)
+              umma(lb + 32, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
+              // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
+              umma(lb + 128, desc_adv(kDY, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
+            }
+          }
+        } else { report_timeout(20); s_abort = 1; }
+      }
+      __syncwarp();
+      bar_sync(2, NT + 64);   // Q, K', dYoff, dWv written
       if (lane == 0 && s_abort == 0) {
         tc_fence_after_sync();
+        // P~[t][s] = sum_d Q[t][d] K'[s][d]              A: Q K-major, B: K' K-major rows s (N = 32 half)
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const uint32_t dP_ = tmem + ((16u * q) << 16), dS_ = dP_ + 32;
+          const uint32_t dP_ = tmem + ((16u * q) << 16);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
             umma(dP_, desc_adv(kQ, ko), desc_adv(kKP, 4096 * q + ko), ID_KK32, k > 0);
           }
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma(dS_, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
         }
-        umma_commit(&bar_mma[0]);
+        umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
         SL_TOCK_MMA(6)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
+            umma(lb + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
+            // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
+            umma(lb + 256, desc_adv(kU, 32 * k), desc_adv(mDW, TILE * q + 2048 * k), ID_KM64, k > 0);
+          }
+        }
         if (it + 1 < nC) {   // next chunk's tiles, after the workers' burst
           tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
           issue_loads(c - 1, it + 1);
@@ -212,53 +240,41 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       bar_sync(3, NT + 32);   // Pdec, dP written
       if (lane == 0 && s_abort == 0) {
         tc_fence_after_sync();
-        // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
-        // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
+          // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
           const uint32_t lb = tmem + ((16u * q) << 16);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 4; ++k)
             umma(lb + 192, desc_adv(mDP, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
-            umma(lb + 256, desc_adv(kU, 32 * k), desc_adv(mDW, TILE * q + 2048 * k), ID_KM64, k > 0);
-          }
         }
-        umma_commit(&bar_mma[1]);
-        // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
-        // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
+        umma_commit(&bar_mma[1]);   // dX
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
+          // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
           const uint32_t lb = tmem + ((16u * q) << 16);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 4; ++k)
             umma(lb + 64, desc_adv(kDP, 32 * k), desc_adv(mKP, TILE * q + 2048 * k), ID_KM64, k > 0);
-            umma(lb + 128, desc_adv(kDY, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
-          }
         }
-        umma_commit(&bar_mma[2]);
-        // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
-        // dUb[s][p] = sum_d K'[s][d] dWv[p][d]       A: K' K-major, B: dWv K-major rows p (N = 32 half)
+        umma_commit(&bar_mma[2]);   // dQ
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
+          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
           const uint32_t lb = tmem + ((16u * q) << 16);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma(lb + 320, desc_adv(mPD, 2048 * k), desc_adv(mDY, 64 * q + 2048 * k), ID_MM32, k > 0);
+          // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p (N = 32 half)
+          // (does not depend on epilogue 1, but issuing it earlier would hold this warp back from
+          // the barrier the workers are waiting at)
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
             umma(lb + 352, desc_adv(kKP, ko), desc_adv(kDW, 4096 * q + ko), ID_KK32, k > 0);
           }
         }
-        umma_commit(&bar_mma[3]);
-        // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma(lb + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
-        }
+        umma_commit(&bar_mma[3]);   // dU
         umma_commit(&bar_mma[4]);
         SL_TOCK_MMA(9)
         // Output tiles: the workers overwrite dead operand tiles of this stage in place (C with dB,
@@ -272,6 +288,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           tma_store_commit();
         } else { report_timeout(18); s_abort = 1; }
         if (mbar_wait(&bar_st[2], it & 1)) {
+#ifdef SL_TC_TIMING
+          if (g_tc_exp != 2)
+#endif
           tma_store_3d(&p.tmdU, tDY, 0, t0, bh);
           tma_store_commit();
         } else { report_timeout(19); s_abort = 1; }
@@ -562,6 +581,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       }
       float sr, si;
       block_sum2(ar, ai, sr, si);   // contains two barriers: also orders the table writes above
+      // the proxy fence for this iteration's shared-memory accesses goes BEFORE the global stores
+      // below (the code after them touches no tile)
+      fence_async_smem();
       if (tid == 0 && c > 0) p.anchor[(size_t)bh * nC + c - 1] = make_float2(sr, si);
     }
     SL_TOCK(14)
@@ -581,7 +603,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       const float sg = sw[1 * 64 + t];
       p.dkcd[o] = make_float2(sg * sw[3 * 64 + t], sg * sw[4 * 64 + t]);
     }
-    fence_async_smem();
     tc_fence_before_sync();
     }  // worker
     __syncthreads();
