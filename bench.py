@@ -12,9 +12,12 @@ JSON line:
                         ranks) with inputs resident in HBM, through the C ABI launchers
   e2e                   the same step through the public op with HOST (pinned) buffers:
                         host->device copies of all inputs and device->host copies of Y and
-                        all gradients are inside the timed region
-  roofline              algorithmic bytes of fwd+bwd / measured step time vs the measured
-                        HBM copy bandwidth of this pool (MEASURED_PEAKS.json)
+                        all gradients are inside the timed region (the batch is fed in slices on
+                        three streams so that the two copy directions and the kernels overlap)
+  roofline              the dominant kernel (the backward sweep): its algorithmic bytes / its
+                        CUDA-event time vs the measured HBM copy bandwidth of this pool
+                        (MEASURED_PEAKS.json); "step" and "fwd" give the same figure for the
+                        whole step and for the forward kernel
   cpu_baseline          the C/OpenMP port of the reference's sequential scan (oracle/),
                         timed on the host cores on a bounded sample (N=1, rank 0 only)
 
@@ -41,6 +44,10 @@ sys.path.insert(0, str(ROOT))
 CFG = dict(batch=8, heads=16, T=4096, P=64, N=64, chunk=64)
 METRIC = "v2x2ssd fwd+bwd tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the backward sweep at this exact
+# workload, from the committed ncu capture (a profiler figure, not measured live by this script)
+NCU_TRAFFIC_BWD_BYTES = 549_827_328 + 309_716_480
+NCU_TRAFFIC_SOURCE = "profiles/scan_tc_fwd_bwd_config1.md (ncu --set full, one launch)"
 
 
 def algorithmic_bytes(c) -> dict:
@@ -77,7 +84,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -189,7 +196,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    from slinoss_b200 import _C
+    from slinoss_b200 import _C, shard
     from slinoss_b200.ops.v2x2ssd import v2x2ssd_cute
     from slinoss_b200.synthetic import make_scan_case
 
@@ -197,7 +204,7 @@ def main():
         _C.lib().sl_tune_tc_warps(args.tc_warps)
     c = CFG
     case_h = make_scan_case(c["batch"], c["heads"], c["T"], c["P"], c["N"], dtype=torch.bfloat16,
-                            seed=rank)
+                            seed=shard.rank_seed(0, rank))
     case = case_h.to(dev)
     U, M, K, B, C, dY = case.U, case.M, case.K, case.B, case.C, case.dY
 
@@ -248,29 +255,48 @@ def main():
         bwd_ms += e1.elapsed_time(e2)
     fwd_ms /= min(args.steps, 5)
     bwd_ms /= min(args.steps, 5)
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public op with host buffers --------------------------------
+    # The batch is fed in slices; host->device copies, the op (forward + autograd backward) and
+    # device->host copies run on three streams, so the two PCIe directions and the kernels
+    # overlap.  Every step moves ALL inputs in and ALL results (Y and the five gradients) out.
     pin = lambda t: t.pin_memory()
     h_in = [pin(t) for t in (case_h.U, case_h.M, case_h.K, case_h.B, case_h.C, case_h.dY)]
     h2d = sum(t.numel() * t.element_size() for t in h_in)
     d_in = [torch.empty_like(t, device=dev) for t in h_in]
-    h_out = None
-    d2h = 0
+    n_slices = c["batch"]   # one batch entry per slice: short pipeline fill and drain
+    bs = c["batch"] // n_slices
+    out_shapes = [(case_h.U.shape, torch.bfloat16), (case_h.U.shape, torch.bfloat16),
+                  (case_h.M.shape, torch.float32), (case_h.K.shape, torch.float32),
+                  (case_h.B.shape, torch.bfloat16), (case_h.C.shape, torch.bfloat16)]   # Y, dU, dM, dK, dB, dC
+    h_out = [torch.empty(s, dtype=dt).pin_memory() for s, dt in out_shapes]
+    d2h = sum(t.numel() * t.element_size() for t in h_out)
+    s_in, s_op, s_out = (torch.cuda.Stream(dev) for _ in range(3))
+    main_stream = torch.cuda.current_stream(dev)
 
     def step_e2e():
-        nonlocal h_out, d2h
-        for d, h in zip(d_in, h_in):
-            d.copy_(h, non_blocking=True)
-        leaves = [t.requires_grad_(True) for t in (x.detach() for x in d_in[:5])]
-        Y = v2x2ssd_cute(*leaves, chunk_size=c["chunk"], path=args.path)
-        grads = torch.autograd.grad(Y, leaves, d_in[5])
-        outs = (Y.detach(), *grads)
-        if h_out is None:
-            h_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-            d2h = sum(t.numel() * t.element_size() for t in h_out)
-        for h, o in zip(h_out, outs):
-            h.copy_(o, non_blocking=True)
+        for s in (s_in, s_op, s_out):
+            s.wait_stream(main_stream)
+        for i in range(n_slices):
+            sl = slice(i * bs, (i + 1) * bs)
+            with torch.cuda.stream(s_in):
+                for d, h in zip(d_in, h_in):
+                    d[sl].copy_(h[sl], non_blocking=True)
+                ev_in = torch.cuda.Event(); ev_in.record(s_in)
+            with torch.cuda.stream(s_op):
+                s_op.wait_event(ev_in)
+                leaves = [d[sl].detach().requires_grad_(True) for d in d_in[:5]]
+                Y = v2x2ssd_cute(*leaves, chunk_size=c["chunk"], path=args.path)
+                grads = torch.autograd.grad(Y, leaves, d_in[5][sl])
+                outs = (Y.detach(), *grads)
+                ev_op = torch.cuda.Event(); ev_op.record(s_op)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_op)
+                for h, o in zip(h_out, outs):
+                    o.record_stream(s_out)
+                    h[sl].copy_(o, non_blocking=True)
+        for s in (s_in, s_op, s_out):
+            main_stream.wait_stream(s)
 
     e2e_steps = max(2, min(args.steps, 5))
     for _ in range(2):
@@ -282,17 +308,19 @@ def main():
     t_end.record()
     barrier()
     e2e_ms = t_start.elapsed_time(t_end)
+    clocks = sampler.stop() if rank == 0 else None   # sampled over the device-timed and the end-to-end loops
 
-    times = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, fwd_ms, bwd_ms = times.tolist()
+    # the job is as slow as its slowest rank: MAX over ranks of every device-timed figure
+    total_ms, e2e_ms, fwd_ms, bwd_ms = (shard.reduce_step_ms(v, dev) for v in (total_ms, e2e_ms, fwd_ms, bwd_ms))
     if rank == 0:
         tokens_step = world * c["batch"] * c["T"]
         ms_step = total_ms / args.steps
         ab = algorithmic_bytes(c)
         peak, peak_kind = measured_peak()
         achieved = ab["total"] / (ms_step * 1e-3) / 1e9
+        bwd_gbs = ab["bwd"] / (bwd_ms * 1e-3) / 1e9
+        full_tc = args.path != "simt" and not args.small
+        traffic = NCU_TRAFFIC_BWD_BYTES if full_tc else None
         line = {
             "metric": METRIC, "value": tokens_step / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -302,14 +330,16 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": launches_timed,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
-                         "scope": "whole fwd+bwd step (all kernels); algorithmic bytes "
-                                  f"{ab['total']} per step",
-                         "fwd": {"ms": fwd_ms, "achieved": ab["fwd"] / (fwd_ms * 1e-3) / 1e9,
-                                 "frac": ab["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak},
-                         "bwd": {"ms": bwd_ms, "achieved": ab["bwd"] / (bwd_ms * 1e-3) / 1e9,
-                                 "frac": ab["bwd"] / (bwd_ms * 1e-3) / 1e9 / peak}},
+            "roofline": {"bound": "hbm", "kernel": "backward sweep (scan_tc_bwd_kernel + its scalar finish)",
+                         "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
+                         "traffic": traffic, "traffic_source": NCU_TRAFFIC_SOURCE if traffic else None,
+                         "peak_source": peak_kind, "algorithmic_bytes": ab["bwd"], "ms": bwd_ms,
+                         "share_of_step": bwd_ms / (fwd_ms + bwd_ms),
+                         "step": {"ms": ms_step, "algorithmic_bytes": ab["total"], "achieved": achieved,
+                                  "frac": achieved / peak},
+                         "fwd": {"ms": fwd_ms, "algorithmic_bytes": ab["fwd"],
+                                 "achieved": ab["fwd"] / (fwd_ms * 1e-3) / 1e9,
+                                 "frac": ab["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak}},
             "clocks": clocks,
             "kernel_path": args.path,
         }

@@ -1,0 +1,135 @@
+"""The N > 1 path on CPU: two ``gloo`` ranks, one process each.
+
+The scan shards by batch with no data-path collective; what a multi-GPU job adds is the
+host plumbing of ``slinoss_b200.shard`` (who owns which streams, MAX-over-ranks timing,
+SUM-over-ranks throughput) and, when the mixer is trained data parallel, the averaging of
+the replicated weights' gradients.  Each rank runs the package's real host code above the
+C ABI with the oracle-backed launchers of tests/fake_cabi.py underneath.
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from slinoss_b200 import shard
+
+WORLD = 2
+
+
+class _Patch:
+    """The one method of pytest's monkeypatch that FakeCABI.install uses."""
+
+    @staticmethod
+    def setattr(obj, name, value):
+        setattr(obj, name, value)
+
+
+def _init(rank, store_path):
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=WORLD)
+    torch.manual_seed(0)
+    torch.set_num_threads(1)
+    from tests.fake_cabi import FakeCABI
+    return FakeCABI().install(_Patch)
+
+
+def _rel(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+
+
+# ---------------------------------------------------------------------------------------
+def _scan_worker(rank, store_path, out_path):
+    _init(rank, store_path)
+    from oracle import scan_np
+    from slinoss_b200.ops.v2x2ssd import v2x2ssd_cute
+    from slinoss_b200.synthetic import make_scan_case
+    try:
+        full = make_scan_case(4, 2, 40, 4, 4, seed=3)            # the same bits on every rank
+        mine = shard.shard_batch([*full.tensors(), full.dY], dist.get_world_size(), rank)
+        leaves = [t.clone().requires_grad_(True) for t in mine[:5]]
+        Y = v2x2ssd_cute(*leaves, chunk_size=16)
+        grads = torch.autograd.grad(Y, leaves, mine[5])
+        # whole-job bookkeeping: rank r pretends its step took (r + 1) ms
+        units = mine[0].shape[0] * mine[0].shape[2]
+        per_s, total_units, max_ms = shard.job_throughput(units, float(rank + 1))
+        gathered = [None] * dist.get_world_size()
+        dist.all_gather_object(gathered, [Y.detach().numpy()] + [g.numpy() for g in grads])
+        if rank == 0:
+            n = lambda t: t.double().numpy()
+            want = scan_np.v2x2ssd(*[n(t) for t in full.tensors()], chunk_size=16)
+            wg = scan_np.v2x2ssd_bwd(*[n(t) for t in full.tensors()], n(full.dY))
+            got = [np.concatenate([g[i] for g in gathered], axis=0) for i in range(6)]
+            errs = [_rel(got[0], want[0])] + [_rel(got[1 + i], wg[k]) for i, k in enumerate("UMKBC")]
+            np.savez(out_path, errs=np.array(errs), per_s=per_s, total_units=total_units, max_ms=max_ms)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_own_disjoint_scan_shards_and_need_no_collective(tmp_path):
+    store, out = tmp_path / "store", tmp_path / "out.npz"
+    mp.spawn(_scan_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
+    r = np.load(out)
+    assert r["errs"].max() <= 1e-5, r["errs"]                  # float32 casts of a float64 oracle
+    assert int(r["total_units"]) == 4 * 40                       # SUM over ranks of batch x T
+    assert float(r["max_ms"]) == 2.0                             # MAX over ranks
+    assert abs(float(r["per_s"]) - 160 / 2e-3) < 1e-6
+
+
+# ---------------------------------------------------------------------------------------
+def _mixer_worker(rank, store_path, out_path):
+    _init(rank, store_path)
+    import slinoss_b200 as sb
+    try:
+        torch.manual_seed(11)
+        mixer = sb.SLinOSSMixer(16, d_state=8, expand=2, d_head=8, d_conv=4, chunk_size=8)
+        x = torch.randn(4, 12, 16)
+        w = torch.randn(4, 12, 16)
+
+        def grads_of(xb, wb):
+            mixer.zero_grad(set_to_none=True)
+            (mixer(xb) * wb).mean().backward()
+            return [p.grad.clone() for p in mixer.parameters()]
+
+        full = grads_of(x, w)                                    # single-process answer
+        xs, ws = shard.shard_batch([x, w], dist.get_world_size(), rank)
+        local = grads_of(xs, ws)
+        shard.allreduce_mean_(local)
+        errs = [_rel(a.numpy(), b.numpy()) for a, b in zip(local, full)]
+        if rank == 0:
+            np.savez(out_path, errs=np.array(errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_average_the_mixer_weight_gradients(tmp_path):
+    store, out = tmp_path / "store", tmp_path / "out.npz"
+    mp.spawn(_mixer_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
+    assert np.load(out)["errs"].max() <= 2e-5
+
+
+# ---------------------------------------------------------------------------------------
+def test_shard_bounds_cover_the_units_once():
+    for n in (0, 1, 7, 8, 33):
+        for world in (1, 2, 3, 8):
+            spans = [shard.shard_bounds(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [hi - lo for lo, hi in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard.shard_bounds(4, 2, 2)
+
+
+def test_single_process_meaning_without_a_group():
+    assert shard.world_size() == 1 and shard.rank() == 0
+    assert shard.reduce_step_ms(3.5) == 3.5
+    assert shard.job_throughput(100, 2.0) == (100 / 2e-3, 100, 2.0)
+    g = [torch.ones(3), None]
+    shard.allreduce_mean_(g)
+    assert torch.equal(g[0], torch.ones(3))
+    assert shard.rank_seed(5, 0) != shard.rank_seed(5, 1)
