@@ -171,11 +171,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       // (it starts after the workers' first passes: global loads issued while every worker warp
       // bursts shared-memory traffic at the top of the iteration stalled the whole SM for about a
       // DRAM round trip)
-      bar_sync(2, NT + 64);
+      bar_sync(2, NT + 64);   // the workers only arrive here (bar_arrive): they never wait for this warp
       if (it + 1 < nC) chunk_scalars(sc_tab + ((it + 1) & 1) * (11 * 64), Mb, Kb, t0 - L, T, lane);
     } else if (!worker) {
-      // Issue warp: TMA loads of the next (earlier) chunk, then the MMAs of this chunk.  It meets
-      // the workers at the two "operands ready" barriers (id 2) and at the end of the iteration.
+      // Issue warp (one lane): every MMA of this chunk, the TMA loads of the next (earlier) chunk and
+      // the TMA stores of this chunk's outputs.  The workers never wait for this warp, only for the
+      // commit barriers of the products they read: they arrive on named barriers 2 ("passes done")
+      // and 4 ("epilogue 1 done") without waiting and move on.
       // K-major (kX) and MN-major (mX) base descriptors of every operand tile of this chunk
       const uint64_t kQ = make_desc(aQ, 16, 1024), mQ = make_desc(aQ, 8192, 1024);
       const uint64_t kKP = make_desc(aKP, 16, 1024), mKP = make_desc(aKP, 8192, 1024);
@@ -185,27 +187,27 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
       const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024);
       const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
-      // MMAs on raw tiles go out as soon as the stage has landed, those on rotated tiles after the
-      // workers' passes, and only the three products of the masked tiles (dP, Pdec) wait for epilogue 1.
-      if (lane == 0 && s_abort == 0) {
-        if (mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) {
-          tc_fence_after_sync();
+      bool go = lane == 0 && s_abort == 0;
+      if (go) do {
+        // (1) products of raw tiles, as soon as the stage has landed
+        if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(20); s_abort = 1; go = false; break; }
+        tc_fence_after_sync();
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const uint32_t lb = tmem + ((16u * q) << 16);
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              // dS[t][s] = sum_p dY[t][p] U[s][p]          A: dY K-major, B: U K-major rows s (N = 32 half)
-              umma(lb + 32, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
-              // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
-              umma(lb + 128, desc_adv(kDY, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
-            }
+          for (int k = 0; k < 4; ++k) {
+            // dS[t][s] = sum_p dY[t][p] U[s][p]          A: dY K-major, B: U K-major rows s (N = 32 half)
+            umma(lb + 32, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
+            // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
+            umma(lb + 128, desc_adv(kDY, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
           }
-        } else { report_timeout(20); s_abort = 1; }
-      }
+        }
+      } while (false);
       __syncwarp();
-      bar_sync(2, NT + 64);   // Q, K', dYoff, dWv written
-      if (lane == 0 && s_abort == 0) {
+      // (2) products of rotated tiles, once the workers' passes are done (Q, K', dYoff, dWv written)
+      bar_sync(2, NT + 64);
+      if (go && s_abort == 0) {
         tc_fence_after_sync();
         // P~[t][s] = sum_d Q[t][d] K'[s][d]              A: Q K-major, B: K' K-major rows s (N = 32 half)
 #pragma unroll
@@ -219,26 +221,25 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
         umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
         SL_TOCK_MMA(6)
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
-            umma(lb + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
-            // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
-            umma(lb + 256, desc_adv(kU, 32 * k), desc_adv(mDW, TILE * q + 2048 * k), ID_KM64, k > 0);
-          }
-        }
-        if (it + 1 < nC) {   // next chunk's tiles, after the workers' burst
+        if (it + 1 < nC) {   // next chunk's tiles (after the workers' burst at the top of the iteration)
           tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
           issue_loads(c - 1, it + 1);
         }
         SL_TOCK_MMA(18)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
+            umma(lb + 256, desc_adv(kU, 32 * k), desc_adv(mDW, TILE * q + 2048 * k), ID_KM64, k > 0);
+        }
       }
       __syncwarp();
-      bar_sync(3, NT + 32);   // Pdec, dP written
-      if (lane == 0 && s_abort == 0) {
+      // (3) products of the masked tiles, once epilogue 1 has written Pdec and dP; ordered by the
+      // epilogue that consumes them (dX, dQ, dU, dZ)
+      bar_sync(4, NT + 32);
+      if (go && s_abort == 0) do {
         tc_fence_after_sync();
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
@@ -260,14 +261,12 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         umma_commit(&bar_mma[2]);   // dQ
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
           const uint32_t lb = tmem + ((16u * q) << 16);
+          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma(lb + 320, desc_adv(mPD, 2048 * k), desc_adv(mDY, 64 * q + 2048 * k), ID_MM32, k > 0);
           // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p (N = 32 half)
-          // (does not depend on epilogue 1, but issuing it earlier would hold this warp back from
-          // the barrier the workers are waiting at)
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
@@ -275,26 +274,28 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           }
         }
         umma_commit(&bar_mma[3]);   // dU
-        umma_commit(&bar_mma[4]);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
+            umma(lb + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
+        }
+        umma_commit(&bar_mma[4]);   // dZ
         SL_TOCK_MMA(9)
-        // Output tiles: the workers overwrite dead operand tiles of this stage in place (C with dB,
+        // (4) output tiles: the workers overwrite dead operand tiles of this stage in place (C with dB,
         // B with dC, dY with dU) and signal; one TMA store per tile writes full 128-byte rows.
-        if (mbar_wait(&bar_st[0], it & 1)) {
-          tma_store_3d(&p.tmdB, tC, 0, t0, bh); tma_store_3d(&p.tmdB, tC + TILE, 64, t0, bh);
-          tma_store_commit();
-        } else { report_timeout(17); s_abort = 1; }
-        if (mbar_wait(&bar_st[1], it & 1)) {
-          tma_store_3d(&p.tmdC, tB, 0, t0, bh); tma_store_3d(&p.tmdC, tB + TILE, 64, t0, bh);
-          tma_store_commit();
-        } else { report_timeout(18); s_abort = 1; }
-        if (mbar_wait(&bar_st[2], it & 1)) {
-#ifdef SL_TC_TIMING
-          if (g_tc_exp != 2)
-#endif
-          tma_store_3d(&p.tmdU, tDY, 0, t0, bh);
-          tma_store_commit();
-        } else { report_timeout(19); s_abort = 1; }
-      }
+        if (!mbar_wait(&bar_st[0], it & 1)) { report_timeout(17); s_abort = 1; break; }
+        tma_store_3d(&p.tmdB, tC, 0, t0, bh); tma_store_3d(&p.tmdB, tC + TILE, 64, t0, bh);
+        tma_store_commit();
+        if (!mbar_wait(&bar_st[1], it & 1)) { report_timeout(18); s_abort = 1; break; }
+        tma_store_3d(&p.tmdC, tB, 0, t0, bh); tma_store_3d(&p.tmdC, tB + TILE, 64, t0, bh);
+        tma_store_commit();
+        if (!mbar_wait(&bar_st[2], it & 1)) { report_timeout(19); s_abort = 1; break; }
+        tma_store_3d(&p.tmdU, tDY, 0, t0, bh);
+        tma_store_commit();
+      } while (false);
       __syncwarp();
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
@@ -390,7 +391,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     SL_TOCK(4)
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(2, NT + 64);
+    bar_sync(3, NT);             // workers only ...
+    bar_arrive(2, NT + 64);      // ... the scalar and issue warps are told without being waited for
     live = s_abort == 0;
     SL_TOCK(5)
 
@@ -429,7 +431,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     }
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(3, NT + 32);
+    bar_sync(3, NT);
+    bar_arrive(4, NT + 32);
     live = s_abort == 0;
     SL_TOCK(8)
 

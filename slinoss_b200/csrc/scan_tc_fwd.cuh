@@ -143,17 +143,17 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       // scalars of the NEXT chunk, started once the workers are through the rotation pass (global
       // loads issued during the workers' shared-memory burst at the top of the iteration stalled
       // the whole SM for about a DRAM round trip)
-      bar_sync(2, NT + 64);
+      bar_sync(2, NT + 64);   // the workers only arrive here (bar_arrive): they never wait for this warp
       if (c + 1 < p.nchunks) chunk_scalars(sc_tab + ((c + 1) & 1) * (NSCAL * 64), Mb, Kb, t0 + L, T, lane);
     } else if (!worker) {
-      // Issue warp: the MMAs of this chunk and the TMA loads of the NEXT one.  It meets the workers
-      // at the "operands ready" barriers (id 2) and at the end of the iteration.
+      // Issue warp (one lane): the MMAs of this chunk, the TMA loads of the NEXT one and the TMA
+      // stores.  The workers never wait for this warp, only for the commit barriers of the products
+      // they read: they arrive on named barriers 2 ("rotation done") and 4 ("S tile written") without
+      // waiting and move on.
       const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
-      // the stores of the previous chunk (its Y tile, its state tiles) must have read shared memory
-      // before the workers overwrite the state tiles and before the stage is refilled below
-      if (lane == 0) tma_store_wait_read();
-      bar_sync(2, NT + 64);   // Q, K', K'' written; U landed; Zv tile stored by the previous chunk
-      if (lane == 0 && s_abort == 0) {
+      bar_sync(2, NT + 64);   // rotation done: Q, K', K'' written; U landed; Zv tile stored by the previous chunk
+      const bool go = lane == 0 && s_abort == 0;
+      if (go) {
         tc_fence_after_sync();
         if (!STATES_ONLY) {
           // scores and off-term: [S | Yoff] = Q [K' ; Zv]^T
@@ -172,7 +172,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
           umma(tmem + 192, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
         umma_commit(&bar_mma[1]);
         SL_TICK_MMA(3)
-        if (c + 1 < p.nchunks) issue_loads(c + 1);   // next chunk's tiles, after the workers' burst
+        if (c + 1 < p.nchunks) {   // next chunk's tiles, after the workers' burst
+          tma_store_wait_read();   // the Y store of the previous chunk read the U slot being refilled
+          issue_loads(c + 1);
+        }
         if (p.states16) {   // the 16-bit state tile of this chunk is exactly what the backward wants
           tma_store_3d(&p.tmS, st + 2 * TILE, 0, c * 64, bh);
           tma_store_3d(&p.tmS, st + 4 * TILE, 64, c * 64, bh);
@@ -180,9 +183,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         }
       }
       __syncwarp();
-      if (!STATES_ONLY) {
-        bar_sync(3, NT + 32);   // S tile written
-        if (lane == 0 && s_abort == 0) {
+      if (!STATES_ONLY) bar_sync(4, NT + 32);   // S tile written
+      if (go && s_abort == 0) {
+        if (!STATES_ONLY) {
           tc_fence_after_sync();
           const uint64_t bS = make_desc(aS, 16, 1024);
 #pragma unroll
@@ -197,8 +200,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
             } else { report_timeout(5); s_abort = 1; }
           }
         }
-        __syncwarp();
+        // the state tiles stored above are overwritten by the workers in the next iteration: their
+        // store must have read them by then (the Y store, if any, may still be in flight)
+        if (Y_TMA) tma_store_wait_read_keep1(); else tma_store_wait_read();
       }
+      __syncwarp();
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
     if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1)) { report_timeout(1); s_abort = 1; live = false; }
@@ -245,7 +251,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     }
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(2, NT + 64);
+    bar_sync(3, NT);             // workers only ...
+    bar_arrive(2, NT + 64);      // ... the scalar and issue warps are told without being waited for
     live = s_abort == 0;
     SL_TICK(2)
 
@@ -286,7 +293,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       }
       fence_async_smem();
       tc_fence_before_sync();
-      bar_sync(3, NT + 32);   // the issue warp now issues Y_diag = S U
+      bar_sync(3, NT);
+      bar_arrive(4, NT + 32);   // the issue warp now issues Y_diag = S U
       live = s_abort == 0;
       SL_TICK(5)
     }

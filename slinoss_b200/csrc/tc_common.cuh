@@ -98,6 +98,10 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// ... all but the most recent one
+__device__ __forceinline__ void tma_store_wait_read_keep1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // all committed store groups of this thread are complete (their writes performed)
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -152,6 +156,11 @@ __device__ __forceinline__ uint64_t desc_adv(uint64_t base, uint32_t byte_off) {
 // named barrier among the first `nthreads` threads of the CTA (id 1..15)
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// arrive on a named barrier without waiting (producer side; the consumers bar_sync on the same id)
+__device__ __forceinline__ void bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
