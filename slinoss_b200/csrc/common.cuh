@@ -26,6 +26,30 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) {
   return __float2half_rn(v);
 }
 
+// 16-byte vectors of io elements: 4 floats or 8 16-bit values, handled as floats
+template <typename T> struct Vec16 { static constexpr int N = 16 / (int)sizeof(T); };
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&v)[Vec16<T>::N]) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i) v[i] = to_f32(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[Vec16<T>::N]) {
+  const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i) v[i] = to_f32(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const float (&v)[Vec16<T>::N]) {
+  uint4 r;
+  T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i) e[i] = from_f32<T>(v[i]);
+  *reinterpret_cast<uint4*>(p) = r;
+}
+
 struct cf {  // complex float
   float re, im;
 };

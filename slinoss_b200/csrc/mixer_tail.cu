@@ -153,6 +153,218 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_kernel(TailParams p) {
     for (int i = threadIdx.x; i < p.H; i += blockDim.x) atomicAdd(p.d_d_skip + i, s_dskip[i]);
 }
 
+// ---- vector path: every thread owns 16-byte pieces (8 or 4 channels of one head) ---------------
+// Needs P % V == 0 (a piece never straddles two heads), 16-byte aligned pointers and a gate row
+// stride that is a multiple of V.  One CTA owns one row at a time; a thread keeps the same
+// channels for every row it visits, so the weight / skip gradients are accumulated in registers
+// over the CTA's rows and added to the float32 accumulators once at the end.
+constexpr int TAIL_VIT_MAX = 2;   // pieces per thread: channels <= 2 * 256 * V
+
+template <typename T, int TAIL_VIT>
+__global__ void __launch_bounds__(TAIL_THREADS) tail_fwd_vec_kernel(TailParams p) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float s_red[TAIL_THREADS / 32];
+  const int C = p.H * p.P;
+  const T* Y = reinterpret_cast<const T*>(p.Y);
+  const T* S = reinterpret_cast<const T*>(p.skip);
+  const T* gate = reinterpret_cast<const T*>(p.gate);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  T* out = reinterpret_cast<T*>(p.normed);
+  float wv[TAIL_VIT][V], dsk[TAIL_VIT];
+  int hh[TAIL_VIT], pp[TAIL_VIT];
+#pragma unroll
+  for (int i = 0; i < TAIL_VIT; ++i) {
+    const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+    hh[i] = 0; pp[i] = 0; dsk[i] = 0.f;
+    if (c < C) {
+      hh[i] = c / p.P; pp[i] = c - hh[i] * p.P;
+      load16<T>(w + c, wv[i]);
+      if (S) dsk[i] = p.d_skip[hh[i]];
+    }
+  }
+  // The raw 16-byte pieces of the NEXT row are fetched before the current row is reduced, so the
+  // loads overlap the block reduction and the stores.
+  const long long rows = (long long)p.batch * p.T;
+  uint4 nY[TAIL_VIT], nG[TAIL_VIT], nS[TAIL_VIT];
+  auto fetch = [&](long long row) {
+    const int t = (int)(row % p.T), b = (int)(row / p.T);
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        const size_t yi = (((size_t)b * p.H + hh[i]) * p.T + t) * p.P + pp[i];
+        nY[i] = *reinterpret_cast<const uint4*>(Y + yi);
+        nG[i] = *reinterpret_cast<const uint4*>(gate + (size_t)row * p.gs + c);
+        if (S) nS[i] = *reinterpret_cast<const uint4*>(S + yi);
+      }
+    }
+  };
+  if (blockIdx.x < rows) fetch(blockIdx.x);
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint4 cY[TAIL_VIT], cG[TAIL_VIT], cS[TAIL_VIT];
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) { cY[i] = nY[i]; cG[i] = nG[i]; cS[i] = nS[i]; }
+    if (row + gridDim.x < rows) fetch(row + gridDim.x);
+    float hid[TAIL_VIT][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        float y[V], g[V];
+        unpack16<T>(cY[i], y);
+        unpack16<T>(cG[i], g);
+        if (S) {
+          float sv[V];
+          unpack16<T>(cS[i], sv);
+#pragma unroll
+          for (int k = 0; k < V; ++k) y[k] = round_io<T>(y[k] + sv[k] * dsk[i]);
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          hid[i][k] = round_io<T>(y[k] * silu_f(g[k]));
+          ss += hid[i][k] * hid[i][k];
+        }
+      }
+    }
+    ss = block_sum(ss, s_red);
+    const float rstd = rsqrtf(ss / (float)C + p.eps);
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        float o[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) o[k] = hid[i][k] * rstd * wv[i][k];
+        store16<T>(out + (size_t)row * C + c, o);
+      }
+    }
+  }
+}
+
+template <typename T, int TAIL_VIT>
+__global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_vec_kernel(TailParams p) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float s_red[TAIL_THREADS / 32];
+  const int C = p.H * p.P;
+  const T* Y = reinterpret_cast<const T*>(p.Y);
+  const T* S = reinterpret_cast<const T*>(p.skip);
+  const T* gate = reinterpret_cast<const T*>(p.gate);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const T* dn = reinterpret_cast<const T*>(p.dn);
+  T* dY = reinterpret_cast<T*>(p.dY);
+  T* dgate = reinterpret_cast<T*>(p.dgate);
+  T* dS = reinterpret_cast<T*>(p.dskip_in);
+  float wv[TAIL_VIT][V], dw_acc[TAIL_VIT][V], dsk[TAIL_VIT], dsk_acc[TAIL_VIT];
+  int hh[TAIL_VIT], pp[TAIL_VIT];
+#pragma unroll
+  for (int i = 0; i < TAIL_VIT; ++i) {
+    const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+    hh[i] = 0; pp[i] = 0; dsk[i] = 0.f; dsk_acc[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_acc[i][k] = 0.f;
+    if (c < C) {
+      hh[i] = c / p.P; pp[i] = c - hh[i] * p.P;
+      load16<T>(w + c, wv[i]);
+      if (S) dsk[i] = p.d_skip[hh[i]];
+    }
+  }
+  const long long rows = (long long)p.batch * p.T;
+  uint4 nY[TAIL_VIT], nG[TAIL_VIT], nS[TAIL_VIT], nD[TAIL_VIT];
+  auto fetch = [&](long long row) {   // raw pieces of the next row, in flight while this one is reduced
+    const int t = (int)(row % p.T), b = (int)(row / p.T);
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        const size_t yi = (((size_t)b * p.H + hh[i]) * p.T + t) * p.P + pp[i];
+        nY[i] = *reinterpret_cast<const uint4*>(Y + yi);
+        nG[i] = *reinterpret_cast<const uint4*>(gate + (size_t)row * p.gs + c);
+        nD[i] = *reinterpret_cast<const uint4*>(dn + (size_t)row * C + c);
+        if (S) nS[i] = *reinterpret_cast<const uint4*>(S + yi);
+      }
+    }
+  };
+  if (blockIdx.x < rows) fetch(blockIdx.x);
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int t = (int)(row % p.T), b = (int)(row / p.T);
+    float pre[TAIL_VIT][V], sv[TAIL_VIT][V], g[TAIL_VIT][V], dnv[TAIL_VIT][V];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        unpack16<T>(nY[i], pre[i]);
+        unpack16<T>(nG[i], g[i]);
+        unpack16<T>(nD[i], dnv[i]);
+        if (S) unpack16<T>(nS[i], sv[i]);
+      }
+    }
+    if (row + gridDim.x < rows) fetch(row + gridDim.x);
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        if (S) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) pre[i][k] = round_io<T>(pre[i][k] + sv[i][k] * dsk[i]);
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float hid = round_io<T>(pre[i][k] * silu_f(g[i][k]));
+          ss += hid * hid;
+          dot += hid * dnv[i][k] * wv[i][k];
+        }
+      }
+    }
+    ss = block_sum(ss, s_red);
+    dot = block_sum(dot, s_red);
+    const float rstd = rsqrtf(ss / (float)C + p.eps);
+    const float coef = dot * rstd * rstd * rstd / (float)C;
+#pragma unroll
+    for (int i = 0; i < TAIL_VIT; ++i) {
+      const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+      if (c < C) {
+        const size_t yi = (((size_t)b * p.H + hh[i]) * p.T + t) * p.P + pp[i];
+        float o_dy[V], o_dg[V], o_ds[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float gg = g[i][k], sg = sigmoid_f(gg);
+          const float hid = round_io<T>(pre[i][k] * (gg * sg));
+          dw_acc[i][k] += dnv[i][k] * hid * rstd;
+          const float dh = rstd * dnv[i][k] * wv[i][k] - hid * coef;
+          const float dpre = dh * gg * sg;
+          o_dg[k] = dh * pre[i][k] * sg * (1.f + gg * (1.f - sg));
+          o_dy[k] = dpre;
+          if (S) { o_ds[k] = dpre * dsk[i]; dsk_acc[i] += dpre * sv[i][k]; }
+        }
+        store16<T>(dgate + (size_t)row * C + c, o_dg);
+        store16<T>(dY + yi, o_dy);
+        if (S && dS) store16<T>(dS + yi, o_ds);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TAIL_VIT; ++i) {
+    const int c = (threadIdx.x + i * TAIL_THREADS) * V;
+    if (c < C) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) atomicAdd(p.d_w + c + k, dw_acc[i][k]);
+      if (S && p.d_d_skip) atomicAdd(p.d_d_skip + hh[i], dsk_acc[i]);
+    }
+  }
+}
+
+template <typename T>
+bool tail_vec_ok(const TailParams& p) {
+  constexpr int V = Vec16<T>::N;
+  const long long C = (long long)p.H * p.P;
+  auto al = [](const void* q) { return q == nullptr || aligned(q, 16); };
+  return p.P % V == 0 && p.gs % V == 0 && C <= (long long)TAIL_VIT_MAX * TAIL_THREADS * V && al(p.Y) &&
+         al(p.gate) && al(p.skip) && al(p.w) && al(p.dn) && al(p.normed) && al(p.dY) && al(p.dgate) &&
+         al(p.dskip_in);
+}
+
 int tail_check(const void* Y, const void* gate, const void* skip, const float* d_skip,
                const void* w, int batch, int heads, int T, int P, int io_dtype) {
   if (!Y || !gate || !w) return SL_ERR_NULL_POINTER;
@@ -179,7 +391,12 @@ extern "C" int sl_mixer_tail_fwd(const void* Y, const void* gate, int64_t gate_r
   const long long rows = (long long)batch * T;
   const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  SL_DISPATCH_DTYPE(io_dtype, Tt, { tail_fwd_kernel<Tt><<<grid, TAIL_THREADS, 0, st>>>(p); });
+  SL_DISPATCH_DTYPE(io_dtype, Tt, {
+    if (tail_vec_ok<Tt>(p)) {
+      if ((long long)heads * P <= TAIL_THREADS * Vec16<Tt>::N) tail_fwd_vec_kernel<Tt, 1><<<grid, TAIL_THREADS, 0, st>>>(p);
+      else tail_fwd_vec_kernel<Tt, 2><<<grid, TAIL_THREADS, 0, st>>>(p);
+    } else tail_fwd_kernel<Tt><<<grid, TAIL_THREADS, 0, st>>>(p);
+  });
   note_launches(1);
   return launch_status();
 }
@@ -198,10 +415,15 @@ extern "C" int sl_mixer_tail_bwd(const void* Y, const void* gate, int64_t gate_r
   p.d_w = d_norm_weight; p.gs = gate_row_stride; p.eps = eps;
   p.batch = batch; p.H = heads; p.T = T; p.P = P;
   const long long rows = (long long)batch * T;
-  const unsigned grid = (unsigned)(rows < 148 * 4 ? rows : 148 * 4);
+  const unsigned grid = (unsigned)(rows < 148 * 2 ? rows : 148 * 2);   // two resident CTAs per SM
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)heads * sizeof(float);
-  SL_DISPATCH_DTYPE(io_dtype, Tt, { tail_bwd_kernel<Tt><<<grid, TAIL_THREADS, smem, st>>>(p); });
+  SL_DISPATCH_DTYPE(io_dtype, Tt, {
+    if (tail_vec_ok<Tt>(p)) {
+      if ((long long)heads * P <= TAIL_THREADS * Vec16<Tt>::N) tail_bwd_vec_kernel<Tt, 1><<<grid, TAIL_THREADS, 0, st>>>(p);
+      else tail_bwd_vec_kernel<Tt, 2><<<grid, TAIL_THREADS, 0, st>>>(p);
+    } else tail_bwd_kernel<Tt><<<grid, TAIL_THREADS, smem, st>>>(p);
+  });
   note_launches(1);
   return launch_status();
 }

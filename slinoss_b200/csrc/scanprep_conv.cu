@@ -22,6 +22,29 @@ namespace {
 
 constexpr int CONV_TT = 32;  // tokens per CTA in the value kernels
 
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  } else {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = to_f32(e[i]);
+  }
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&v)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+    uint2 r;
+    T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+}
+
 struct ValueParams {
   const void *x, *w, *bias, *state_in;
   void *state_out, *U;
@@ -152,6 +175,245 @@ __global__ void __launch_bounds__(256) value_bwd_kernel(ValueBwdParams q) {
   if (q.dbias) atomicAdd(q.dbias + c, dbacc);
 }
 
+// ---- vector path of the value kernels ----------------------------------------------------------------
+// A thread owns 4 consecutive channels (one 8- or 16-byte access per token) and walks CONV_TT
+// tokens; a warp covers 128 consecutive channels, a CTA of 256 threads 8 token sub-tiles of the
+// same 128 channels, so that the conv weight / bias gradients of the 8 sub-tiles are combined in
+// shared memory and added to the float32 accumulators once per CTA.
+// Needs P % 4 == 0 (a piece stays inside one head), strides that are multiples of 4 and aligned
+// pointers; anything else takes the one-channel-per-thread kernels above.
+constexpr int CONV_V = 4;
+constexpr int CONV_SUB = 8;   // token sub-tiles per CTA
+
+template <typename T>
+__device__ __forceinline__ void load_xv(const ValueParams& p, const T* x, const T* st, int b, int t, int c,
+                                        float (&v)[CONV_V]) {
+  if (t >= 0) { load4<T>(x + ((size_t)b * p.T + t) * p.xs + c, v); return; }
+  const int j = p.W - 1 + t;
+#pragma unroll
+  for (int k = 0; k < CONV_V; ++k)
+    v[k] = (st && j >= 0) ? to_f32(st[((size_t)b * p.C + c + k) * (p.W - 1) + j]) : 0.f;
+}
+
+template <typename T, int V> __device__ __forceinline__ void loadv(const T* p, float (&v)[V]) {
+  if constexpr (V == 4) load4<T>(p, v); else load16<T>(p, v);
+}
+template <typename T, int V> __device__ __forceinline__ void storev(T* p, const float (&v)[V]) {
+  if constexpr (V == 4) store4<T>(p, v); else store16<T>(p, v);
+}
+
+// Forward: V = 8 channels per thread for 16-bit io (16-byte accesses), 4 for float32.
+template <typename T, int V>
+__global__ void __launch_bounds__(256) value_fwd_vec_kernel(ValueParams p) {
+  const int c = (blockIdx.x * 32 + (threadIdx.x & 31)) * V;
+  const int t0 = (blockIdx.y * CONV_SUB + (threadIdx.x >> 5)) * CONV_TT, b = blockIdx.z;
+  if (c >= p.C || t0 >= p.T) return;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* st = reinterpret_cast<const T*>(p.state_in);
+  T* U = reinterpret_cast<T*>(p.U);
+  const int h = c / p.P, pp = c - h * p.P;
+  T* Ub = U + (size_t)b * p.usb + (size_t)h * p.ush + pp;
+  const T* xb = x + (size_t)b * p.T * p.xs + c;
+  const int t1 = min(t0 + CONV_TT, p.T);
+  if (!p.w) {
+    for (int t = t0; t < t1; ++t) {
+      float v[V];
+      loadv<T, V>(xb + (size_t)t * p.xs, v);
+      storev<T, V>(Ub + (size_t)t * p.ust, v);
+    }
+    return;
+  }
+  const T* w = reinterpret_cast<const T*>(p.w);
+  float wj[4][V], win[4][V], bias[V];
+  auto x_at = [&](int t, int k) -> float {   // scalar access for the halo (t may be negative)
+    if (t >= 0) return to_f32(xb[(size_t)t * p.xs + k]);
+    const int j = p.W - 1 + t;
+    return (st && j >= 0) ? to_f32(st[((size_t)b * p.C + c + k) * (p.W - 1) + j]) : 0.f;
+  };
+  if (p.W == 4 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
+    // taps of V channels are 4 V contiguous values; bias and the three halo rows are one piece each
+    float wf[4 * V];
+#pragma unroll
+    for (int i = 0; i < 4 * V / Vec16<T>::N; ++i) {
+      float q[Vec16<T>::N];
+      load16<T>(w + (size_t)c * 4 + i * Vec16<T>::N, q);
+#pragma unroll
+      for (int e = 0; e < Vec16<T>::N; ++e) wf[i * Vec16<T>::N + e] = q[e];
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wj[j][k] = wf[4 * k + j];
+      bias[k] = 0.f; win[0][k] = 0.f;
+    }
+    if (p.bias) loadv<T, V>(reinterpret_cast<const T*>(p.bias) + c, bias);
+#pragma unroll
+    for (int q = 1; q < 4; ++q) {
+      const int t = t0 - 4 + q;
+      if (t >= 0) loadv<T, V>(xb + (size_t)t * p.xs, win[q]);
+      else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) win[q][k] = x_at(t, k);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)   // right-aligned taps; static indices keep wj in registers
+        wj[j][k] = (j >= 4 - p.W) ? to_f32(w[(size_t)(c + k) * p.W + (j - (4 - p.W))]) : 0.f;
+      bias[k] = p.bias ? to_f32(reinterpret_cast<const T*>(p.bias)[c + k]) : 0.f;
+      win[0][k] = 0.f;
+#pragma unroll
+      for (int q = 1; q < 4; ++q) win[q][k] = (4 - q <= p.W - 1) ? x_at(t0 - 4 + q, k) : 0.f;
+    }
+  }
+#pragma unroll 8
+  for (int t = t0; t < t1; ++t) {
+    float xin[V], o[V];
+    loadv<T, V>(xb + (size_t)t * p.xs, xin);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      win[0][k] = win[1][k]; win[1][k] = win[2][k]; win[2][k] = win[3][k]; win[3][k] = xin[k];
+      const float a = bias[k] + wj[0][k] * win[0][k] + wj[1][k] * win[1][k] + wj[2][k] * win[2][k] +
+                      wj[3][k] * win[3][k];
+      o[k] = silu_f(a);
+    }
+    storev<T, V>(Ub + (size_t)t * p.ust, o);
+  }
+  if (p.state_out && t1 == p.T) {
+    T* so = reinterpret_cast<T*>(p.state_out);
+    for (int j = 0; j < p.W - 1; ++j) {
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+        so[((size_t)b * p.C + c + k) * (p.W - 1) + j] = from_f32<T>(x_at(p.T - (p.W - 1) + j, k));
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) value_bwd_vec_kernel(ValueBwdParams q) {
+  const ValueParams& p = q.f;
+  __shared__ float s_acc[CONV_SUB][5][32 * CONV_V];   // dw (4 taps) and dbias partials per sub-tile
+  const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * CONV_V;
+  const int t0 = (blockIdx.y * CONV_SUB + sub) * CONV_TT, b = blockIdx.z;
+  const bool live = c < p.C && t0 < p.T;
+  float dwacc[4][CONV_V], dbacc[CONV_V];
+#pragma unroll
+  for (int k = 0; k < CONV_V; ++k) {
+    dbacc[k] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dwacc[j][k] = 0.f;
+  }
+  if (live) {
+    const T* x = reinterpret_cast<const T*>(p.x);
+    const T* st = reinterpret_cast<const T*>(p.state_in);
+    const T* dU = reinterpret_cast<const T*>(q.dU);
+    T* dx = reinterpret_cast<T*>(q.dx);
+    const int h = c / p.P, pp = c - h * p.P;
+    const T* dUb = dU + (size_t)b * p.usb + (size_t)h * p.ush + pp;
+    const int t1 = min(t0 + CONV_TT, p.T);
+    if (!p.w) {
+      for (int t = t0; t < t1; ++t) {
+        float v[CONV_V];
+        load4<T>(dUb + (size_t)t * p.ust, v);
+        store4<T>(dx + ((size_t)b * p.T + t) * p.C + c, v);
+      }
+    } else {
+      const T* w = reinterpret_cast<const T*>(p.w);
+      const int W = p.W;
+      float wj[4][CONV_V], win[4][CONV_V], da[4][CONV_V], bias[CONV_V];
+#pragma unroll
+      for (int k = 0; k < CONV_V; ++k) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          da[j][k] = 0.f;
+          wj[j][k] = (j >= 4 - W) ? to_f32(w[(size_t)(c + k) * W + (j - (4 - W))]) : 0.f;
+        }
+        bias[k] = p.bias ? to_f32(reinterpret_cast<const T*>(p.bias)[c + k]) : 0.f;
+        win[0][k] = 0.f;
+      }
+      const int s_begin = t0;   // the first tile also owns the gradient of the carried conv state
+#pragma unroll
+      for (int r = 1; r < 4; ++r) {
+        if (4 - r <= W - 1) load_xv<T>(p, x, st, b, s_begin - 4 + r, c, win[r]);
+        else {
+#pragma unroll
+          for (int k = 0; k < CONV_V; ++k) win[r][k] = 0.f;
+        }
+      }
+      // s runs over the tokens whose da is formed; dx[s-3] is complete at step s
+      const int s_end = min(t1 + 3, p.T + 3);
+#pragma unroll 4
+      for (int s = s_begin; s < s_end; ++s) {
+        float xin[CONV_V], gy[CONV_V], g[CONV_V];
+        const bool in = s < p.T;
+        if (in) {
+          load4<T>(x + ((size_t)b * p.T + s) * p.xs + c, xin);
+          load4<T>(dUb + (size_t)s * p.ust, gy);
+        }
+        const bool mine = s < t1;   // each token's weight / bias contribution is counted once
+#pragma unroll
+        for (int k = 0; k < CONV_V; ++k) {
+          win[0][k] = win[1][k]; win[1][k] = win[2][k]; win[2][k] = win[3][k];
+          da[0][k] = da[1][k]; da[1][k] = da[2][k]; da[2][k] = da[3][k];
+          float d = 0.f;
+          if (in) {
+            win[3][k] = xin[k];
+            const float a = bias[k] + wj[0][k] * win[0][k] + wj[1][k] * win[1][k] + wj[2][k] * win[2][k] +
+                            wj[3][k] * win[3][k];
+            d = gy[k] * dsilu_f(a);
+            if (mine) {
+              dwacc[0][k] += d * win[0][k]; dwacc[1][k] += d * win[1][k];
+              dwacc[2][k] += d * win[2][k]; dwacc[3][k] += d * win[3][k];
+              dbacc[k] += d;
+            }
+          } else {
+            win[3][k] = 0.f;
+          }
+          da[3][k] = d;
+          g[k] = wj[3][k] * da[0][k] + wj[2][k] * da[1][k] + wj[1][k] * da[2][k] + wj[0][k] * da[3][k];
+        }
+        const int t = s - 3;
+        if (t >= t0 && t < t1) store4<T>(dx + ((size_t)b * p.T + t) * p.C + c, g);
+        else if (t < 0 && t0 == 0 && q.dstate && t >= -(W - 1)) {
+#pragma unroll
+          for (int k = 0; k < CONV_V; ++k)
+            reinterpret_cast<T*>(q.dstate)[((size_t)b * p.C + c + k) * (W - 1) + (W - 1 + t)] = from_f32<T>(g[k]);
+        }
+      }
+    }
+  }
+  if (!p.w) return;
+#pragma unroll
+  for (int k = 0; k < CONV_V; ++k) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s_acc[sub][j][lane * CONV_V + k] = dwacc[j][k];
+    s_acc[sub][4][lane * CONV_V + k] = dbacc[k];
+  }
+  __syncthreads();
+  // 5 x 128 sums of CONV_SUB partials; one atomic per (channel, tap) per CTA
+  for (int i = threadIdx.x; i < 5 * 32 * CONV_V; i += blockDim.x) {
+    const int j = i / (32 * CONV_V), cc = i - j * (32 * CONV_V);
+    const int ch = blockIdx.x * 32 * CONV_V + cc;
+    if (ch >= p.C) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int r = 0; r < CONV_SUB; ++r) v += s_acc[r][j][cc];
+    if (j < 4) { if (j >= 4 - p.W) atomicAdd(q.dw + (size_t)ch * p.W + (j - (4 - p.W)), v); }
+    else if (q.dbias) atomicAdd(q.dbias + ch, v);
+  }
+}
+
+inline bool value_vec_ok(const ValueParams& p, const void* a, const void* b, int V = CONV_V) {
+  const int align = 16;
+  return p.P % V == 0 && p.C % V == 0 && p.xs % V == 0 && p.usb % V == 0 &&
+         p.ush % V == 0 && p.ust % V == 0 && aligned(p.x, align) && aligned(p.U, align) &&
+         (a == nullptr || aligned(a, align)) && (b == nullptr || aligned(b, align));
+}
+
 // ---- B / C parameterisation ------------------------------------------------------
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -235,6 +497,176 @@ __global__ void __launch_bounds__(256) bc_bwd_kernel(const T* __restrict__ bc,
       dst[(size_t)(2 * which + 1) * N + n] = from_f32<T>(g_ph * 3.14159265358979323846f * (1.f - th * th));
     }
   }
+}
+
+// ---- vector path of the B / C kernels (N % 4 == 0, N <= 64) ----------------------------------------
+// One warp per (batch, token, group) record of 4 rows x N: lanes 0-15 produce B, lanes 16-31 C;
+// a lane owns 4 consecutive n: two 8-byte loads (amplitude and phase logits), one 16-byte store of
+// 4 complex values.  The mean over n is a shuffle reduction inside the 16-lane half.  With 16-bit
+// io the transcendental functions are the fast intrinsics (their error is far below the output's
+// rounding); float32 io keeps the precise ones.
+template <bool FAST> __device__ __forceinline__ float softplus_v(float x) {
+  if (FAST) return fmaxf(x, 0.f) + __logf(1.f + __expf(-fabsf(x)));
+  return softplus_f(x);
+}
+template <bool FAST> __device__ __forceinline__ float tanh_v(float x) {
+  if (FAST) {   // one MUFU op, relative error 2^-11: below the rounding of 16-bit outputs
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  return tanhf(x);
+}
+template <bool FAST> __device__ __forceinline__ float sigmoid_v(float x) {
+  if (FAST) return 0.5f * tanh_v<true>(0.5f * x) + 0.5f;
+  return sigmoid_f(x);
+}
+template <bool FAST> __device__ __forceinline__ void sincos_v(float x, float* s, float* c) {
+  if (FAST) __sincosf(x, s, c);   // |x| <= pi here
+  else sincosf(x, s, c);
+}
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float q[4];
+    load4<T>(p + 4 * h, q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[4 * h + i] = q[i];
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    store16<T>(p, v);
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      *reinterpret_cast<float4*>(p + 4 * h) = make_float4(v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
+  }
+}
+__device__ __forceinline__ float half_warp_sum(float v) {   // over the 16 lanes of a half-warp
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int BC_RPW = 1;   // records per warp (the kernels are bound by the MUFU pipe, not by latency)
+
+template <typename T>
+__global__ void __launch_bounds__(256) bc_fwd_vec_kernel(const T* __restrict__ bc, T* __restrict__ Bo,
+                                                         T* __restrict__ Co, int batch, int Tn,
+                                                         int G, int N, float eps) {
+  constexpr bool FAST = sizeof(T) == 2;
+  const int lane = threadIdx.x & 31, which = lane >> 4, n0 = 4 * (lane & 15);
+  const long long rows = (long long)batch * Tn * G;
+  const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * BC_RPW;
+  if (row0 >= rows) return;
+  const bool act = n0 < N;
+  float amp[BC_RPW][4], ph[BC_RPW][4];
+#pragma unroll
+  for (int r = 0; r < BC_RPW; ++r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { amp[r][i] = 0.f; ph[r][i] = 0.f; }
+    if (act && row0 + r < rows) {
+      const T* src = bc + (size_t)(row0 + r) * 4 * N + (size_t)(2 * which) * N + n0;
+      load4<T>(src, amp[r]);
+      load4<T>(src + N, ph[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < BC_RPW; ++r) {
+    const long long row = row0 + r;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      amp[r][i] = act ? softplus_v<FAST>(amp[r][i]) : 0.f;
+      ss += amp[r][i] * amp[r][i];
+    }
+    ss = half_warp_sum(ss);
+    if (!act || row >= rows) continue;
+    const float inv = rsqrtf(fmaxf(ss / (float)N, eps));
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float sn, cs;
+      sincos_v<FAST>(3.14159265358979323846f * tanh_v<FAST>(ph[r][i]), &sn, &cs);
+      const float a = amp[r][i] * inv;
+      o[2 * i] = a * cs; o[2 * i + 1] = a * sn;
+    }
+    const int g = (int)(row % G);
+    const long long bt = row / G;
+    const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+    T* dst = (which ? Co : Bo) + (((size_t)b * G + g) * Tn + t) * 2 * N + 2 * n0;
+    store8<T>(dst, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bc_bwd_vec_kernel(const T* __restrict__ bc,
+                                                         const T* __restrict__ dBo,
+                                                         const T* __restrict__ dCo,
+                                                         T* __restrict__ dbc, int batch, int Tn,
+                                                         int G, int N, float eps) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int RPW = BC_RPW;
+  const int lane = threadIdx.x & 31, which = lane >> 4, n0 = 4 * (lane & 15);
+  const long long rows = (long long)batch * Tn * G;
+  const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW;
+  if (row0 >= rows) return;
+  const bool act = n0 < N;
+  float xa[RPW][4], xp[RPW][4], gr[RPW][8];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { xa[r][i] = 0.f; xp[r][i] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gr[r][i] = 0.f;
+    const long long row = row0 + r;
+    if (act && row < rows) {
+      const int g = (int)(row % G);
+      const long long bt = row / G;
+      const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+      const size_t off = (size_t)row * 4 * N + (size_t)(2 * which) * N + n0;
+      load4<T>(bc + off, xa[r]);
+      load4<T>(bc + off + N, xp[r]);
+      load8<T>((which ? dCo : dBo) + (((size_t)b * G + g) * Tn + t) * 2 * N + 2 * n0, gr[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    const long long row = row0 + r;
+    float a[4], th[4], sn[4], cs[4];
+    float ss = 0.f, gsum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a[i] = act ? softplus_v<FAST>(xa[r][i]) : 0.f;
+      th[i] = tanh_v<FAST>(xp[r][i]);
+      sincos_v<FAST>(3.14159265358979323846f * th[i], &sn[i], &cs[i]);
+      ss += a[i] * a[i];
+      gsum += a[i] * (cs[i] * gr[r][2 * i] + sn[i] * gr[r][2 * i + 1]);
+    }
+    ss = half_warp_sum(ss); gsum = half_warp_sum(gsum);
+    if (!act || row >= rows) continue;
+    const float ms = ss / (float)N;
+    const float inv = rsqrtf(fmaxf(ms, eps));
+    const float g_ms = ms > eps ? -0.5f * inv * inv * inv * gsum : 0.f;
+    float da[4], dp[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float gre = gr[r][2 * i], gim = gr[r][2 * i + 1];
+      const float g_amp = inv * (cs[i] * gre + sn[i] * gim) + g_ms * 2.f * a[i] / (float)N;
+      const float g_ph = a[i] * inv * (cs[i] * gim - sn[i] * gre);
+      da[i] = g_amp * sigmoid_v<FAST>(xa[r][i]);
+      dp[i] = g_ph * 3.14159265358979323846f * (1.f - th[i] * th[i]);
+    }
+    const size_t off = (size_t)row * 4 * N + (size_t)(2 * which) * N + n0;
+    store4<T>(dbc + off, da);
+    store4<T>(dbc + off + N, dp);
+  }
+}
+
+inline bool bc_vec_ok(int N, const void* a, const void* b, const void* c, const void* d) {
+  return N % 4 == 0 && N <= 64 && aligned(a, 16) && aligned(b, 16) && aligned(c, 16) &&
+         (d == nullptr || aligned(d, 16));
 }
 
 // ---- transition / tap coefficients (float64 inside) ---------------------------------
@@ -415,19 +847,26 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     p.state_out = conv_state_out; p.U = U; p.xs = value_row_stride;
     p.usb = u_stride_b; p.ush = u_stride_h; p.ust = u_stride_t;
     p.batch = batch; p.T = T; p.C = heads * P; p.P = P; p.W = conv_weight ? d_conv : 1;
-    dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
-    SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, st>>>(p); });
+    const int vf = io_dtype == SL_F32 ? 4 : 8;   // channels per thread: 16-byte accesses
+    if (value_vec_ok(p, nullptr, nullptr, vf)) {
+      dim3 grid((p.C + 32 * vf - 1) / (32 * vf), (T + CONV_SUB * CONV_TT - 1) / (CONV_SUB * CONV_TT), batch);
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_vec_kernel<Tt, Vec16<Tt>::N><<<grid, 256, 0, st>>>(p); });
+    } else {
+      dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, st>>>(p); });
+    }
     note_launches(1);
   }
   if (bc) {
     if (!Bo || !Co || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
+    const bool vec = bc_vec_ok(N, bc, Bo, Co, nullptr);
+    const unsigned nblk = vec ? (unsigned)((rows + 8 * BC_RPW - 1) / (8 * BC_RPW)) : blocks;
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
-      bc_fwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc),
-                                               reinterpret_cast<Tt*>(Bo),
-                                               reinterpret_cast<Tt*>(Co), batch, T, groups, N,
-                                               cfg->eps);
+      auto k = vec ? bc_fwd_vec_kernel<Tt> : bc_fwd_kernel<Tt>;
+      k<<<nblk, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
+                                reinterpret_cast<Tt*>(Co), batch, T, groups, N, cfg->eps);
     });
     note_launches(1);
   }
@@ -468,20 +907,28 @@ extern "C" int sl_scanprep_conv_bwd(
     p.xs = value_row_stride; p.usb = u_stride_b; p.ush = u_stride_h; p.ust = u_stride_t;
     p.batch = batch; p.T = T; p.C = heads * P; p.P = P; p.W = conv_weight ? d_conv : 1;
     q.dU = dU; q.dx = d_value; q.dstate = d_conv_state; q.dw = d_conv_weight; q.dbias = d_conv_bias;
-    dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
-    SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+    ValueParams pv = p;
+    pv.U = const_cast<void*>(dU);
+    if (value_vec_ok(pv, d_value, nullptr)) {
+      dim3 grid((p.C + 32 * CONV_V - 1) / (32 * CONV_V), (T + CONV_SUB * CONV_TT - 1) / (CONV_SUB * CONV_TT), batch);
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_vec_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+    } else {
+      dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+    }
     note_launches(1);
   }
   if (dBo) {
     if (!dCo || !bc || !d_bc || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
+    const bool vec = bc_vec_ok(N, bc, dBo, dCo, d_bc);
+    const unsigned nblk = vec ? (unsigned)((rows + 8 * BC_RPW - 1) / (8 * BC_RPW)) : blocks;
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
-      bc_bwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc),
-                                               reinterpret_cast<const Tt*>(dBo),
-                                               reinterpret_cast<const Tt*>(dCo),
-                                               reinterpret_cast<Tt*>(d_bc), batch, T, groups, N,
-                                               cfg->eps);
+      auto k = vec ? bc_bwd_vec_kernel<Tt> : bc_bwd_kernel<Tt>;
+      k<<<nblk, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<const Tt*>(dBo),
+                                reinterpret_cast<const Tt*>(dCo), reinterpret_cast<Tt*>(d_bc), batch, T,
+                                groups, N, cfg->eps);
     });
     note_launches(1);
   }

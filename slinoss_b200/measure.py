@@ -1,0 +1,216 @@
+"""Device timing of every C-ABI entry point at the sizes of the reference's configs.
+
+    python -m slinoss_b200.measure [--what decode,scanprep,tail,mixer,scan] [--iters 20]
+
+Prints one JSON line per measured call: CUDA-event time (mean of ``iters`` back-to-back
+launches after warm-up, on the launching stream), the call's algorithmic bytes (every
+input read once, every output written once) and the fraction of the HBM roofline that
+makes.  ``bench.py`` is the headline (scan forward+backward at config 1); this module
+covers the other rows of the hot path: decode (config 3), fused conv + scan preparation
+and the mixer tail at the mixer configuration (config 2), and the whole mixer layer.
+
+Inputs are seeded synthetic tensors of the configs' shapes and value ranges.  All inputs of a
+call exceed the 126 MB L2 except where noted in the line (``"l2"``).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
+def time_ms(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def report(name, ms, algo_bytes, config, extra=None):
+    peak, kind = hbm_peak()
+    gbs = algo_bytes / (ms * 1e-3) / 1e9
+    line = {"call": name, "ms": ms, "algorithmic_bytes": algo_bytes, "achieved_gbs": gbs,
+            "peak_gbs": peak, "peak_source": kind, "frac": gbs / peak, "config": config}
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+    return line
+
+
+# ---------------------------------------------------------------------------------------
+def measure_decode(iters, dev):
+    """Config 3: batch 256, heads 32, P 64, N 64, bf16 vectors, float32 state."""
+    from . import _C
+    g = torch.Generator().manual_seed(0)
+    b, h, P, N = 256, 32, 64, 64
+    r = lambda *s: torch.randn(*s, generator=g)
+    U = r(b, h, P).to(torch.bfloat16).to(dev)
+    Bv = (r(b, h, 2 * N) / N ** 0.5).to(torch.bfloat16).to(dev)
+    Cv = (r(b, h, 2 * N) / N ** 0.5).to(torch.bfloat16).to(dev)
+    rad = torch.clamp(torch.exp(-torch.nn.functional.softplus(r(b, h))), 0.9, 0.999)
+    th = (torch.rand(b, h, generator=g) * 2 - 1) * torch.pi
+    M = torch.stack([rad * torch.cos(th), rad * torch.sin(th)], -1).contiguous().to(dev)
+    K = (0.05 * r(b, h, 2, 2)).to(dev)
+    state = (0.1 * r(b, h, P, 2 * N)).to(dev)
+    state2 = torch.empty_like(state)
+    Bp, Up = torch.zeros_like(Bv), torch.zeros_like(U)
+    cfg = "config 3: batch 256 x heads 32 x P 64 x N 64, one token"
+
+    def out_of_place():
+        _C.scan_decode(U, M, K, Bv, Cv, state, Bp, Up, y_dtype=torch.bfloat16, state_out=state2)
+
+    def in_place():
+        _C.scan_decode(U, M, K, Bv, Cv, state, Bp, Up, y_dtype=torch.bfloat16, state_out=state)
+
+    algo = nbytes(state, state2, U, Bv, Cv, M, K, Bp, Up) + nbytes(U)
+    report("sl_v2x2ssd_decode (state out of place)", time_ms(out_of_place, iters), algo, cfg)
+    report("sl_v2x2ssd_decode (state in place)", time_ms(in_place, iters), algo, cfg)
+
+
+def _mixer_tensors(dev, batch=8, T=2048, heads=32, P=64, N=64):
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g)
+    d_inner = heads * P
+    proj = r(batch, T, 2 * d_inner).to(torch.bfloat16).to(dev)      # gate | value, as in_proj leaves them
+    gate, value = proj[..., :d_inner], proj[..., d_inner:]
+    params = r(batch, T, 3 * heads).to(torch.bfloat16).to(dev)
+    bc = r(batch, T, heads, 4, N).to(torch.bfloat16).to(dev)
+    w = (0.3 * r(d_inner, 4)).to(torch.bfloat16).to(dev)
+    bias = (0.1 * r(d_inner)).to(torch.bfloat16).to(dev)
+    return gate, value, params, bc, w, bias
+
+
+def measure_scanprep(iters, dev):
+    """Config 2 sizes: batch 8, T 2048, heads 32, P 64, N 64, conv width 4, bf16."""
+    from . import _C
+    from .layers import SLinOSSScanPrep
+    heads, P, N = 32, 64, 64
+    gate, value, params, bc, w, bias = _mixer_tensors(dev)
+    owner = SLinOSSScanPrep(n_heads=heads, d_state=N, d_head=P, device=dev)
+    biases = tuple(getattr(owner, k).detach().float().contiguous()
+                   for k in ("dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias", "theta_sign"))
+    cfg = _C.make_config(owner)
+    name = "config 2: batch 8 x T 2048 x heads 32 x P 64 x N 64, conv width 4, bf16"
+    outs = _C.scanprep_conv_fwd(value, w, bias, None, params, bc, biases, cfg, heads=heads, P=P,
+                                want_state=True)
+    U, M, K, Bo, Co, nstate = outs
+    vbytes = value.shape[0] * value.shape[1] * value.shape[2] * 2
+    algo_f = vbytes + nbytes(params, bc, w, bias, U, M, K, Bo, Co, nstate)
+    report("sl_scanprep_conv_fwd (conv + SiLU + scan preparation, 3 kernels)",
+           time_ms(lambda: _C.scanprep_conv_fwd(value, w, bias, None, params, bc, biases, cfg,
+                                                heads=heads, P=P, want_state=True), iters),
+           algo_f, name)
+    dU, dM, dK = torch.randn_like(U), torch.randn_like(M), torch.randn_like(K)
+    dB, dC = torch.randn_like(Bo), torch.randn_like(Co)
+    res = _C.scanprep_conv_bwd(value, w, bias, None, params, bc, biases, cfg, dU, dM, dK, dB, dC,
+                               heads=heads, P=P)
+    algo_b = vbytes + nbytes(params, bc, w, bias, dU, dM, dK, dB, dC, res["d_value"], res["d_params"],
+                             res["d_bc"])
+    report("sl_scanprep_conv_bwd (3 kernels; includes zeroing of the float32 accumulators)",
+           time_ms(lambda: _C.scanprep_conv_bwd(value, w, bias, None, params, bc, biases, cfg, dU, dM,
+                                                dK, dB, dC, heads=heads, P=P), iters),
+           algo_b, name)
+
+
+def measure_tail(iters, dev):
+    from . import _C
+    heads, P = 32, 64
+    gate, value, *_ = _mixer_tensors(dev)
+    g = torch.Generator().manual_seed(1)
+    Y = torch.randn(8, heads, 2048, P, generator=g).to(torch.bfloat16).to(dev)
+    Uskip = torch.randn(8, heads, 2048, P, generator=g).to(torch.bfloat16).to(dev)
+    d_skip = torch.ones(heads, device=dev)
+    wn = torch.ones(heads * P, device=dev, dtype=torch.bfloat16)
+    name = "config 2: batch 8 x T 2048 x d_inner 2048 (32 heads x 64), bf16"
+    normed = _C.mixer_tail_fwd(Y, gate, Uskip, d_skip, wn, 1e-5)
+    gbytes = gate.shape[0] * gate.shape[1] * gate.shape[2] * 2
+    report("sl_mixer_tail_fwd", time_ms(lambda: _C.mixer_tail_fwd(Y, gate, Uskip, d_skip, wn, 1e-5), iters),
+           nbytes(Y, Uskip, normed) + gbytes, name)
+    dn = torch.randn_like(normed)
+    outs = _C.mixer_tail_bwd(Y, gate, Uskip, d_skip, wn, 1e-5, dn)
+    report("sl_mixer_tail_bwd (includes zeroing of the float32 accumulators)",
+           time_ms(lambda: _C.mixer_tail_bwd(Y, gate, Uskip, d_skip, wn, 1e-5, dn), iters),
+           nbytes(Y, Uskip, dn, outs[0], outs[1], outs[2]) + gbytes, name)
+
+
+def measure_mixer(iters, dev):
+    """Whole mixer layer, forward + backward, config 2 (GEMMs are cuBLAS; tensor-pipe bound)."""
+    import slinoss_b200 as sb
+    torch.manual_seed(0)
+    mixer = sb.SLinOSSMixer(1024, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(dev).to(torch.bfloat16)
+    x = torch.randn(8, 2048, 1024, device=dev, dtype=torch.bfloat16, requires_grad=True)
+
+    def step():
+        out = mixer(x)
+        out.backward(out)
+        mixer.zero_grad(set_to_none=True)
+        x.grad = None
+
+    ms = time_ms(step, max(3, iters // 4))
+    flops = 3 * 2 * 8 * 2048 * 1024 * (12384 + 2048)    # in_proj + out_proj, fwd + 2x bwd
+    print(json.dumps({"call": "SLinOSSMixer forward+backward (config 2)", "ms": ms,
+                      "tokens_per_s": 8 * 2048 / (ms * 1e-3), "gemm_tflops_equivalent": flops / (ms * 1e-3) / 1e12,
+                      "config": "x (8, 2048, 1024) bf16, d_inner 2048, 32 heads x 64, N 64, d_conv 4"}), flush=True)
+
+
+def measure_scan(iters, dev):
+    """Config 1 scan forward / backward through the C ABI (the figures bench.py headlines)."""
+    from . import _C
+    from .synthetic import make_scan_case
+    c = make_scan_case(8, 16, 4096, 64, 64, dtype=torch.bfloat16, seed=0).to(dev)
+    name = "config 1: batch 8 x heads 16 x T 4096 x P 64 x N 64, bf16"
+    fwd = lambda: _C.scan_fwd(c.U, c.M, c.K, c.B, c.C, None, None, None, chunk_size=64,
+                              y_dtype=torch.bfloat16, want_final=False, save_states=True)
+    _, fin, st = fwd()
+    bht = 8 * 16 * 4096
+    report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name)
+    report("sl_v2x2ssd_bwd (saved chunk states)",
+           time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
+                                       chunk_size=64, saved=(st, fin)), iters), bht * 1456, name)
+    report("sl_v2x2ssd_bwd (recomputing chunk states)",
+           time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
+                                       chunk_size=64), iters), bht * 1456, name)
+
+
+WHAT = {"decode": measure_decode, "scanprep": measure_scanprep, "tail": measure_tail,
+        "mixer": measure_mixer, "scan": measure_scan}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="decode,scanprep,tail,mixer,scan")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("slinoss_b200.measure needs a CUDA device: the kernels have no CPU path.")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    for k in args.what.split(","):
+        WHAT[k.strip()](args.iters, dev)
+
+
+if __name__ == "__main__":
+    main()
