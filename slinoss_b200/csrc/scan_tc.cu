@@ -321,7 +321,7 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
                       : launch_tc_bwd<__half, 4>(p, (int)BH, st);
   }
   if (rc != SL_OK) return rc;
-  scan_tc_bwd_finish_kernel<<<(int)BH, 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
+  scan_tc_bwd_finish_kernel<<<dim3((unsigned)BH, (unsigned)((nC + 3) / 4)), 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
   note_launches(2);
   return launch_status();
 }

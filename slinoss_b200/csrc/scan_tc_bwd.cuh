@@ -629,7 +629,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   if (warp == 0) tmem_dealloc(tmem, B_TMEM_COLS);
 }
 
-// dM and dK from the per-token scalars.  One warp per chunk (two tokens per lane).
+// dM and dK from the per-token scalars.  One warp per chunk (two tokens per lane); chunks are
+// independent given the anchors, so the grid is (batch*heads, chunks / 4).
 __global__ void __launch_bounds__(128) scan_tc_bwd_finish_kernel(const float* __restrict__ M,
                                                                  const float* __restrict__ K,
                                                                  const float2* __restrict__ dg,
@@ -640,7 +641,8 @@ __global__ void __launch_bounds__(128) scan_tc_bwd_finish_kernel(const float* __
                                                                  float* __restrict__ dK, int T, int nC) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t bh = blockIdx.x;
-  for (int c = warp; c < nC; c += 4) {
+  // grid.y covers the chunks four at a time: every warp of the grid owns exactly one chunk
+  for (int c = blockIdx.y * 4 + warp; c < nC; c += 4 * gridDim.y) {
     const int tA = c * 64 + 2 * lane, tB = tA + 1;
     float2 sA = make_float2(0.f, 0.f), sB = sA;
     if (tA < T) sA = sterm[bh * T + tA];

@@ -325,17 +325,32 @@ __global__ void __launch_bounds__(256) value_bwd_vec_kernel(ValueBwdParams q) {
       const T* w = reinterpret_cast<const T*>(p.w);
       const int W = p.W;
       float wj[4][CONV_V], win[4][CONV_V], da[4][CONV_V], bias[CONV_V];
+      const int s_begin = t0;   // the first tile also owns the gradient of the carried conv state
 #pragma unroll
       for (int k = 0; k < CONV_V; ++k) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          da[j][k] = 0.f;
-          wj[j][k] = (j >= 4 - W) ? to_f32(w[(size_t)(c + k) * W + (j - (4 - W))]) : 0.f;
-        }
-        bias[k] = p.bias ? to_f32(reinterpret_cast<const T*>(p.bias)[c + k]) : 0.f;
-        win[0][k] = 0.f;
+        for (int j = 0; j < 4; ++j) da[j][k] = 0.f;
+        win[0][k] = 0.f; bias[k] = 0.f;
       }
-      const int s_begin = t0;   // the first tile also owns the gradient of the carried conv state
+      if (W == 4 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
+        // the taps of the 4 channels are 16 contiguous values; bias is one 4-wide piece
+#pragma unroll
+        for (int k = 0; k < CONV_V; ++k) {
+          float q4[4];
+          load4<T>(w + (size_t)(c + k) * 4, q4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) wj[j][k] = q4[j];
+        }
+        if (p.bias) load4<T>(reinterpret_cast<const T*>(p.bias) + c, bias);
+      } else {
+#pragma unroll
+        for (int k = 0; k < CONV_V; ++k) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            wj[j][k] = (j >= 4 - W) ? to_f32(w[(size_t)(c + k) * W + (j - (4 - W))]) : 0.f;
+          bias[k] = p.bias ? to_f32(reinterpret_cast<const T*>(p.bias)[c + k]) : 0.f;
+        }
+      }
 #pragma unroll
       for (int r = 1; r < 4; ++r) {
         if (4 - r <= W - 1) load_xv<T>(p, x, st, b, s_begin - 4 + r, c, win[r]);
