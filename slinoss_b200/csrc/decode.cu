@@ -40,6 +40,45 @@ __global__ void __launch_bounds__(256) decode_kernel(
   __syncthreads();
   const float mr = M[bh * 2], mi = M[bh * 2 + 1];
   const bool vec4 = (N % 2) == 0;
+  if (D == 128 && (P % (8 * nw)) == 0) {
+    // N = 64: a state row is one float4 per lane.  A warp takes 8 consecutive rows at a time and
+    // issues all 8 loads before any arithmetic, so 4 KB per warp are in flight.
+    const float4 a = reinterpret_cast<const float4*>(s_bp)[lane];
+    const float4 c = reinterpret_cast<const float4*>(s_bc)[lane];
+    const float4 cc = reinterpret_cast<const float4*>(s_c)[lane];
+    for (int p0 = 8 * w; p0 < P; p0 += 8 * nw) {
+      float4 z[8];
+      float u[8], up[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        z[r] = reinterpret_cast<const float4*>(state_in + (bh * P + p0 + r) * D)[lane];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        u[r] = to_f32(U[bh * P + p0 + r]);
+        up[r] = Uprev ? to_f32(Uprev[bh * P + p0 + r]) : 0.f;
+      }
+      float acc[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        float4 o;
+        o.x = mr * z[r].x - mi * z[r].y + up[r] * a.x + u[r] * c.x;
+        o.y = mr * z[r].y + mi * z[r].x + up[r] * a.y + u[r] * c.y;
+        o.z = mr * z[r].z - mi * z[r].w + up[r] * a.z + u[r] * c.z;
+        o.w = mr * z[r].w + mi * z[r].z + up[r] * a.w + u[r] * c.w;
+        reinterpret_cast<float4*>(state_out + (bh * P + p0 + r) * D)[lane] = o;
+        acc[r] = cc.x * o.x + cc.y * o.y + cc.z * o.z + cc.w * o.w;
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) acc[r] = warp_sum(acc[r]);
+      if (lane < 8) {
+        float v = acc[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) v = lane == r ? acc[r] : v;
+        Y[bh * P + p0 + lane] = from_f32<TY>(v);
+      }
+    }
+    return;
+  }
 #pragma unroll 2
   for (int p = w; p < P; p += nw) {
     const float u = to_f32(U[bh * P + p]);
