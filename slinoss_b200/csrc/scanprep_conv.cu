@@ -15,6 +15,8 @@
 //
 // Backward mirrors the three kernels; parameter-bias and conv weight/bias
 // gradients are reduced per CTA and accumulated with float atomics.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace sl {
@@ -202,9 +204,9 @@ template <typename T, int V> __device__ __forceinline__ void storev(T* p, const 
   if constexpr (V == 4) store4<T>(p, v); else store16<T>(p, v);
 }
 
-// Forward: V = 8 channels per thread for 16-bit io (16-byte accesses), 4 for float32.
+// Forward (instantiated with V = CONV_V channels per thread).
 template <typename T, int V>
-__global__ void __launch_bounds__(256) value_fwd_vec_kernel(ValueParams p) {
+__global__ void __launch_bounds__(256, 3) value_fwd_vec_kernel(ValueParams p) {
   const int c = (blockIdx.x * 32 + (threadIdx.x & 31)) * V;
   const int t0 = (blockIdx.y * CONV_SUB + (threadIdx.x >> 5)) * CONV_TT, b = blockIdx.z;
   if (c >= p.C || t0 >= p.T) return;
@@ -269,10 +271,8 @@ __global__ void __launch_bounds__(256) value_fwd_vec_kernel(ValueParams p) {
       for (int q = 1; q < 4; ++q) win[q][k] = (4 - q <= p.W - 1) ? x_at(t0 - 4 + q, k) : 0.f;
     }
   }
-#pragma unroll 8
-  for (int t = t0; t < t1; ++t) {
-    float xin[V], o[V];
-    loadv<T, V>(xb + (size_t)t * p.xs, xin);
+  auto step = [&](int t, const float (&xin)[V]) {
+    float o[V];
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       win[0][k] = win[1][k]; win[1][k] = win[2][k]; win[2][k] = win[3][k]; win[3][k] = xin[k];
@@ -281,6 +281,32 @@ __global__ void __launch_bounds__(256) value_fwd_vec_kernel(ValueParams p) {
       o[k] = silu_f(a);
     }
     storev<T, V>(Ub + (size_t)t * p.ust, o);
+  };
+  if (t1 - t0 == CONV_TT) {
+    // full tile: batches of 8 tokens whose loads are all issued (unconditionally) before the first
+    // store of the batch - the compiler cannot move loads of x over stores to U by itself
+    constexpr int TB = 8;
+    using Raw = typename std::conditional<V * sizeof(T) == 16, uint4, uint2>::type;
+#pragma unroll 1
+    for (int tb = t0; tb < t1; tb += TB) {
+      Raw raw[TB];
+#pragma unroll
+      for (int i = 0; i < TB; ++i) raw[i] = *reinterpret_cast<const Raw*>(xb + (size_t)(tb + i) * p.xs);
+#pragma unroll
+      for (int i = 0; i < TB; ++i) {
+        float xin[V];
+        const T* e = reinterpret_cast<const T*>(&raw[i]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) xin[k] = to_f32(e[k]);
+        step(tb + i, xin);
+      }
+    }
+  } else {
+    for (int t = t0; t < t1; ++t) {
+      float xin[V];
+      loadv<T, V>(xb + (size_t)t * p.xs, xin);
+      step(t, xin);
+    }
   }
   if (p.state_out && t1 == p.T) {
     T* so = reinterpret_cast<T*>(p.state_out);
@@ -293,7 +319,7 @@ __global__ void __launch_bounds__(256) value_fwd_vec_kernel(ValueParams p) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) value_bwd_vec_kernel(ValueBwdParams q) {
+__global__ void __launch_bounds__(256, 2) value_bwd_vec_kernel(ValueBwdParams q) {
   const ValueParams& p = q.f;
   __shared__ float s_acc[CONV_SUB][5][32 * CONV_V];   // dw (4 taps) and dbias partials per sub-tile
   const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
@@ -361,14 +387,8 @@ __global__ void __launch_bounds__(256) value_bwd_vec_kernel(ValueBwdParams q) {
       }
       // s runs over the tokens whose da is formed; dx[s-3] is complete at step s
       const int s_end = min(t1 + 3, p.T + 3);
-#pragma unroll 4
-      for (int s = s_begin; s < s_end; ++s) {
-        float xin[CONV_V], gy[CONV_V], g[CONV_V];
-        const bool in = s < p.T;
-        if (in) {
-          load4<T>(x + ((size_t)b * p.T + s) * p.xs + c, xin);
-          load4<T>(dUb + (size_t)s * p.ust, gy);
-        }
+      auto step = [&](int s, bool in, const float (&xin)[CONV_V], const float (&gy)[CONV_V]) {
+        float g[CONV_V];
         const bool mine = s < t1;   // each token's weight / bias contribution is counted once
 #pragma unroll
         for (int k = 0; k < CONV_V; ++k) {
@@ -397,6 +417,41 @@ __global__ void __launch_bounds__(256) value_bwd_vec_kernel(ValueBwdParams q) {
 #pragma unroll
           for (int k = 0; k < CONV_V; ++k)
             reinterpret_cast<T*>(q.dstate)[((size_t)b * p.C + c + k) * (W - 1) + (W - 1 + t)] = from_f32<T>(g[k]);
+        }
+      };
+      if (s_end - s_begin == CONV_TT + 3 && s_end <= p.T) {
+        // full tile with its look-ahead inside the sequence: 35 steps as 5 batches of 7 whose loads
+        // are all issued (unconditionally) before the first store of the batch
+        constexpr int SB = 7;
+        static_assert((CONV_TT + 3) % SB == 0, "batching of the backward walk");
+#pragma unroll 1
+        for (int sb = s_begin; sb < s_end; sb += SB) {
+          using Raw = typename std::conditional<sizeof(T) == 4, uint4, uint2>::type;   // 4 channels
+          Raw xr[SB], gr[SB];
+#pragma unroll
+          for (int i = 0; i < SB; ++i) {
+            xr[i] = *reinterpret_cast<const Raw*>(x + ((size_t)b * p.T + sb + i) * p.xs + c);
+            gr[i] = *reinterpret_cast<const Raw*>(dUb + (size_t)(sb + i) * p.ust);
+          }
+#pragma unroll
+          for (int i = 0; i < SB; ++i) {
+            float xin[CONV_V], gy[CONV_V];
+            const T* ex = reinterpret_cast<const T*>(&xr[i]);
+            const T* eg = reinterpret_cast<const T*>(&gr[i]);
+#pragma unroll
+            for (int k = 0; k < CONV_V; ++k) { xin[k] = to_f32(ex[k]); gy[k] = to_f32(eg[k]); }
+            step(sb + i, true, xin, gy);
+          }
+        }
+      } else {
+        for (int s = s_begin; s < s_end; ++s) {
+          float xin[CONV_V], gy[CONV_V];
+          const bool in = s < p.T;
+          if (in) {
+            load4<T>(x + ((size_t)b * p.T + s) * p.xs + c, xin);
+            load4<T>(dUb + (size_t)s * p.ust, gy);
+          }
+          step(s, in, xin, gy);
         }
       }
     }
@@ -862,10 +917,10 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     p.state_out = conv_state_out; p.U = U; p.xs = value_row_stride;
     p.usb = u_stride_b; p.ush = u_stride_h; p.ust = u_stride_t;
     p.batch = batch; p.T = T; p.C = heads * P; p.P = P; p.W = conv_weight ? d_conv : 1;
-    const int vf = io_dtype == SL_F32 ? 4 : 8;   // channels per thread: 16-byte accesses
+    const int vf = CONV_V;   // 4 channels per thread (8- or 16-byte pieces)
     if (value_vec_ok(p, nullptr, nullptr, vf)) {
       dim3 grid((p.C + 32 * vf - 1) / (32 * vf), (T + CONV_SUB * CONV_TT - 1) / (CONV_SUB * CONV_TT), batch);
-      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_vec_kernel<Tt, Vec16<Tt>::N><<<grid, 256, 0, st>>>(p); });
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_vec_kernel<Tt, CONV_V><<<grid, 256, 0, st>>>(p); });
     } else {
       dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
       SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, st>>>(p); });
