@@ -184,10 +184,10 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_fwd_vec_kernel(TailParams p
   }
   // The raw 16-byte pieces of the NEXT row are fetched before the current row is reduced, so the
   // loads overlap the block reduction and the stores.
-  const long long rows = (long long)p.batch * p.T;
+  const unsigned rows = (unsigned)p.batch * (unsigned)p.T;   // < 2^31, checked by the launcher
   uint4 nY[TAIL_VIT], nG[TAIL_VIT], nS[TAIL_VIT];
-  auto fetch = [&](long long row) {
-    const int t = (int)(row % p.T), b = (int)(row / p.T);
+  auto fetch = [&](unsigned row) {
+    const int t = (int)(row % (unsigned)p.T), b = (int)(row / (unsigned)p.T);
 #pragma unroll
     for (int i = 0; i < TAIL_VIT; ++i) {
       const int c = (threadIdx.x + i * TAIL_THREADS) * V;
@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_fwd_vec_kernel(TailParams p
     }
   };
   if (blockIdx.x < rows) fetch(blockIdx.x);
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
     uint4 cY[TAIL_VIT], cG[TAIL_VIT], cS[TAIL_VIT];
 #pragma unroll
     for (int i = 0; i < TAIL_VIT; ++i) { cY[i] = nY[i]; cG[i] = nG[i]; cS[i] = nS[i]; }
@@ -269,10 +269,10 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_vec_kernel(TailParams p
       if (S) dsk[i] = p.d_skip[hh[i]];
     }
   }
-  const long long rows = (long long)p.batch * p.T;
+  const unsigned rows = (unsigned)p.batch * (unsigned)p.T;   // < 2^31, checked by the launcher
   uint4 nY[TAIL_VIT], nG[TAIL_VIT], nS[TAIL_VIT], nD[TAIL_VIT];
-  auto fetch = [&](long long row) {   // raw pieces of the next row, in flight while this one is reduced
-    const int t = (int)(row % p.T), b = (int)(row / p.T);
+  auto fetch = [&](unsigned row) {   // raw pieces of the next row, in flight while this one is reduced
+    const int t = (int)(row % (unsigned)p.T), b = (int)(row / (unsigned)p.T);
 #pragma unroll
     for (int i = 0; i < TAIL_VIT; ++i) {
       const int c = (threadIdx.x + i * TAIL_THREADS) * V;
@@ -286,8 +286,8 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_vec_kernel(TailParams p
     }
   };
   if (blockIdx.x < rows) fetch(blockIdx.x);
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const int t = (int)(row % p.T), b = (int)(row / p.T);
+  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int t = (int)(row % (unsigned)p.T), b = (int)(row / (unsigned)p.T);
     float pre[TAIL_VIT][V], sv[TAIL_VIT][V], g[TAIL_VIT][V], dnv[TAIL_VIT][V];
     float ss = 0.f, dot = 0.f;
 #pragma unroll
@@ -360,7 +360,7 @@ bool tail_vec_ok(const TailParams& p) {
   constexpr int V = Vec16<T>::N;
   const long long C = (long long)p.H * p.P;
   auto al = [](const void* q) { return q == nullptr || aligned(q, 16); };
-  return p.P % V == 0 && p.gs % V == 0 && C <= (long long)TAIL_VIT_MAX * TAIL_THREADS * V && al(p.Y) &&
+  return (long long)p.batch * p.T < (1ll << 31) && p.P % V == 0 && p.gs % V == 0 && C <= (long long)TAIL_VIT_MAX * TAIL_THREADS * V && al(p.Y) &&
          al(p.gate) && al(p.skip) && al(p.w) && al(p.dn) && al(p.normed) && al(p.dY) && al(p.dgate) &&
          al(p.dskip_in);
 }

@@ -627,8 +627,8 @@ __global__ void __launch_bounds__(256) bc_fwd_vec_kernel(const T* __restrict__ b
                                                          int G, int N, float eps) {
   constexpr bool FAST = sizeof(T) == 2;
   const int lane = threadIdx.x & 31, which = lane >> 4, n0 = 4 * (lane & 15);
-  const long long rows = (long long)batch * Tn * G;
-  const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * BC_RPW;
+  const unsigned rows = (unsigned)batch * (unsigned)Tn * (unsigned)G;   // < 2^31, checked by the launcher
+  const unsigned row0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * BC_RPW;
   if (row0 >= rows) return;
   const bool act = n0 < N;
   float amp[BC_RPW][4], ph[BC_RPW][4];
@@ -644,7 +644,7 @@ __global__ void __launch_bounds__(256) bc_fwd_vec_kernel(const T* __restrict__ b
   }
 #pragma unroll
   for (int r = 0; r < BC_RPW; ++r) {
-    const long long row = row0 + r;
+    const unsigned row = row0 + r;
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -662,9 +662,9 @@ __global__ void __launch_bounds__(256) bc_fwd_vec_kernel(const T* __restrict__ b
       const float a = amp[r][i] * inv;
       o[2 * i] = a * cs; o[2 * i + 1] = a * sn;
     }
-    const int g = (int)(row % G);
-    const long long bt = row / G;
-    const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+    const int g = (int)(row % (unsigned)G);
+    const unsigned bt = row / (unsigned)G;
+    const int t = (int)(bt % (unsigned)Tn), b = (int)(bt / (unsigned)Tn);
     T* dst = (which ? Co : Bo) + (((size_t)b * G + g) * Tn + t) * 2 * N + 2 * n0;
     store8<T>(dst, o);
   }
@@ -679,8 +679,8 @@ __global__ void __launch_bounds__(256) bc_bwd_vec_kernel(const T* __restrict__ b
   constexpr bool FAST = sizeof(T) == 2;
   constexpr int RPW = BC_RPW;
   const int lane = threadIdx.x & 31, which = lane >> 4, n0 = 4 * (lane & 15);
-  const long long rows = (long long)batch * Tn * G;
-  const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW;
+  const unsigned rows = (unsigned)batch * (unsigned)Tn * (unsigned)G;   // < 2^31, checked by the launcher
+  const unsigned row0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW;
   if (row0 >= rows) return;
   const bool act = n0 < N;
   float xa[RPW][4], xp[RPW][4], gr[RPW][8];
@@ -690,11 +690,11 @@ __global__ void __launch_bounds__(256) bc_bwd_vec_kernel(const T* __restrict__ b
     for (int i = 0; i < 4; ++i) { xa[r][i] = 0.f; xp[r][i] = 0.f; }
 #pragma unroll
     for (int i = 0; i < 8; ++i) gr[r][i] = 0.f;
-    const long long row = row0 + r;
+    const unsigned row = row0 + r;
     if (act && row < rows) {
-      const int g = (int)(row % G);
-      const long long bt = row / G;
-      const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+      const int g = (int)(row % (unsigned)G);
+      const unsigned bt = row / (unsigned)G;
+      const int t = (int)(bt % (unsigned)Tn), b = (int)(bt / (unsigned)Tn);
       const size_t off = (size_t)row * 4 * N + (size_t)(2 * which) * N + n0;
       load4<T>(bc + off, xa[r]);
       load4<T>(bc + off + N, xp[r]);
@@ -703,7 +703,7 @@ __global__ void __launch_bounds__(256) bc_bwd_vec_kernel(const T* __restrict__ b
   }
 #pragma unroll
   for (int r = 0; r < RPW; ++r) {
-    const long long row = row0 + r;
+    const unsigned row = row0 + r;
     float a[4], th[4], sn[4], cs[4];
     float ss = 0.f, gsum = 0.f;
 #pragma unroll
@@ -734,8 +734,8 @@ __global__ void __launch_bounds__(256) bc_bwd_vec_kernel(const T* __restrict__ b
   }
 }
 
-inline bool bc_vec_ok(int N, const void* a, const void* b, const void* c, const void* d) {
-  return N % 4 == 0 && N <= 64 && aligned(a, 16) && aligned(b, 16) && aligned(c, 16) &&
+inline bool bc_vec_ok(long long rows, int N, const void* a, const void* b, const void* c, const void* d) {
+  return rows < (1ll << 31) && N % 4 == 0 && N <= 64 && aligned(a, 16) && aligned(b, 16) && aligned(c, 16) &&
          (d == nullptr || aligned(d, 16));
 }
 
@@ -931,7 +931,7 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     if (!Bo || !Co || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    const bool vec = bc_vec_ok(N, bc, Bo, Co, nullptr);
+    const bool vec = bc_vec_ok(rows, N, bc, Bo, Co, nullptr);
     const unsigned nblk = vec ? (unsigned)((rows + 8 * BC_RPW - 1) / (8 * BC_RPW)) : blocks;
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
       auto k = vec ? bc_fwd_vec_kernel<Tt> : bc_fwd_kernel<Tt>;
@@ -992,7 +992,7 @@ extern "C" int sl_scanprep_conv_bwd(
     if (!dCo || !bc || !d_bc || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    const bool vec = bc_vec_ok(N, bc, dBo, dCo, d_bc);
+    const bool vec = bc_vec_ok(rows, N, bc, dBo, dCo, d_bc);
     const unsigned nblk = vec ? (unsigned)((rows + 8 * BC_RPW - 1) / (8 * BC_RPW)) : blocks;
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
       auto k = vec ? bc_bwd_vec_kernel<Tt> : bc_bwd_kernel<Tt>;
