@@ -67,8 +67,9 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+// (__fdividef: 2 ulp, and 0 for a denominator beyond 2^126, which is the right limit here)
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 // ---- host side -----------------------------------------------------------------
 inline size_t dtype_size(int dt) { return dt == SL_F32 ? 4 : 2; }
