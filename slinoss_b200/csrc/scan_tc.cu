@@ -43,10 +43,12 @@ constexpr uint32_t TILE = 8192;           // one [64][128 B] tile
 constexpr uint32_t STAGE = 7 * TILE;      // U | B0 | Zv0 | B1 | Zv1 | C0 | C1  (Zv written by the CTA)
 constexpr uint32_t OFF_KPP = 2 * STAGE;   // K'' (2 tiles)
 constexpr uint32_t OFF_S = OFF_KPP + 2 * TILE;
-constexpr uint32_t OFF_SCAL = OFF_S + TILE;
+constexpr uint32_t OFF_Y = OFF_S + TILE;  // 16-bit Y tile staged for its TMA store
+constexpr uint32_t OFF_SCAL = OFF_Y + TILE;
 constexpr int NSCAL = 12;                 // per-token float arrays
 constexpr uint32_t SMEM_BYTES = OFF_SCAL + 2 * NSCAL * 64 * 4 + 64 + 1024;
-constexpr uint32_t TMEM_COLS = 512;       // S 0..63 | Yoff 64..127 | Ydiag 128..191 | Inc 192..319
+// TMEM columns: [S | Yoff] 0..127 and 128..255 (chunk parity) | Ydiag 256..319 and 320..383 | Inc 384..511
+constexpr uint32_t TMEM_COLS = 512;
 
 __device__ int g_tc_status = 0;
 #ifdef SL_TC_TIMING

@@ -133,6 +133,54 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
 #define SL_TICK_MMA(i)
 #endif
 
+  // ---- output epilogue of chunk cp: y = Y_diag + exp(l_t) Y_off.  It runs one iteration late, in the gap
+  // while the [S | Yoff] MMAs of the next chunk execute (their accumulators alternate by chunk parity).
+  float et_keep = 0.f;   // exp(l_t) of this thread's row in the chunk whose output is still pending
+  auto output_epilogue = [&](int cp, bool live) {
+    if (live && !mbar_wait(&bar_mma[2], cp & 1)) { report_timeout(4); s_abort = 1; live = false; }
+    tc_fence_after_sync();
+    if (live) {
+      const int t0p = cp * L;
+      uint32_t yd[SC], yo[SC];
+      tmem_ld<SC>(tmem + lane_base + 256 + 64 * (cp & 1) + cg * SC, yd);
+      tmem_ld<SC>(tmem + lane_base + 128 * (cp & 1) + 64 + cg * SC, yo);
+      tmem_ld_wait();
+      const float et = et_keep;
+      if constexpr (sizeof(TY) == 2) {
+        if (act) {   // into the staging tile; rows beyond T are clipped by the store
+          using PY = Pack2<TY>;
+#pragma unroll
+          for (int v = 0; v < SC / 8; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = 8 * v + 2 * e;
+              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
+                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
+            }
+            *reinterpret_cast<uint4*>(smem + OFF_Y + sw128(row, cg * (SC / 8) + v)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      } else if (act && t0p + row < T) {
+        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0p + row) * 64 + cg * SC;
+#pragma unroll
+        for (int v = 0; v < SC / 4; ++v) {
+          float4 o;
+          o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
+          o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
+          o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
+          o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
+        }
+      }
+    }
+    if (Y_TMA) {   // the Y tile is complete once every worker warp has arrived
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_st);
+    }
+  };
+
   for (int c = 0; c < p.nchunks && ok; ++c) {
     SL_TICK(0)
     const int t0 = c * L;
@@ -151,6 +199,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       // they read: they arrive on named barriers 2 ("rotation done") and 4 ("S tile written") without
       // waiting and move on.
       const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
+      const uint32_t tSY = tmem + 128 * (c & 1), tYD = tmem + 256 + 64 * (c & 1), tINC = tmem + 384;
       bar_sync(2, NT + 64);   // rotation done: Q, K', K'' written; U landed; Zv tile stored by the previous chunk
       const bool go = lane == 0 && s_abort == 0;
       if (go) {
@@ -161,7 +210,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
           const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            umma(tmem, desc_adv(bC, (k >> 2) * TILE + (k & 3) * 32),
+            umma(tSY, desc_adv(bC, (k >> 2) * TILE + (k & 3) * 32),
                  desc_adv(bB, (k >> 2) * 2 * TILE + (k & 3) * 32), ID_S, k > 0);
           umma_commit(&bar_mma[0]);
         }
@@ -169,17 +218,24 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         const uint64_t bK = make_desc(aKPP, 8192, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma(tmem + 192, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
+          umma(tINC, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
         umma_commit(&bar_mma[1]);
         SL_TICK_MMA(3)
         if (c + 1 < p.nchunks) {   // next chunk's tiles, after the workers' burst
-          tma_store_wait_read();   // the Y store of the previous chunk read the U slot being refilled
+          // the stage being refilled held chunk c-1, whose last reader is its Y_diag MMA
+          if (!STATES_ONLY && c > 0 && !mbar_wait(&bar_mma[2], (c - 1) & 1)) { report_timeout(8); s_abort = 1; }
           issue_loads(c + 1);
         }
         if (p.states16) {   // the 16-bit state tile of this chunk is exactly what the backward wants
           tma_store_3d(&p.tmS, st + 2 * TILE, 0, c * 64, bh);
           tma_store_3d(&p.tmS, st + 4 * TILE, 64, c * 64, bh);
           tma_store_commit();
+        }
+        if (Y_TMA && c > 0) {   // the workers stage the Y tile of the PREVIOUS chunk while the MMAs above run
+          if (mbar_wait(&bar_st, (c - 1) & 1)) {
+            tma_store_3d(&p.tmY, smem + OFF_Y, 0, t0 - L, bh);
+            tma_store_commit();
+          } else { report_timeout(5); s_abort = 1; }
         }
       }
       __syncwarp();
@@ -190,19 +246,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
           const uint64_t bS = make_desc(aS, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)   // Y_diag = S U
-            umma(tmem + 128, desc_adv(bS, 32 * k), desc_adv(bU, 2048 * k), ID_Y, k > 0);
+            umma(tYD, desc_adv(bS, 32 * k), desc_adv(bU, 2048 * k), ID_Y, k > 0);
           umma_commit(&bar_mma[2]);
           SL_TICK_MMA(6)
-          if (Y_TMA) {   // the workers put the 16-bit Y tile over the (dead) U tile and signal
-            if (mbar_wait(&bar_st, c & 1)) {
-              tma_store_3d(&p.tmY, st, 0, t0, bh);
-              tma_store_commit();
-            } else { report_timeout(5); s_abort = 1; }
-          }
         }
-        // the state tiles stored above are overwritten by the workers in the next iteration: their
-        // store must have read them by then (the Y store, if any, may still be in flight)
-        if (Y_TMA) tma_store_wait_read_keep1(); else tma_store_wait_read();
+        // the state tiles and the Y tile stored in this iteration are overwritten by the workers in
+        // the next one: their stores must have read them by then (they were issued long ago)
+        tma_store_wait_read();
       }
       __syncwarp();
     } else {
@@ -257,7 +307,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     SL_TICK(2)
 
     if (!STATES_ONLY) {
-      // ---- [S | Yoff] and Inc MMAs are issued by the look-ahead warp --------------------------------
+      // ---- [S | Yoff] and Inc MMAs are issued by the issue warp; meanwhile the output of the previous
+      // chunk is finished ---------------------------------------------------------------------------------
+      if (c > 0) output_epilogue(c - 1, live);
+      live = live && s_abort == 0;
       if (live && !mbar_wait(&bar_mma[0], c & 1)) { report_timeout(2); s_abort = 1; live = false; }
       tc_fence_after_sync();
       SL_TICK(4)
@@ -265,8 +318,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       // ---- scores epilogue: decay, causal mask, diagonal -> 16-bit S tile ------------------------
       if (live) {
         uint32_t r[SC];
-        tmem_ld<SC>(tmem + lane_base + cg * SC, r);
+        tmem_ld<SC>(tmem + lane_base + 128 * (c & 1) + cg * SC, r);
         tmem_ld_wait();
+        et_keep = sc[1 * 64 + row];
         if (act) {
         const float lt = sc[row];
         const float dgv = s_diag[row];
@@ -299,7 +353,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       SL_TICK(5)
     }
 
-    // ---- state update first (Inc does not depend on the scores), the output epilogue after it ------
+    // ---- state update (hides the Y_diag MMAs; the output epilogue follows in the next iteration) ---------
     if (live && !mbar_wait(&bar_mma[1], c & 1)) { report_timeout(3); s_abort = 1; live = false; }
     tc_fence_after_sync();
     SL_TICK(7)
@@ -307,7 +361,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     if (live) {
       const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
       uint32_t inc[ZC];
-      tmem_ld<ZC>(tmem + lane_base + 192 + cg * ZC, inc);
+      tmem_ld<ZC>(tmem + lane_base + 384 + cg * ZC, inc);
       tmem_ld_wait();
       if (act) {
 #pragma unroll
@@ -320,50 +374,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       }
     }
     SL_TICK(8)
-    if (!STATES_ONLY && live && !mbar_wait(&bar_mma[2], c & 1)) { report_timeout(4); s_abort = 1; live = false; }
-    tc_fence_after_sync();
-    // ---- output epilogue: y = Y_diag + exp(l_t) Y_off -----------------------------------------------
-    if (!STATES_ONLY && live) {
-      uint32_t yd[SC], yo[SC];
-      tmem_ld<SC>(tmem + lane_base + 128 + cg * SC, yd);
-      tmem_ld<SC>(tmem + lane_base + 64 + cg * SC, yo);
-      tmem_ld_wait();
-      const float et = sc[1 * 64 + row];
-      if constexpr (sizeof(TY) == 2) {
-        if (act) {   // into the U tile (dead once Y_diag and Inc are done); rows beyond T are clipped by the store
-          using PY = Pack2<TY>;
-#pragma unroll
-          for (int v = 0; v < SC / 8; ++v) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 8 * v + 2 * e;
-              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
-                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
-            }
-            *reinterpret_cast<uint4*>(st + sw128(row, cg * (SC / 8) + v)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      } else if (act && t0 + row < T) {
-        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0 + row) * 64 + cg * SC;
-        {
-#pragma unroll
-          for (int v = 0; v < SC / 4; ++v) {
-            float4 o;
-            o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
-            o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
-            o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
-            o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
-          }
-        }
-      }
-    }
-    if (Y_TMA) {   // the Y tile is complete once every worker warp has arrived
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_st);
-    }
     SL_TICK(9)
     fence_async_smem();
     tc_fence_before_sync();
@@ -373,6 +383,16 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     SL_TICK(10)
   }
 
+  if (!STATES_ONLY && ok) {
+    if (worker) {
+      output_epilogue(p.nchunks - 1, true);
+    } else if (Y_TMA && warp == 4 * NW + 1 && lane == 0) {
+      if (mbar_wait(&bar_st, (p.nchunks - 1) & 1)) {
+        tma_store_3d(&p.tmY, smem + OFF_Y, 0, (p.nchunks - 1) * L, bh);
+        tma_store_commit();
+      } else { report_timeout(5); s_abort = 1; }
+    }
+  }
   if (ok && p.zfinal && act) {
     float* dst = p.zfinal + ((size_t)bh * 64 + row) * 128 + d0;
 #pragma unroll
