@@ -159,6 +159,63 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #define SL_TOCK_MMA(i)
 #endif
 
+  // ---- epilogue 5 of the chunk of iteration itp (run one iteration late): dz <- e^{l_end} dWv + dZ,
+  // and the anchor S = <dz, z> of the boundary below that chunk ------------------------------------------
+  float em_keep = 0.f;   // e^{l_end} of the chunk whose epilogue 5 is pending
+  auto epilogue5 = [&](int itp, bool live) {
+    const int cp = nC - 1 - itp;
+    const uint8_t* tZp = smem + (itp & 1) * B_STAGE + 6 * TILE;
+    if (live && !mbar_wait(&bar_mma[4], itp & 1)) { report_timeout(16); s_abort = 1; live = false; }
+    tc_fence_after_sync();
+    const float em = em_keep;
+    float ar = 0.f, ai = 0.f;
+    if (live) {
+#pragma unroll
+      for (int part = 0; part < ZC / PC; ++part) {
+        uint32_t zi[PC];
+        tmem_ld<PC>(tmem + lane_base + 384 + d0 + PC * part, zi);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < PC / 8; ++ch) {
+          const uint4 zv4 = *reinterpret_cast<const uint4*>(tZp + hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch));
+          const uint32_t zw[4] = {zv4.x, zv4.y, zv4.z, zv4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = 8 * ch + 2 * e, jj = PC * part + j;
+            const float da = em * dz[jj] + __uint_as_float(zi[j]);
+            const float db = em * dz[jj + 1] + __uint_as_float(zi[j + 1]);
+            dz[jj] = da; dz[jj + 1] = db;
+            const float2 z = PK::unpack(zw[e]);   // (a, b): z = a - i b ; dz = da - i db
+            ar += da * z.x + db * z.y;            // dz conj(z)
+            ai += da * z.y - db * z.x;
+          }
+        }
+      }
+    }
+    float sr, si;
+    block_sum2(ar, ai, sr, si);
+    if (tid == 0 && cp > 0 && live) p.anchor[(size_t)bh * nC + cp - 1] = make_float2(sr, si);
+  };
+  // ---- dWv tile of a chunk: dz rotated by the unit phase of Pi_end: (a,b) -> (ur a - ui b, ui a + ur b),
+  // and the row e^{l_end - l_t} of that chunk ------------------------------------------------------------------
+  auto make_dwv = [&](const float* sc) {
+    const float ur = sc[10 * 64 + 2], ui = sc[10 * 64 + 3];
+    if (tid < 64) sw[0 * 64 + tid] = __expf(fminf(sc[63] - sc[tid], 0.f));
+    uint8_t* dw = smem + B_OFF_DW + hf * TILE;
+#pragma unroll
+    for (int ch = 0; ch < ZC / 8; ++ch) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float a = dz[8 * ch + 2 * e], bq = dz[8 * ch + 2 * e + 1];
+        const float na = ur * a - ui * bq, nb = ui * a + ur * bq;
+        dz[8 * ch + 2 * e] = na; dz[8 * ch + 2 * e + 1] = nb;
+        w[e] = PK::pack(na, nb);
+      }
+      *reinterpret_cast<uint4*>(dw + sw128(row, d0 / 8 + ch)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  };
+
   for (int it = 0; it < nC && ok; ++it) {
     const int c = nC - 1 - it, t0 = c * L;
     SL_TOCK(0)
@@ -205,7 +262,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       } while (false);
       __syncwarp();
-      // (2) products of rotated tiles, once the workers' passes are done (Q, K', dYoff, dWv written)
+      // (2) products of rotated tiles, once the workers' passes are done (Q, K', dYoff written)
       bar_sync(2, NT + 64);
       if (go && s_abort == 0) {
         tc_fence_after_sync();
@@ -221,7 +278,14 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
         umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
         SL_TOCK_MMA(6)
-        if (it + 1 < nC) {   // next chunk's tiles (after the workers' burst at the top of the iteration)
+      }
+      __syncwarp();
+      // (2b) once the workers have finished epilogue 5 of the previous chunk (the Zv tiles of the other
+      // stage are free) and written this chunk's dWv
+      bar_sync(6, NT + 32);
+      if (go && s_abort == 0) {
+        tc_fence_after_sync();
+        if (it + 1 < nC) {   // next chunk's tiles
           tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
           issue_loads(c - 1, it + 1);
         }
@@ -299,28 +363,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       __syncwarp();
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
-    // ---- dWv tile: dz rotated by the unit phase of Pi_end:  (a,b) -> (ur a - ui b, ui a + ur b) ----
-    {
-      const float ur = sc[10 * 64 + 2], ui = sc[10 * 64 + 3];
-#ifdef SL_TC_TIMING
-      if (bh == 0 && tid == 0 && it == 8) { g_tc_timing[19] = clock64() + (ur + ui == 123.f); }
-#endif
-      if (tid < 64) sw[0 * 64 + tid] = __expf(fminf(sc[63] - sc[tid], 0.f));
-      SL_TOCK(20)
-      uint8_t* dw = smem + B_OFF_DW + hf * TILE;
-#pragma unroll
-      for (int ch = 0; ch < ZC / 8; ++ch) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = dz[8 * ch + 2 * e], bq = dz[8 * ch + 2 * e + 1];
-          const float na = ur * a - ui * bq, nb = ui * a + ur * bq;
-          dz[8 * ch + 2 * e] = na; dz[8 * ch + 2 * e + 1] = nb;
-          w[e] = PK::pack(na, nb);
-        }
-        *reinterpret_cast<uint4*>(dw + sw128(row, d0 / 8 + ch)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
     SL_TOCK(16)
     if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(11); s_abort = 1; live = false; }
     SL_TOCK(1)
@@ -395,6 +437,15 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     bar_arrive(2, NT + 64);      // ... the scalar and issue warps are told without being waited for
     live = s_abort == 0;
     SL_TOCK(5)
+    // ---- in the shadow of the P~ MMAs: epilogue 5 of the previous iteration, then this chunk's dWv ------
+    if (it > 0) epilogue5(it - 1, live);
+    live = live && s_abort == 0;
+    if (live) make_dwv(sc);
+    em_keep = sc[1 * 64 + 63];
+    fence_async_smem();
+    tc_fence_before_sync();
+    bar_sync(3, NT);
+    bar_arrive(6, NT + 32);      // dWv written, the previous dZ accumulator and Zv tiles released
 
     // ---- MMA group 1 (issued by the look-ahead warp): P~ = Q K'^T, dS = dY U^T ------------------------
     if (live && !mbar_wait(&bar_mma[0], it & 1)) { report_timeout(12); s_abort = 1; live = false; }
@@ -553,42 +604,12 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     __syncwarp();
     if (lane == 0) mbar_arrive(&bar_st[2]);
     SL_TOCK(13)
-    if (live && !mbar_wait(&bar_mma[4], it & 1)) { report_timeout(16); s_abort = 1; live = false; }
-    tc_fence_after_sync();
-    // ---- epilogue 5: dz <- e^{l_end} dWv + dZ ; anchor of the boundary below ----------------------------------
-    {
-      const float em = sc[1 * 64 + 63];
-      float ar = 0.f, ai = 0.f;
-      if (live) {
-#pragma unroll
-      for (int part = 0; part < ZC / PC; ++part) {
-        uint32_t zi[PC];
-        tmem_ld<PC>(tmem + lane_base + 384 + d0 + PC * part, zi);
-        tmem_ld_wait();
-#pragma unroll
-        for (int ch = 0; ch < PC / 8; ++ch) {
-          const uint4 zv4 = *reinterpret_cast<const uint4*>(tZ + hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch));
-          const uint32_t zw[4] = {zv4.x, zv4.y, zv4.z, zv4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = 8 * ch + 2 * e, jj = PC * part + j;
-            const float da = em * dz[jj] + __uint_as_float(zi[j]);
-            const float db = em * dz[jj + 1] + __uint_as_float(zi[j + 1]);
-            dz[jj] = da; dz[jj + 1] = db;
-            const float2 z = PK::unpack(zw[e]);   // (a, b): z = a - i b ; dz = da - i db
-            ar += da * z.x + db * z.y;            // dz conj(z)
-            ai += da * z.y - db * z.x;
-          }
-        }
-      }
-      }
-      float sr, si;
-      block_sum2(ar, ai, sr, si);   // contains two barriers: also orders the table writes above
-      // the proxy fence for this iteration's shared-memory accesses goes BEFORE the global stores
-      // below (the code after them touches no tile)
-      fence_async_smem();
-      if (tid == 0 && c > 0) p.anchor[(size_t)bh * nC + c - 1] = make_float2(sr, si);
-    }
+    // (epilogue 5 of this chunk - the update of dz - runs in the next iteration, in the shadow of the
+    // P~ MMAs; its inputs, the dZ accumulator and the Zv tiles of this stage, stay untouched until then)
+    bar_sync(1, NT);   // the partial sums written by epilogues 2 and 3 are read by other threads below
+    // the proxy fence for this iteration's shared-memory accesses goes BEFORE the global stores
+    // below (the code after them touches no tile)
+    fence_async_smem();
     SL_TOCK(14)
     // ---- per-token scalars of this chunk ---------------------------------------------------------------------
     if (live && tid < 64 && t0 + tid < T) {
@@ -613,6 +634,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     if (s_abort) { ok = false; break; }
   }
 
+  if (ok && worker) epilogue5(nC - 1, true);
+  ok = ok && s_abort == 0;
   if (ok && p.dinit && worker) {
     float* dst = p.dinit + ((size_t)bh * 64 + row) * 128 + 64 * hf + d0;
 #pragma unroll
