@@ -408,14 +408,12 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
         const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
         uint32_t qo[4], ko[4];
-        float dg = 0.f, cbr = 0.f, cbi = 0.f;
+        float cbr = 0.f, cbi = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
           qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
           ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
-          const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
-          dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
           cbr += cc.x * bb.x + cc.y * bb.y;                                       // c conj(b)
           cbi += cc.y * bb.x - cc.x * bb.y;
         }
@@ -423,11 +421,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         *reinterpret_cast<uint4*>(smem + B_OFF_KP + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
-          dg += __shfl_xor_sync(0xffffffffu, dg, o);
           cbr += __shfl_xor_sync(0xffffffffu, cbr, o);
           cbi += __shfl_xor_sync(0xffffffffu, cbi, o);
         }
-        if (rcol == 0) { sw[2 * 64 + r] = dg; sw[3 * 64 + r] = cbr; sw[4 * 64 + r] = cbi; }
+        // diagonal term Re sum conj(c) kc b = Re(kc conj(sum c conj(b)))
+        if (rcol == 0) { sw[2 * 64 + r] = kr * cbr + ki * cbi; sw[3 * 64 + r] = cbr; sw[4 * 64 + r] = cbi; }
       }
     }
     SL_TOCK(4)
