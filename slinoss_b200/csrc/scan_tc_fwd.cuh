@@ -2,19 +2,22 @@
 //
 // NW = warps per TMEM lane quadrant (2 or 4).  The CTA has 4*NW worker warps; warp w reads TMEM
 // lanes 32*(w & 3) .. +31 (a hardware rule) and, inside every accumulator, the column group
-// (w >> 2) of NW.  All MMAs have M = 64, whose rows live in lanes 0..15 of every quadrant, so in
-// the epilogues lane i < 16 of warp (quad, cg) owns row 16*quad + i and 1/NW of the columns;
-// the upper half-warp only takes part in the rotation pass.  Every tcgen05.mma costs the issuing
-// thread ~50 cycles whatever its N, so operands are laid out for few, wide instructions:
-// [K' ; Zv] is one 128-row B operand (scores and off-term in one MMA per k-step) and K'' is one
-// 128-column MN-major operand.
+// (w >> 2) of NW.  All MMAs have M = 64, whose rows live in lanes 0..15 of every quadrant.  The
+// epilogues read them with the 16x256b shape of tcgen05.ld, which spreads those 16 lanes over all
+// 32 threads of the warp: thread t owns rows 16*quad + t/4 and + 8 and, in every block of 8
+// columns, the column pair 2*(t%4), 2*(t%4)+1 - a complex pair stays inside one thread.  Every
+// tcgen05.mma costs the tensor pipe >= 44 cycles whatever its N, so operands are laid out for few,
+// wide instructions: [K' ; Zv] is one 128-row B operand (scores and off-term in one MMA per
+// k-step) and K'' is one 128-column MN-major operand.
 //
 // STATES_ONLY: the state pre-sweep of the backward pass (no C, no scores, no Y).
 template <typename TIn, typename TY, bool STATES_ONLY, int NW>
 __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
   constexpr int NT = 128 * NW;  // worker threads; two more warps: per-chunk scalars, TMA + MMA issue
-  constexpr int ZC = 128 / NW;  // state columns per active thread (pairs stay inside a thread)
-  constexpr int SC = 64 / NW;   // score / output columns per active thread
+  constexpr int ZC = 128 / NW;  // state columns per warp
+  constexpr int SC = 64 / NW;   // score / output columns per warp
+  constexpr int SB = SC / 8;    // 8-column blocks of a score / output group
+  constexpr int ZB = ZC / 8;    // 8-column blocks of a state group: 2 ZB state values per thread and row
   constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -29,8 +32,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool worker = warp < 4 * NW;     // warp 4 NW runs chunk_scalars one chunk ahead, warp 4 NW + 1 issues
   const int quad = warp & 3, cg = worker ? (warp >> 2) : 0;
-  const int row = 16 * quad + (lane & 15);                   // epilogue identity
-  const bool act = worker && lane < 16;                      // rows of M = 64 accumulators
+  const int rowA = 16 * quad + (lane >> 2), rowB = rowA + 8;  // epilogue identity: two rows ...
+  const int cq = lane & 3;                                    // ... and one column pair per 8-column block
   const int rcol = tid & 15, rrow0 = tid >> 4;               // rotation identity
   const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
   const int bh = blockIdx.x, b = bh / p.heads, h = bh % p.heads;
@@ -70,53 +73,53 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   if (tid == 0) issue_loads(0);
 
   // ---- carried state, conjugated: zv[2j], zv[2j+1] = (re, -im) of column pair j of this thread ----
-  const int d0 = cg * ZC;             // first state column (0..127) of this thread
-  float zv[ZC];
+  const int d0 = cg * ZC;             // first state column (0..127) of this warp
+  // zv[4 i + 2 h + k]: block i, row (h ? rowB : rowA), k = 0 real part, 1 minus the imaginary part
+  float zv[4 * ZB];
 #pragma unroll
-  for (int j = 0; j < ZC; ++j) zv[j] = 0.f;
-  if (act) {
+  for (int j = 0; j < 4 * ZB; ++j) zv[j] = 0.f;
+  if (worker) {
     const TIn* Bp = reinterpret_cast<const TIn*>(p.Bprev);
     const TIn* Up = reinterpret_cast<const TIn*>(p.Uprev);
-    float cr = 0.f, ci = 0.f, up = 0.f;
+    float cr = 0.f, ci = 0.f, up[2] = {0.f, 0.f};
     if (Bp) {  // pending prev-tap of the token before the sequence: u_prev (x) (kp_0 / m_0) b_prev
       const float mr = Mb[0], mi = Mb[1], kr = Kb[0], ki = Kb[1];
       const float den = mr * mr + mi * mi;
       cr = (kr * mr + ki * mi) / den; ci = (ki * mr - kr * mi) / den;
-      up = to_f32(Up[(size_t)bh * 64 + row]);
+      up[0] = to_f32(Up[(size_t)bh * 64 + rowA]);
+      up[1] = to_f32(Up[(size_t)bh * 64 + rowB]);
     }
 #pragma unroll
-    for (int j = 0; j < ZC / 2; ++j) {
-      const int d = d0 + 2 * j;
-      float re = 0.f, im = 0.f;
-      if (p.z0) {
-        const float2 z = *reinterpret_cast<const float2*>(p.z0 + ((size_t)bh * 64 + row) * 128 + d);
-        re = z.x; im = z.y;
+    for (int i = 0; i < ZB; ++i) {
+      const int d = d0 + 8 * i + 2 * cq;
+      float br = 0.f, bi = 0.f;
+      if (Bp) { br = to_f32(Bp[(size_t)bg * 128 + d]); bi = to_f32(Bp[(size_t)bg * 128 + d + 1]); }
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float re = 0.f, im = 0.f;
+        if (p.z0) {
+          const float2 z = *reinterpret_cast<const float2*>(p.z0 + ((size_t)bh * 64 + (hh ? rowB : rowA)) * 128 + d);
+          re = z.x; im = z.y;
+        }
+        re += up[hh] * (cr * br - ci * bi);
+        im += up[hh] * (cr * bi + ci * br);
+        zv[4 * i + 2 * hh] = re; zv[4 * i + 2 * hh + 1] = -im;
       }
-      if (Bp) {
-        const float br = to_f32(Bp[(size_t)bg * 128 + d]), bi = to_f32(Bp[(size_t)bg * 128 + d + 1]);
-        re += up * (cr * br - ci * bi);
-        im += up * (cr * bi + ci * br);
-      }
-      zv[2 * j] = re; zv[2 * j + 1] = -im;
     }
   }
-  auto pack8 = [&](int ch) {
-    uint4 v;
-    v.x = PK::pack(zv[8 * ch + 0], zv[8 * ch + 1]); v.y = PK::pack(zv[8 * ch + 2], zv[8 * ch + 3]);
-    v.z = PK::pack(zv[8 * ch + 4], zv[8 * ch + 5]); v.w = PK::pack(zv[8 * ch + 6], zv[8 * ch + 7]);
-    return v;
-  };
   // 16-bit copy of the state for chunk c: rows p, K-major along d, in the Zv slots of stage c & 1
   // (directly below the K' rows, so that [K' ; Zv] is one 128-row operand)
   auto store_zv_tile = [&](int c) {
     uint8_t* stg = smem + (c & 1) * STAGE;
 #pragma unroll
-    for (int ch = 0; ch < ZC / 8; ++ch) {
-      const int ci = d0 / 8 + ch;   // 16-byte chunk index along d (0..15)
-      *reinterpret_cast<uint4*>(stg + (2 + 2 * (ci >> 3)) * TILE + sw128(row, ci & 7)) = pack8(ch);
+    for (int i = 0; i < ZB; ++i) {
+      const int ci = d0 / 8 + i;   // 16-byte chunk index along d (0..15)
+      uint8_t* tile = stg + (2 + 2 * (ci >> 3)) * TILE + 4 * cq;
+      *reinterpret_cast<uint32_t*>(tile + sw128(rowA, ci & 7)) = PK::pack(zv[4 * i], zv[4 * i + 1]);
+      *reinterpret_cast<uint32_t*>(tile + sw128(rowB, ci & 7)) = PK::pack(zv[4 * i + 2], zv[4 * i + 3]);
     }
   };
-  if (act) store_zv_tile(0);
+  if (worker) store_zv_tile(0);
   if (warp == 4 * NW) chunk_scalars(sc_tab, Mb, Kb, 0, T, lane);
   __syncthreads();
 
@@ -135,42 +138,30 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
 
   // ---- output epilogue of chunk cp: y = Y_diag + exp(l_t) Y_off.  It runs one iteration late, in the gap
   // while the [S | Yoff] MMAs of the next chunk execute (their accumulators alternate by chunk parity).
-  float et_keep = 0.f;   // exp(l_t) of this thread's row in the chunk whose output is still pending
+  float et_keep[2] = {0.f, 0.f};   // exp(l_t) of this thread's two rows in the chunk whose output is pending
   auto output_epilogue = [&](int cp, bool live) {
     if (live && !mbar_wait(&bar_mma[2], cp & 1)) { report_timeout(4); s_abort = 1; live = false; }
     tc_fence_after_sync();
     if (live) {
       const int t0p = cp * L;
-      uint32_t yd[SC], yo[SC];
-      tmem_ld<SC>(tmem + lane_base + 256 + 64 * (cp & 1) + cg * SC, yd);
-      tmem_ld<SC>(tmem + lane_base + 128 * (cp & 1) + 64 + cg * SC, yo);
+      uint32_t yd[4 * SB], yo[4 * SB];
+      tmem_ld_16x256<SB>(tmem + lane_base + 256 + 64 * (cp & 1) + cg * SC, yd);
+      tmem_ld_16x256<SB>(tmem + lane_base + 128 * (cp & 1) + 64 + cg * SC, yo);
       tmem_ld_wait();
-      const float et = et_keep;
-      if constexpr (sizeof(TY) == 2) {
-        if (act) {   // into the staging tile; rows beyond T are clipped by the store
-          using PY = Pack2<TY>;
 #pragma unroll
-          for (int v = 0; v < SC / 8; ++v) {
-            uint32_t w[4];
+      for (int i = 0; i < SB; ++i) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 8 * v + 2 * e;
-              w[e] = PY::pack(__uint_as_float(yd[j]) + et * __uint_as_float(yo[j]),
-                              __uint_as_float(yd[j + 1]) + et * __uint_as_float(yo[j + 1]));
-            }
-            *reinterpret_cast<uint4*>(smem + OFF_Y + sw128(row, cg * (SC / 8) + v)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int hh = 0; hh < 2; ++hh) {
+          const int R = hh ? rowB : rowA;
+          const float et = hh ? et_keep[1] : et_keep[0];
+          const float y0 = __uint_as_float(yd[4 * i + 2 * hh]) + et * __uint_as_float(yo[4 * i + 2 * hh]);
+          const float y1 = __uint_as_float(yd[4 * i + 2 * hh + 1]) + et * __uint_as_float(yo[4 * i + 2 * hh + 1]);
+          if constexpr (sizeof(TY) == 2) {   // into the staging tile; rows beyond T are clipped by the store
+            *reinterpret_cast<uint32_t*>(smem + OFF_Y + sw128(R, cg * SB + i) + 4 * cq) = Pack2<TY>::pack(y0, y1);
+          } else if (t0p + R < T) {
+            float* dst = reinterpret_cast<float*>(p.Y) + ((size_t)bh * T + t0p + R) * 64 + cg * SC + 8 * i + 2 * cq;
+            *reinterpret_cast<float2*>(dst) = make_float2(y0, y1);
           }
-        }
-      } else if (act && t0p + row < T) {
-        TY* dst = reinterpret_cast<TY*>(p.Y) + ((size_t)bh * T + t0p + row) * 64 + cg * SC;
-#pragma unroll
-        for (int v = 0; v < SC / 4; ++v) {
-          float4 o;
-          o.x = __uint_as_float(yd[4 * v]) + et * __uint_as_float(yo[4 * v]);
-          o.y = __uint_as_float(yd[4 * v + 1]) + et * __uint_as_float(yo[4 * v + 1]);
-          o.z = __uint_as_float(yd[4 * v + 2]) + et * __uint_as_float(yo[4 * v + 2]);
-          o.w = __uint_as_float(yd[4 * v + 3]) + et * __uint_as_float(yo[4 * v + 3]);
-          *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * v) = o;
         }
       }
     }
@@ -317,32 +308,27 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
 
       // ---- scores epilogue: decay, causal mask, diagonal -> 16-bit S tile ------------------------
       if (live) {
-        uint32_t r[SC];
-        tmem_ld<SC>(tmem + lane_base + 128 * (c & 1) + cg * SC, r);
+        uint32_t r[4 * SB];
+        tmem_ld_16x256<SB>(tmem + lane_base + 128 * (c & 1) + cg * SC, r);
         tmem_ld_wait();
-        et_keep = sc[1 * 64 + row];
-        if (act) {
-        const float lt = sc[row];
-        const float dgv = s_diag[row];
-        uint8_t* tS = smem + OFF_S;
+        et_keep[0] = sc[1 * 64 + rowA]; et_keep[1] = sc[1 * 64 + rowB];
+        uint8_t* tS = smem + OFF_S + 4 * cq;
 #pragma unroll
-        for (int ch = 0; ch < SC / 8; ++ch) {
-          uint32_t w[4];
+        for (int hh = 0; hh < 2; ++hh) {
+          const int R = hh ? rowB : rowA;
+          const float lt = sc[R], dgv = s_diag[R];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+          for (int i = 0; i < SB; ++i) {
             float v2[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-              const int j = 8 * ch + 2 * e + q, s = cg * SC + j;
-              float v = __uint_as_float(r[j]) * __expf(fminf(lt - sc[s], 0.f));
-              v = s < row ? v : (s == row ? dgv : 0.f);
+              const int s = cg * SC + 8 * i + 2 * cq + q;
+              float v = __uint_as_float(r[4 * i + 2 * hh + q]) * __expf(fminf(lt - sc[s], 0.f));
+              v = s < R ? v : (s == R ? dgv : 0.f);
               v2[q] = v;
             }
-            w[e] = PK::pack(v2[0], v2[1]);
+            *reinterpret_cast<uint32_t*>(tS + sw128(R, cg * SB + i)) = PK::pack(v2[0], v2[1]);
           }
-          *reinterpret_cast<uint4*>(tS + sw128(row, cg * (SC / 8) + ch)) =
-              make_uint4(w[0], w[1], w[2], w[3]);
-        }
         }
       }
       fence_async_smem();
@@ -360,18 +346,19 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     // ---- state update: zv = conj(Pi_end) zv + Inc ---------------------------------------------------
     if (live) {
       const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
-      uint32_t inc[ZC];
-      tmem_ld<ZC>(tmem + lane_base + 384 + cg * ZC, inc);
-      tmem_ld_wait();
-      if (act) {
 #pragma unroll
-        for (int j = 0; j < ZC / 2; ++j) {
-          const float a = zv[2 * j], bq = zv[2 * j + 1];
-          zv[2 * j] = pr * a + pi * bq + __uint_as_float(inc[2 * j]);
-          zv[2 * j + 1] = pr * bq - pi * a + __uint_as_float(inc[2 * j + 1]);
+      for (int part = 0; part < ZB / 4; ++part) {
+        uint32_t inc[16];
+        tmem_ld_16x256<4>(tmem + lane_base + 384 + d0 + 32 * part, inc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {   // 8 complex values: 4 blocks x 2 rows
+          const float a = zv[16 * part + 2 * j], bq = zv[16 * part + 2 * j + 1];
+          zv[16 * part + 2 * j] = pr * a + pi * bq + __uint_as_float(inc[2 * j]);
+          zv[16 * part + 2 * j + 1] = pr * bq - pi * a + __uint_as_float(inc[2 * j + 1]);
         }
-        store_zv_tile(c + 1);
       }
+      store_zv_tile(c + 1);
     }
     SL_TICK(8)
     SL_TICK(9)
@@ -393,12 +380,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       } else { report_timeout(5); s_abort = 1; }
     }
   }
-  if (ok && p.zfinal && act) {
-    float* dst = p.zfinal + ((size_t)bh * 64 + row) * 128 + d0;
+  if (ok && p.zfinal && worker) {
 #pragma unroll
-    for (int j = 0; j < ZC / 4; ++j)
-      *reinterpret_cast<float4*>(dst + 4 * j) =
-          make_float4(zv[4 * j], -zv[4 * j + 1], zv[4 * j + 2], -zv[4 * j + 3]);
+    for (int i = 0; i < ZB; ++i) {
+      const int d = d0 + 8 * i + 2 * cq;
+      *reinterpret_cast<float2*>(p.zfinal + ((size_t)bh * 64 + rowA) * 128 + d) = make_float2(zv[4 * i], -zv[4 * i + 1]);
+      *reinterpret_cast<float2*>(p.zfinal + ((size_t)bh * 64 + rowB) * 128 + d) = make_float2(zv[4 * i + 2], -zv[4 * i + 3]);
+    }
   }
   // unwind: nothing of ours may still be in flight when shared memory / TMEM are released
   if (!ok && tid == 0) {

@@ -214,6 +214,32 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x (8 NB) columns spread over all 32 threads of the warp (the shape for M = 64
+// accumulators, whose rows sit in lanes 0..15 of a quadrant): thread t receives, for every
+// 8-column block i < NB, rows t/4 and t/4 + 8 at columns 8 i + 2 (t%4) and + 1:
+//   r[4 i + 0], r[4 i + 1] = row t/4     ;   r[4 i + 2], r[4 i + 3] = row t/4 + 8
+template <int NB>
+__device__ __forceinline__ void tmem_ld_16x256(uint32_t taddr, uint32_t (&r)[4 * NB]) {
+  static_assert(NB == 1 || NB == 2 || NB == 4, "unsupported block count");
+  if constexpr (NB == 1) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+  } else if constexpr (NB == 2) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+  }
+}
 // N consecutive columns, N in {8, 16, 32, 64}
 template <int N>
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]) {
