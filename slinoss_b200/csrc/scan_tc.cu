@@ -203,7 +203,7 @@ size_t scan_tc_bwd_workspace(const ScanDims& d) {
   return std::max(scan_simt_bwd_workspace(d), tc_bwd_layout(d).total);
 }
 
-int g_tc_nw = 4;   // warps per TMEM lane quadrant (tuning knob: 1, 2 or 4)
+int g_tc_nw = 4;   // warps per TMEM lane quadrant (tuning knob: 2 or 4)
 
 template <typename TIn, typename TY, bool STATES_ONLY, int NW>
 static int launch_tc_fwd_nw(const TcFwdParams& p, int grid, cudaStream_t st) {
@@ -314,12 +314,10 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   p.dinit = dinit; p.T = d.T; p.nchunks = nC;
   int rc = SL_ERR_UNSUPPORTED;
   if (bf) {
-    rc = g_tc_nw == 1 ? launch_tc_bwd<__nv_bfloat16, 1>(p, (int)BH, st)
-       : g_tc_nw == 2 ? launch_tc_bwd<__nv_bfloat16, 2>(p, (int)BH, st)
+    rc = g_tc_nw == 2 ? launch_tc_bwd<__nv_bfloat16, 2>(p, (int)BH, st)
                       : launch_tc_bwd<__nv_bfloat16, 4>(p, (int)BH, st);
   } else {
-    rc = g_tc_nw == 1 ? launch_tc_bwd<__half, 1>(p, (int)BH, st)
-       : g_tc_nw == 2 ? launch_tc_bwd<__half, 2>(p, (int)BH, st)
+    rc = g_tc_nw == 2 ? launch_tc_bwd<__half, 2>(p, (int)BH, st)
                       : launch_tc_bwd<__half, 4>(p, (int)BH, st);
   }
   if (rc != SL_OK) return rc;
@@ -337,7 +335,7 @@ extern "C" __attribute__((visibility("default"))) void sl_dbg_timing(long long* 
 }
 #endif
 
-void scan_tc_set_warps(int nw) { g_tc_nw = (nw == 1 || nw == 2) ? nw : 4; }
+void scan_tc_set_warps(int nw) { g_tc_nw = nw == 2 ? 2 : 4; }
 
 int scan_tc_device_status() {
   int v = 0;

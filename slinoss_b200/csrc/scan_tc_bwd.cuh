@@ -26,7 +26,9 @@ constexpr uint32_t B_OFF_DW = B_OFF_DP + TILE;         // dWv (2)
 constexpr uint32_t B_OFF_SCAL = B_OFF_DW + 2 * TILE;
 constexpr int B_NSCAL = 2 * 11 + 5 + 32;   // 2 x 11 look-ahead rows, 5 worker rows, 4 x 8 partial sums
 constexpr uint32_t B_SMEM_BYTES = B_OFF_SCAL + B_NSCAL * 64 * 4 + 1024;
-// TMEM columns: P~ 0 | dS 32 | dQa 64 | dQb 128 | dXa 192 | dXb 256 | dUa 320 | dUb 352 | dZ 384
+// TMEM columns: P~ 0 | dS 64 | dQ 128 | dXa 192 | dXb 256 | dUa 320 | dUb 384 | dZ 448.  P~, dS, dUa and dUb are
+// single N = 64 products (rows in lanes 0..15 of a quadrant, read with the 16x256b load shape); dQ, dX and dZ
+// are two N-halves each, the second at TMEM lane offset 16 (read with the 32x32b shape).
 constexpr uint32_t B_TMEM_COLS = 512;
 
 struct alignas(64) TcBwdParams {
@@ -68,6 +70,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   const bool worker = warp < 4 * NW;
   const int quad = warp & 3, cg = worker ? (warp >> 2) : 0;
   const int row = 16 * quad + (lane & 15), hf = lane >> 4;
+  const int rowA = 16 * quad + (lane >> 2), rowB = rowA + 8, cq = lane & 3;   // identity for the 16x256b loads
+  constexpr int WC = 64 / NW, WB = WC / 8;   // columns / 8-column blocks per warp of a 64-wide accumulator
+  static_assert(NW == 2 || NW == 4, "one to four 8-column blocks per warp");
   const int rcol = tid & 15, rrow0 = tid >> 4;
   const int d0 = cg * ZC;                    // first column (inside the half) of this thread
   const int bh = blockIdx.x;
@@ -144,6 +149,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   __syncthreads();
 
   constexpr uint32_t ID_KK32 = make_idesc(64, 32, PK::fmt, 0, 0);
+  constexpr uint32_t ID_KK64 = make_idesc(64, 64, PK::fmt, 0, 0);
   constexpr uint32_t ID_KM64 = make_idesc(64, 64, PK::fmt, 0, 1);
   constexpr uint32_t ID_MM64 = make_idesc(64, 64, PK::fmt, 1, 1);
   constexpr uint32_t ID_MM32 = make_idesc(64, 32, PK::fmt, 1, 1);
@@ -173,7 +179,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll
       for (int part = 0; part < ZC / PC; ++part) {
         uint32_t zi[PC];
-        tmem_ld<PC>(tmem + lane_base + 384 + d0 + PC * part, zi);
+        tmem_ld<PC>(tmem + lane_base + 448 + d0 + PC * part, zi);
         tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < PC / 8; ++ch) {
@@ -242,7 +248,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       const uint64_t kDY = make_desc(smem_u32(tDY), 16, 1024), mDY = make_desc(smem_u32(tDY), 8192, 1024);
       const uint64_t mZ = make_desc(smem_u32(tZ), 8192, 1024);
       const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
-      const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024);
+      const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024), kDYO = make_desc(aDYO, 16, 1024);
       const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
       bool go = lane == 0 && s_abort == 0;
       if (go) do {
@@ -250,34 +256,31 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(20); s_abort = 1; go = false; break; }
         tc_fence_after_sync();
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // dS[t][s] = sum_p dY[t][p] U[s][p]          A: dY K-major, B: U K-major rows s (N = 32 half)
-            umma(lb + 32, desc_adv(kDY, 32 * k), desc_adv(kU, 4096 * q + 32 * k), ID_KK32, k > 0);
-            // dQb[t][d] = sum_p dY[t][p] Zv[p][d]        A: dY K-major, B: Zv MN-major (rows = p)
-            umma(lb + 128, desc_adv(kDY, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
-          }
-        }
+        for (int k = 0; k < 4; ++k)
+          // dS[t][s] = sum_p dY[t][p] U[s][p]            A: dY K-major, B: U K-major rows s
+          umma(tmem + 64, desc_adv(kDY, 32 * k), desc_adv(kU, 32 * k), ID_KK64, k > 0);
       } while (false);
       __syncwarp();
       // (2) products of rotated tiles, once the workers' passes are done (Q, K', dYoff written)
       bar_sync(2, NT + 64);
       if (go && s_abort == 0) {
         tc_fence_after_sync();
-        // P~[t][s] = sum_d Q[t][d] K'[s][d]              A: Q K-major, B: K' K-major rows s (N = 32 half)
+        // P~[t][s] = sum_d Q[t][d] K'[s][d]              A: Q K-major, B: K' K-major rows s
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t dP_ = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-            umma(dP_, desc_adv(kQ, ko), desc_adv(kKP, 4096 * q + ko), ID_KK32, k > 0);
-          }
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+          umma(tmem + 0, desc_adv(kQ, ko), desc_adv(kKP, ko), ID_KK64, k > 0);
         }
         umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
         SL_TOCK_MMA(6)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t lb = tmem + ((16u * q) << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            // dQ[t][d] = sum_p dYoff[t][p] Zv[p][d] (+ dP K' below)   A: dYoff K-major, B: Zv MN-major (rows = p)
+            umma(lb + 128, desc_adv(kDYO, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
+        }
       }
       __syncwarp();
       // (2b) once the workers have finished epilogue 5 of the previous chunk (the Zv tiles of the other
@@ -320,22 +323,18 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           const uint32_t lb = tmem + ((16u * q) << 16);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma(lb + 64, desc_adv(kDP, 32 * k), desc_adv(mKP, TILE * q + 2048 * k), ID_KM64, k > 0);
+            umma(lb + 128, desc_adv(kDP, 32 * k), desc_adv(mKP, TILE * q + 2048 * k), ID_KM64, 1);
         }
         umma_commit(&bar_mma[2]);   // dQ
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]      A: Pdec MN-major, B: dY MN-major (N = 32 half)
+        for (int k = 0; k < 4; ++k)
+          // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]        A: Pdec MN-major, B: dY MN-major
+          umma(tmem + 320, desc_adv(mPD, 2048 * k), desc_adv(mDY, 2048 * k), ID_MM64, k > 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma(lb + 320, desc_adv(mPD, 2048 * k), desc_adv(mDY, 64 * q + 2048 * k), ID_MM32, k > 0);
-          // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p (N = 32 half)
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-            umma(lb + 352, desc_adv(kKP, ko), desc_adv(kDW, 4096 * q + ko), ID_KK32, k > 0);
-          }
+        for (int k = 0; k < 8; ++k) {
+          // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p
+          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
+          umma(tmem + 384, desc_adv(kKP, ko), desc_adv(kDW, ko), ID_KK64, k > 0);
         }
         umma_commit(&bar_mma[3]);   // dU
 #pragma unroll
@@ -344,7 +343,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
-            umma(lb + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
+            umma(lb + 448, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
         }
         umma_commit(&bar_mma[4]);   // dZ
         SL_TOCK_MMA(9)
@@ -452,30 +451,25 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 
     // ---- epilogue 1: decayed, strictly causal Pdec and dP as 16-bit tiles -------------------------------
     if (live) {
-      uint32_t pr[SC], ds[SC];
-      tmem_ld<SC>(tmem + lane_base + 0 + cg * SC, pr);
-      tmem_ld<SC>(tmem + lane_base + 32 + cg * SC, ds);
+      uint32_t pr[4 * WB], ds[4 * WB];
+      tmem_ld_16x256<WB>(tmem + lane_base + 0 + cg * WC, pr);
+      tmem_ld_16x256<WB>(tmem + lane_base + 64 + cg * WC, ds);
       tmem_ld_wait();
-      const float lt = sc[row];
 #pragma unroll
-      for (int ch = 0; ch < SC / 8; ++ch) {
-        uint32_t wp[4], wd[4];
+      for (int hh = 0; hh < 2; ++hh) {
+        const int R = hh ? rowB : rowA;
+        const float lt = sc[R];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float vp[2], vd[2];
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int j = 8 * ch + 2 * e + q, s = 32 * hf + cg * SC + j;
-            const float dec = s < row ? __expf(fminf(lt - sc[s], 0.f)) : 0.f;
-            vp[q] = dec * __uint_as_float(pr[j]);
-            vd[q] = dec * __uint_as_float(ds[j]);
-          }
-          wp[e] = PK::pack(vp[0], vp[1]);
-          wd[e] = PK::pack(vd[0], vd[1]);
+        for (int i = 0; i < WB; ++i) {
+          const int s0 = cg * WC + 8 * i + 2 * cq;
+          const float dec0 = s0 < R ? __expf(fminf(lt - sc[s0], 0.f)) : 0.f;
+          const float dec1 = s0 + 1 < R ? __expf(fminf(lt - sc[s0 + 1], 0.f)) : 0.f;
+          const uint32_t off = sw128(R, cg * WB + i) + 4 * cq;
+          *reinterpret_cast<uint32_t*>(smem + B_OFF_PD + off) =
+              PK::pack(dec0 * __uint_as_float(pr[4 * i + 2 * hh]), dec1 * __uint_as_float(pr[4 * i + 2 * hh + 1]));
+          *reinterpret_cast<uint32_t*>(smem + B_OFF_DP + off) =
+              PK::pack(dec0 * __uint_as_float(ds[4 * i + 2 * hh]), dec1 * __uint_as_float(ds[4 * i + 2 * hh + 1]));
         }
-        const uint32_t off = sw128(row, 4 * hf + cg * (SC / 8) + ch);
-        *reinterpret_cast<uint4*>(smem + B_OFF_PD + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-        *reinterpret_cast<uint4*>(smem + B_OFF_DP + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
       }
     }
     fence_async_smem();
@@ -535,14 +529,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     tc_fence_after_sync();
     // ---- epilogue 2: dQ -> dC, <q,dq> ------------------------------------------------------------------
     if (live) {
-      const float et = sc[1 * 64 + row], phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
+      const float phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
       const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
       float ar = 0.f, ai = 0.f;
 #pragma unroll 1
       for (int ch = 0; ch < ZC / 8; ++ch) {   // a real loop: keeps the kernel's code inside the instruction cache
-        uint32_t qa[8], qb[8];
-        tmem_ld<8>(tmem + lane_base + 64 + d0 + 8 * ch, qa);
-        tmem_ld<8>(tmem + lane_base + 128 + d0 + 8 * ch, qb);
+        uint32_t qa[8];
+        tmem_ld<8>(tmem + lane_base + 128 + d0 + 8 * ch, qa);
         tmem_ld_wait();
         const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
         const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
@@ -552,8 +545,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = 2 * e;
-          const float dqr = __uint_as_float(qa[j]) + et * __uint_as_float(qb[j]);
-          const float dqi = __uint_as_float(qa[j + 1]) + et * __uint_as_float(qb[j + 1]);
+          const float dqr = __uint_as_float(qa[j]), dqi = __uint_as_float(qa[j + 1]);
           const float2 q = PK::unpack(qw[e]), bb = PK::unpack(bw[e]);
           ar += q.x * dqr + q.y * dqi;          // conj(q) dq
           ai += q.x * dqi - q.y * dqr;
@@ -576,25 +568,21 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     tc_fence_after_sync();
     // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
     if (live) {
-      uint32_t ua[SC], ub[SC];
-      tmem_ld<SC>(tmem + lane_base + 320 + cg * SC, ua);
-      tmem_ld<SC>(tmem + lane_base + 352 + cg * SC, ub);
+      uint32_t ua[4 * WB], ub[4 * WB];
+      tmem_ld_16x256<WB>(tmem + lane_base + 320 + cg * WC, ua);
+      tmem_ld_16x256<WB>(tmem + lane_base + 384 + cg * WC, ub);
       tmem_ld_wait();
-      const float ee = sw[0 * 64 + row], dgv = sw[2 * 64 + row];
 #pragma unroll
-      for (int ch = 0; ch < SC / 8; ++ch) {
-        const uint32_t off = sw128(row, 4 * hf + cg * (SC / 8) + ch);
-        const uint4 dv = *reinterpret_cast<const uint4*>(tDY + off);
-        const uint32_t dw_[4] = {dv.x, dv.y, dv.z, dv.w};
-        uint32_t o[4];
+      for (int hh = 0; hh < 2; ++hh) {
+        const int R = hh ? rowB : rowA;
+        const float ee = sw[0 * 64 + R], dgv = sw[2 * 64 + R];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = 8 * ch + 2 * e;
-          const float2 d2 = PK::unpack(dw_[e]);
-          o[e] = PK::pack(__uint_as_float(ua[j]) + ee * __uint_as_float(ub[j]) + dgv * d2.x,
-                          __uint_as_float(ua[j + 1]) + ee * __uint_as_float(ub[j + 1]) + dgv * d2.y);
+        for (int i = 0; i < WB; ++i) {
+          uint32_t* cell = reinterpret_cast<uint32_t*>(tDY + sw128(R, cg * WB + i) + 4 * cq);
+          const float2 d2 = PK::unpack(*cell);
+          *cell = PK::pack(__uint_as_float(ua[4 * i + 2 * hh]) + ee * __uint_as_float(ub[4 * i + 2 * hh]) + dgv * d2.x,
+                           __uint_as_float(ua[4 * i + 2 * hh + 1]) + ee * __uint_as_float(ub[4 * i + 2 * hh + 1]) + dgv * d2.y);   // dU over dY, in place
         }
-        *reinterpret_cast<uint4*>(tDY + off) = make_uint4(o[0], o[1], o[2], o[3]);   // dU over dY, in place
       }
     }
     // the tile is complete once every worker warp has arrived; the issue warp then stores it
