@@ -184,7 +184,9 @@ def golden_mixer(slinoss):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of a checkout of the reference (slinoss)>")
+    ref_root = sys.argv[1]
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)
     import slinoss
