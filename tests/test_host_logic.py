@@ -184,3 +184,13 @@ def test_stack_forward_and_step_agree(fake):
             y, state = stack.step(x[:, t], state)
             ys.append(y)
     assert rel(torch.stack(ys, 1), full) < 1e-4
+
+
+def test_measure_module_imports_without_a_gpu_and_refuses_to_run(monkeypatch):
+    from slinoss_b200 import measure
+    assert measure.nbytes(torch.zeros(3, 4), None, torch.zeros(2, dtype=torch.bfloat16)) == 48 + 4
+    peak, kind = measure.hbm_peak()
+    assert peak > 1000 and kind in ("measured", "fallback")
+    monkeypatch.setattr("sys.argv", ["measure"])
+    with pytest.raises(SystemExit, match="no CPU path"):
+        measure.main()
