@@ -26,28 +26,59 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) {
   return __float2half_rn(v);
 }
 
+// Pairs: packed conversions (one F2FP instruction on the ALU pipe) instead of two scalar ones,
+// which run on the much narrower XU pipe.
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  a = fminf(fmaxf(a, -65504.f), 65504.f); b = fminf(fmaxf(b, -65504.f), 65504.f);   // saturate like from_f32
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename T> __device__ __forceinline__ float2 unpack_pair(uint32_t v);
+template <> __device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack_pair<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+// a, b rounded to the io dtype and back (the roundings the reference makes between its steps)
+template <typename T> __device__ __forceinline__ void round_pair(float& a, float& b) {
+  if constexpr (sizeof(T) == 2) {
+    const float2 r = unpack_pair<T>(pack_pair<T>(a, b));
+    a = r.x; b = r.y;
+  }
+}
+
 // 16-byte vectors of io elements: 4 floats or 8 16-bit values, handled as floats
 template <typename T> struct Vec16 { static constexpr int N = 16 / (int)sizeof(T); };
 template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[Vec16<T>::N]);
+template <typename T>
 __device__ __forceinline__ void load16(const T* p, float (&v)[Vec16<T>::N]) {
-  const uint4 r = *reinterpret_cast<const uint4*>(p);
-  const T* e = reinterpret_cast<const T*>(&r);
-#pragma unroll
-  for (int i = 0; i < Vec16<T>::N; ++i) v[i] = to_f32(e[i]);
+  unpack16<T>(*reinterpret_cast<const uint4*>(p), v);
 }
 template <typename T>
 __device__ __forceinline__ void unpack16(const uint4& r, float (&v)[Vec16<T>::N]) {
-  const T* e = reinterpret_cast<const T*>(&r);
+  if constexpr (sizeof(T) == 2) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-  for (int i = 0; i < Vec16<T>::N; ++i) v[i] = to_f32(e[i]);
+    for (int i = 0; i < 4; ++i) { const float2 f = unpack_pair<T>(w[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  } else {
+    v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+  }
 }
 template <typename T>
 __device__ __forceinline__ void store16(T* p, const float (&v)[Vec16<T>::N]) {
-  uint4 r;
-  T* e = reinterpret_cast<T*>(&r);
-#pragma unroll
-  for (int i = 0; i < Vec16<T>::N; ++i) e[i] = from_f32<T>(v[i]);
-  *reinterpret_cast<uint4*>(p) = r;
+  if constexpr (sizeof(T) == 2) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(pack_pair<T>(v[0], v[1]), pack_pair<T>(v[2], v[3]),
+                                              pack_pair<T>(v[4], v[5]), pack_pair<T>(v[6], v[7]));
+  } else {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
 }
 
 struct cf {  // complex float

@@ -218,12 +218,16 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_fwd_vec_kernel(TailParams p
           float sv[V];
           unpack16<T>(cS[i], sv);
 #pragma unroll
-          for (int k = 0; k < V; ++k) y[k] = round_io<T>(y[k] + sv[k] * dsk[i]);
+          for (int k = 0; k < V; k += 2) {
+            y[k] += sv[k] * dsk[i]; y[k + 1] += sv[k + 1] * dsk[i];
+            round_pair<T>(y[k], y[k + 1]);
+          }
         }
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          hid[i][k] = round_io<T>(y[k] * silu_f(g[k]));
-          ss += hid[i][k] * hid[i][k];
+        for (int k = 0; k < V; k += 2) {
+          hid[i][k] = y[k] * silu_f(g[k]); hid[i][k + 1] = y[k + 1] * silu_f(g[k + 1]);
+          round_pair<T>(hid[i][k], hid[i][k + 1]);
+          ss += hid[i][k] * hid[i][k] + hid[i][k + 1] * hid[i][k + 1];
         }
       }
     }
@@ -307,13 +311,17 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_vec_kernel(TailParams p
       if (c < C) {
         if (S) {
 #pragma unroll
-          for (int k = 0; k < V; ++k) pre[i][k] = round_io<T>(pre[i][k] + sv[i][k] * dsk[i]);
+          for (int k = 0; k < V; k += 2) {
+            pre[i][k] += sv[i][k] * dsk[i]; pre[i][k + 1] += sv[i][k + 1] * dsk[i];
+            round_pair<T>(pre[i][k], pre[i][k + 1]);
+          }
         }
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          const float hid = round_io<T>(pre[i][k] * silu_f(g[i][k]));
-          ss += hid * hid;
-          dot += hid * dnv[i][k] * wv[i][k];
+        for (int k = 0; k < V; k += 2) {
+          float h0 = pre[i][k] * silu_f(g[i][k]), h1 = pre[i][k + 1] * silu_f(g[i][k + 1]);
+          round_pair<T>(h0, h1);
+          ss += h0 * h0 + h1 * h1;
+          dot += h0 * dnv[i][k] * wv[i][k] + h1 * dnv[i][k + 1] * wv[i][k + 1];
         }
       }
     }
@@ -328,15 +336,25 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_vec_kernel(TailParams p
         const size_t yi = (((size_t)b * p.H + hh[i]) * p.T + t) * p.P + pp[i];
         float o_dy[V], o_dg[V], o_ds[V];
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          const float gg = g[i][k], sg = sigmoid_f(gg);
-          const float hid = round_io<T>(pre[i][k] * (gg * sg));
-          dw_acc[i][k] += dnv[i][k] * hid * rstd;
-          const float dh = rstd * dnv[i][k] * wv[i][k] - hid * coef;
-          const float dpre = dh * gg * sg;
-          o_dg[k] = dh * pre[i][k] * sg * (1.f + gg * (1.f - sg));
-          o_dy[k] = dpre;
-          if (S) { o_ds[k] = dpre * dsk[i]; dsk_acc[i] += dpre * sv[i][k]; }
+        for (int k2 = 0; k2 < V; k2 += 2) {
+          float sgv[2], hidv[2];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            sgv[q] = sigmoid_f(g[i][k2 + q]);
+            hidv[q] = pre[i][k2 + q] * (g[i][k2 + q] * sgv[q]);
+          }
+          round_pair<T>(hidv[0], hidv[1]);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int k = k2 + q;
+            const float gg = g[i][k], sg = sgv[q], hid = hidv[q];
+            dw_acc[i][k] += dnv[i][k] * hid * rstd;
+            const float dh = rstd * dnv[i][k] * wv[i][k] - hid * coef;
+            const float dpre = dh * gg * sg;
+            o_dg[k] = dh * pre[i][k] * sg * (1.f + gg * (1.f - sg));
+            o_dy[k] = dpre;
+            if (S) { o_ds[k] = dpre * dsk[i]; dsk_acc[i] += dpre * sv[i][k]; }
+          }
         }
         store16<T>(dgate + (size_t)row * C + c, o_dg);
         store16<T>(dY + yi, o_dy);

@@ -30,20 +30,15 @@ template <typename T> __device__ __forceinline__ void load4(const T* p, float (&
     v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
   } else {
     const uint2 r = *reinterpret_cast<const uint2*>(p);
-    const T* e = reinterpret_cast<const T*>(&r);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = to_f32(e[i]);
+    const float2 a = unpack_pair<T>(r.x), b = unpack_pair<T>(r.y);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
   }
 }
 template <typename T> __device__ __forceinline__ void store4(T* p, const float (&v)[4]) {
   if constexpr (sizeof(T) == 4) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
   } else {
-    uint2 r;
-    T* e = reinterpret_cast<T*>(&r);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) e[i] = from_f32<T>(v[i]);
-    *reinterpret_cast<uint2*>(p) = r;
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_pair<T>(v[0], v[1]), pack_pair<T>(v[2], v[3]));
   }
 }
 
