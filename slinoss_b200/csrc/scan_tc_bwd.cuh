@@ -198,9 +198,18 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       }
     }
-    float sr, si;
-    block_sum2(ar, ai, sr, si);
-    if (tid == 0 && cp > 0 && live) p.anchor[(size_t)bh * nC + cp - 1] = make_float2(sr, si);
+    // per-warp partial sums of the anchor; they are added up by finish_anchor() after the next workers'
+    // barrier (no CTA-wide reduction here)
+    ar = warp_sum(ar); ai = warp_sum(ai);
+    if (lane == 0) { s_red[2 * warp] = live ? ar : 0.f; s_red[2 * warp + 1] = live ? ai : 0.f; }
+  };
+  auto finish_anchor = [&](int itp) {   // one thread, after a barrier that follows epilogue5(itp)
+    const int cp = nC - 1 - itp;
+    if (cp <= 0) return;
+    float sr = 0.f, si = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4 * NW; ++k) { sr += s_red[2 * k]; si += s_red[2 * k + 1]; }
+    p.anchor[(size_t)bh * nC + cp - 1] = make_float2(sr, si);
   };
   // ---- dWv tile of a chunk: dz rotated by the unit phase of Pi_end: (a,b) -> (ur a - ui b, ui a + ur b),
   // and the row e^{l_end - l_t} of that chunk ------------------------------------------------------------------
@@ -438,11 +447,14 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     if (it > 0) epilogue5(it - 1, live);
     live = live && s_abort == 0;
     if (live) make_dwv(sc);
+    SL_TOCK(21)
     em_keep = sc[1 * 64 + 63];
     fence_async_smem();
     tc_fence_before_sync();
     bar_sync(3, NT);
     bar_arrive(6, NT + 32);      // dWv written, the previous dZ accumulator and Zv tiles released
+    if (tid == 0 && it > 0 && live) finish_anchor(it - 1);
+    SL_TOCK(22)
 
     // ---- MMA group 1 (issued by the look-ahead warp): P~ = Q K'^T, dS = dY U^T ------------------------
     if (live && !mbar_wait(&bar_mma[0], it & 1)) { report_timeout(12); s_abort = 1; live = false; }
