@@ -90,6 +90,29 @@ def measure_decode(iters, dev):
     report("sl_v2x2ssd_decode (state out of place)", time_ms(out_of_place, iters), algo, cfg)
     report("sl_v2x2ssd_decode (state in place)", time_ms(in_place, iters), algo, cfg)
 
+    # the same call as a serving loop would issue it: 16 tokens captured once in a CUDA graph
+    # (state ping-pongs between two buffers), then replayed
+    tokens = 16
+
+    def loop():
+        a, b2 = state, state2
+        for _ in range(tokens):
+            _C.scan_decode(U, M, K, Bv, Cv, a, Bp, Up, y_dtype=torch.bfloat16, state_out=b2)
+            a, b2 = b2, a
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        loop()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        loop()
+    ms = time_ms(graph.replay, max(2, iters // 4)) / tokens
+    report("sl_v2x2ssd_decode (CUDA-graph replay of 16 tokens, per token)", ms, algo, cfg,
+           {"us_per_sequence_token": ms * 1e3 / b, "tokens_per_s": b / (ms * 1e-3)})
+
 
 def _mixer_tensors(dev, batch=8, T=2048, heads=32, P=64, N=64):
     g = torch.Generator().manual_seed(0)
