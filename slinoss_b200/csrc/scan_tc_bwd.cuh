@@ -8,7 +8,8 @@
 // operands, decays exp(<=0) on float32 accumulators):
 //     P~ = Q K'^T,  dS = dY U^T      -> Pdec = mask_{s<t} e^{l_t-l_s} P~ ,  dP = mask_{s<t} e^{l_t-l_s} dS
 //     dQ = dP K' + e^{l_t} (dY Zv)                     -> dC  (un-rotate, + diagonal term)
-//     dX = dP^T Q + e^{l_end-l_s} (U dWv)              -> dB, dg   (dWv = dz rotated by the unit phase of Pi_end)
+//     dX = dP^T Q + (e^{l_end-l_s} U) dWv              -> dB, dg   (dWv = dz rotated by the unit phase of Pi_end;
+//                                                        the decay is folded into the 16-bit rows of U)
 //     dU = Pdec^T dY + e^{l_end-l_s} (K' dWv^T)        (+ dy_s diag_s)
 //     dz <- e^{l_end} dWv + (e^{l_t} dY)^T Q           (adjoint of the chunk-start state)
 // Per-token scalars for dM / dK go to the workspace and are finished by
@@ -23,12 +24,15 @@ constexpr uint32_t B_OFF_DYO = B_OFF_KP + 2 * TILE;    // e^{l_t} dY (1)
 constexpr uint32_t B_OFF_PD = B_OFF_DYO + TILE;        // Pdec (1)
 constexpr uint32_t B_OFF_DP = B_OFF_PD + TILE;         // dP (1)
 constexpr uint32_t B_OFF_DW = B_OFF_DP + TILE;         // dWv (2)
-constexpr uint32_t B_OFF_SCAL = B_OFF_DW + 2 * TILE;
+constexpr uint32_t B_OFF_UE = B_OFF_DW + 2 * TILE;      // e^{l_end-l_s} U (1)
+constexpr uint32_t B_OFF_SCAL = B_OFF_UE + TILE;
 constexpr int B_NSCAL = 2 * 11 + 5 + 32;   // 2 x 11 look-ahead rows, 5 worker rows, 4 x 8 partial sums
 constexpr uint32_t B_SMEM_BYTES = B_OFF_SCAL + B_NSCAL * 64 * 4 + 1024;
-// TMEM columns: P~ 0 | dS 64 | dQ 128 | dXa 192 | dXb 256 | dUa 320 | dUb 384 | dZ 448.  P~, dS, dUa and dUb are
-// single N = 64 products (rows in lanes 0..15 of a quadrant, read with the 16x256b load shape); dQ, dX and dZ
-// are two N-halves each, the second at TMEM lane offset 16 (read with the 32x32b shape).
+// TMEM columns: P~ then dUa 0 | dS then dUb 64 | dQ 128..255 | dX 256..383 | dZ 384..511.  All products have
+// M = 64 (rows in lanes 0..15 of a quadrant).  P~, dS, dUa and dUb are N = 64 and read with the 16x256b load
+// shape; dQ, dX and dZ are N = 128 products (each the sum of two operand pairs but for dZ) read with the
+// 16x32bx2 shape (thread t: row t % 16 of column half t / 16).  dUa and dUb reuse the columns of P~ and dS,
+// which are dead after epilogue 1.
 constexpr uint32_t B_TMEM_COLS = 512;
 
 struct alignas(64) TcBwdParams {
@@ -153,9 +157,12 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   constexpr uint32_t ID_KM64 = make_idesc(64, 64, PK::fmt, 0, 1);
   constexpr uint32_t ID_MM64 = make_idesc(64, 64, PK::fmt, 1, 1);
   constexpr uint32_t ID_MM32 = make_idesc(64, 32, PK::fmt, 1, 1);
+  constexpr uint32_t ID_KM128 = make_idesc(64, 128, PK::fmt, 0, 1);
+  constexpr uint32_t ID_MM128 = make_idesc(64, 128, PK::fmt, 1, 1);
   const uint32_t aQ = smem_u32(smem + B_OFF_Q), aKP = smem_u32(smem + B_OFF_KP),
                  aDYO = smem_u32(smem + B_OFF_DYO), aPD = smem_u32(smem + B_OFF_PD),
-                 aDP = smem_u32(smem + B_OFF_DP), aDW = smem_u32(smem + B_OFF_DW);
+                 aDP = smem_u32(smem + B_OFF_DP), aDW = smem_u32(smem + B_OFF_DW),
+                 aUE = smem_u32(smem + B_OFF_UE);
   bool ok = true;
 #ifdef SL_TC_TIMING
 #define SL_TOCK(i) if (bh == 0 && tid == 0 && it == 8) g_tc_timing[i] = clock64();
@@ -179,7 +186,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll
       for (int part = 0; part < ZC / PC; ++part) {
         uint32_t zi[PC];
-        tmem_ld<PC>(tmem + lane_base + 448 + d0 + PC * part, zi);
+        tmem_ld_16x32bx2<PC, 64>(tmem + lane_base + 384 + d0 + PC * part, zi);
         tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < PC / 8; ++ch) {
@@ -259,6 +266,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       const uint64_t kDP = make_desc(aDP, 16, 1024), mDP = make_desc(aDP, 8192, 1024);
       const uint64_t mPD = make_desc(aPD, 8192, 1024), mDYO = make_desc(aDYO, 8192, 1024), kDYO = make_desc(aDYO, 16, 1024);
       const uint64_t kDW = make_desc(aDW, 16, 1024), mDW = make_desc(aDW, 8192, 1024);
+      const uint64_t kUE = make_desc(aUE, 16, 1024);
       bool go = lane == 0 && s_abort == 0;
       if (go) do {
         // (1) products of raw tiles, as soon as the stage has landed
@@ -283,13 +291,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
         SL_TOCK_MMA(6)
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            // dQ[t][d] = sum_p dYoff[t][p] Zv[p][d] (+ dP K' below)   A: dYoff K-major, B: Zv MN-major (rows = p)
-            umma(lb + 128, desc_adv(kDYO, 32 * k), desc_adv(mZ, TILE * q + 2048 * k), ID_KM64, k > 0);
-        }
+        for (int k = 0; k < 4; ++k)
+          // dQ[t][d] = sum_p dYoff[t][p] Zv[p][d] (+ dP K' below)   A: dYoff K-major, B: Zv MN-major (rows = p)
+          umma(tmem + 128, desc_adv(kDYO, 32 * k), desc_adv(mZ, 2048 * k), ID_KM128, k > 0);
       }
       __syncwarp();
       // (2b) once the workers have finished epilogue 5 of the previous chunk (the Zv tiles of the other
@@ -303,13 +307,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
         SL_TOCK_MMA(18)
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            // dXb[s][d] = sum_p U[s][p] dWv[p][d]        A: U K-major, B: dWv MN-major (rows = p)
-            umma(lb + 256, desc_adv(kU, 32 * k), desc_adv(mDW, TILE * q + 2048 * k), ID_KM64, k > 0);
-        }
+        for (int k = 0; k < 4; ++k)
+          // dX[s][d] = sum_p (e^{l_end-l_s} U[s][p]) dWv[p][d] (+ dP^T Q below)   A: Uee K-major, B: dWv MN-major
+          umma(tmem + 256, desc_adv(kUE, 32 * k), desc_adv(mDW, 2048 * k), ID_KM128, k > 0);
       }
       __syncwarp();
       // (3) products of the masked tiles, once epilogue 1 has written Pdec and dP; ordered by the
@@ -318,42 +318,30 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       if (go && s_abort == 0) do {
         tc_fence_after_sync();
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          // dXa[s][d] = sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma(lb + 192, desc_adv(mDP, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
-        }
+        for (int k = 0; k < 4; ++k)
+          // dX[s][d] += sum_t dP[t][s] Q[t][d]         A: dP MN-major (rows = t), B: Q MN-major
+          umma(tmem + 256, desc_adv(mDP, 2048 * k), desc_adv(mQ, 2048 * k), ID_MM128, 1);
         umma_commit(&bar_mma[1]);   // dX
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
+        for (int k = 0; k < 4; ++k)
           // dQa[t][d] = sum_s dP[t][s] K'[s][d]        A: dP K-major, B: K' MN-major (rows = s)
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma(lb + 128, desc_adv(kDP, 32 * k), desc_adv(mKP, TILE * q + 2048 * k), ID_KM64, 1);
-        }
+          umma(tmem + 128, desc_adv(kDP, 32 * k), desc_adv(mKP, 2048 * k), ID_KM128, 1);
         umma_commit(&bar_mma[2]);   // dQ
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           // dUa[s][p] = sum_t Pdec[t][s] dY[t][p]        A: Pdec MN-major, B: dY MN-major
-          umma(tmem + 320, desc_adv(mPD, 2048 * k), desc_adv(mDY, 2048 * k), ID_MM64, k > 0);
+          umma(tmem + 0, desc_adv(mPD, 2048 * k), desc_adv(mDY, 2048 * k), ID_MM64, k > 0);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // dUb[s][p] = sum_d K'[s][d] dWv[p][d]         A: K' K-major, B: dWv K-major rows p
           const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          umma(tmem + 384, desc_adv(kKP, ko), desc_adv(kDW, ko), ID_KK64, k > 0);
+          umma(tmem + 64, desc_adv(kKP, ko), desc_adv(kDW, ko), ID_KK64, k > 0);
         }
         umma_commit(&bar_mma[3]);   // dU
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t lb = tmem + ((16u * q) << 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
-            umma(lb + 448, desc_adv(mDYO, 2048 * k), desc_adv(mQ, TILE * q + 2048 * k), ID_MM64, k > 0);
-        }
+        for (int k = 0; k < 4; ++k)
+          // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
+          umma(tmem + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, 2048 * k), ID_MM128, k > 0);
         umma_commit(&bar_mma[4]);   // dZ
         SL_TOCK_MMA(9)
         // (4) output tiles: the workers overwrite dead operand tiles of this stage in place (C with dB,
@@ -386,15 +374,18 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       const uint4 uv = *reinterpret_cast<const uint4*>(tU + off);
       const uint32_t dw_[4] = {dv.x, dv.y, dv.z, dv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
       const float et = sc[1 * 64 + r];
-      uint32_t o[4];
+      const float ee = __expf(fminf(sc[63] - sc[r], 0.f));   // e^{l_end - l_s}
+      uint32_t o[4], ue[4];
       float sg = 0.f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 d2 = PK::unpack(dw_[e]), u2 = PK::unpack(uw[e]);
         sg += d2.x * u2.x + d2.y * u2.y;
         o[e] = PK::pack(et * d2.x, et * d2.y);
+        ue[e] = PK::pack(ee * u2.x, ee * u2.y);
       }
       *reinterpret_cast<uint4*>(smem + B_OFF_DYO + off) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(smem + B_OFF_UE + off) = make_uint4(ue[0], ue[1], ue[2], ue[3]);
       sg += __shfl_xor_sync(0xffffffffu, sg, 4);
       sg += __shfl_xor_sync(0xffffffffu, sg, 2);
       sg += __shfl_xor_sync(0xffffffffu, sg, 1);
@@ -499,14 +490,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     const float sig = sw[1 * 64 + row];
     // ---- epilogue 3 (first): dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
     if (live) {
-      const float ee = sw[0 * 64 + row], wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
+      const float wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
       const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];
       float rr = 0.f, ri = 0.f;
 #pragma unroll 1
       for (int ch = 0; ch < ZC / 8; ++ch) {
-        uint32_t xa[8], xb[8];
-        tmem_ld<8>(tmem + lane_base + 192 + d0 + 8 * ch, xa);
-        tmem_ld<8>(tmem + lane_base + 256 + d0 + 8 * ch, xb);
+        uint32_t xa[8];
+        tmem_ld_16x32bx2<8, 64>(tmem + lane_base + 256 + d0 + 8 * ch, xa);
         tmem_ld_wait();
         const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
         const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
@@ -516,8 +506,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = 2 * e;
-          const float ga = __uint_as_float(xa[j]) + ee * __uint_as_float(xb[j]);
-          const float gb = __uint_as_float(xa[j + 1]) + ee * __uint_as_float(xb[j + 1]);
+          const float ga = __uint_as_float(xa[j]), gb = __uint_as_float(xa[j + 1]);
           const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
           // dX = ga - i gb ; R += conj(b) dX
           rr += bb.x * ga - bb.y * gb;
@@ -547,7 +536,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll 1
       for (int ch = 0; ch < ZC / 8; ++ch) {   // a real loop: keeps the kernel's code inside the instruction cache
         uint32_t qa[8];
-        tmem_ld<8>(tmem + lane_base + 128 + d0 + 8 * ch, qa);
+        tmem_ld_16x32bx2<8, 64>(tmem + lane_base + 128 + d0 + 8 * ch, qa);
         tmem_ld_wait();
         const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
         const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
@@ -581,8 +570,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
     if (live) {
       uint32_t ua[4 * WB], ub[4 * WB];
-      tmem_ld_16x256<WB>(tmem + lane_base + 320 + cg * WC, ua);
-      tmem_ld_16x256<WB>(tmem + lane_base + 384 + cg * WC, ub);
+      tmem_ld_16x256<WB>(tmem + lane_base + 0 + cg * WC, ua);
+      tmem_ld_16x256<WB>(tmem + lane_base + 64 + cg * WC, ub);
       tmem_ld_wait();
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {

@@ -240,6 +240,38 @@ __device__ __forceinline__ void tmem_ld_16x256(uint32_t taddr, uint32_t (&r)[4 *
         : "memory");
   }
 }
+// 16 lanes x N columns, twice: threads 0..15 of the warp receive lanes 0..15 of the quadrant at
+// columns [c, c + N), threads 16..31 the same lanes at columns [c + SPLIT, c + SPLIT + N).  For an
+// M = 64, N = 128 accumulator this hands thread t row (t % 16) of the column half (t / 16).
+template <int N, int SPLIT>
+__device__ __forceinline__ void tmem_ld_16x32bx2(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16 || N == 32, "unsupported width");
+  if constexpr (N == 32) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x32bx2.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32], %33;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr), "n"(SPLIT)
+        : "memory");
+  } else if constexpr (N == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.16x32bx2.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8], %9;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr), "n"(SPLIT)
+                 : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x32bx2.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16], %17;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr), "n"(SPLIT)
+        : "memory");
+  }
+}
 // N consecutive columns, N in {8, 16, 32, 64}
 template <int N>
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]) {
