@@ -178,6 +178,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   auto epilogue5 = [&](int itp, bool live) {
     const int cp = nC - 1 - itp;
     const uint8_t* tZp = smem + (itp & 1) * B_STAGE + 6 * TILE;
+    uint4 zvv[ZC / 8];   // this thread's cells of the Zv tiles, fetched ahead of the wait (a compiler barrier)
+#pragma unroll
+    for (int ch = 0; ch < ZC / 8; ++ch)
+      zvv[ch] = *reinterpret_cast<const uint4*>(tZp + hf * TILE + sw128(row, d0 / 8 + ch));
     if (live && !mbar_wait(&bar_mma[4], itp & 1)) { report_timeout(16); s_abort = 1; live = false; }
     tc_fence_after_sync();
     const float em = em_keep;
@@ -190,7 +194,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < PC / 8; ++ch) {
-          const uint4 zv4 = *reinterpret_cast<const uint4*>(tZp + hf * TILE + sw128(row, d0 / 8 + (PC / 8) * part + ch));
+          const uint4 zv4 = zvv[(PC / 8) * part + ch];
           const uint32_t zw[4] = {zv4.x, zv4.y, zv4.z, zv4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -205,12 +209,12 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       }
     }
-    // per-warp partial sums of the anchor; they are added up by finish_anchor() after the next workers'
-    // barrier (no CTA-wide reduction here)
+    // per-warp partial sums of the anchor; they are added up by finish_anchor() on the scalar warp after
+    // named barrier 7 (no CTA-wide reduction here)
     ar = warp_sum(ar); ai = warp_sum(ai);
     if (lane == 0) { s_red[2 * warp] = live ? ar : 0.f; s_red[2 * warp + 1] = live ? ai : 0.f; }
   };
-  auto finish_anchor = [&](int itp) {   // one thread, after a barrier that follows epilogue5(itp)
+  auto finish_anchor = [&](int itp) {   // one thread of the scalar warp, after the barrier that follows epilogue5(itp)
     const int cp = nC - 1 - itp;
     if (cp <= 0) return;
     float sr = 0.f, si = 0.f;
@@ -252,6 +256,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       // DRAM round trip)
       bar_sync(2, NT + 64);   // the workers only arrive here (bar_arrive): they never wait for this warp
       if (it + 1 < nC) chunk_scalars(sc_tab + ((it + 1) & 1) * (11 * 64), Mb, Kb, t0 - L, T, lane);
+      // the anchor of the previous chunk: a global store by a worker thread here would make that
+      // thread's next proxy fence (epilogue 1) wait for the store, and every worker for that thread
+      bar_sync(7, NT + 32);
+      if (lane == 0 && it > 0 && s_abort == 0) finish_anchor(it - 1);
+      __syncwarp();
     } else if (!worker) {
       // Issue warp (one lane): every MMA of this chunk, the TMA loads of the next (earlier) chunk and
       // the TMA stores of this chunk's outputs.  The workers never wait for this warp, only for the
@@ -444,10 +453,35 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     tc_fence_before_sync();
     bar_sync(3, NT);
     bar_arrive(6, NT + 32);      // dWv written, the previous dZ accumulator and Zv tiles released
-    if (tid == 0 && it > 0 && live) finish_anchor(it - 1);
+    bar_arrive(7, NT + 32);      // anchor partial sums written: the scalar warp adds them up and stores
     SL_TOCK(22)
 
     // ---- MMA group 1 (issued by the look-ahead warp): P~ = Q K'^T, dS = dY U^T ------------------------
+    // The waits and TMEM loads below are compiler barriers, so everything an epilogue reads from shared
+    // memory is fetched by hand BEFORE the wait it would otherwise queue behind.
+    float dec[4 * WB];   // causal decay factors of this thread's (row, column) cells, [hh][i][0..1]
+    {
+      // loads and exponentials are unconditional (a load under a condition is not speculated by the
+      // compiler: eight serial branches, each with its own load-to-exp latency); the mask is a select
+      float ls[2 * WB];
+#pragma unroll
+      for (int i = 0; i < WB; ++i) {
+        const float2 l2 = *reinterpret_cast<const float2*>(sc + cg * WC + 8 * i + 2 * cq);
+        ls[2 * i] = l2.x; ls[2 * i + 1] = l2.y;
+      }
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int R = hh ? rowB : rowA;
+        const float lt = sc[R];
+#pragma unroll
+        for (int i = 0; i < WB; ++i) {
+          const int s0 = cg * WC + 8 * i + 2 * cq;
+          const float e0 = __expf(fminf(lt - ls[2 * i], 0.f)), e1 = __expf(fminf(lt - ls[2 * i + 1], 0.f));
+          dec[(hh * WB + i) * 2 + 0] = s0 < R ? e0 : 0.f;
+          dec[(hh * WB + i) * 2 + 1] = s0 + 1 < R ? e1 : 0.f;
+        }
+      }
+    }
     if (live && !mbar_wait(&bar_mma[0], it & 1)) { report_timeout(12); s_abort = 1; live = false; }
     tc_fence_after_sync();
     SL_TOCK(7)
@@ -458,15 +492,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       tmem_ld_16x256<WB>(tmem + lane_base + 0 + cg * WC, pr);
       tmem_ld_16x256<WB>(tmem + lane_base + 64 + cg * WC, ds);
       tmem_ld_wait();
+      SL_TOCK(19)
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const int R = hh ? rowB : rowA;
-        const float lt = sc[R];
 #pragma unroll
         for (int i = 0; i < WB; ++i) {
-          const int s0 = cg * WC + 8 * i + 2 * cq;
-          const float dec0 = s0 < R ? __expf(fminf(lt - sc[s0], 0.f)) : 0.f;
-          const float dec1 = s0 + 1 < R ? __expf(fminf(lt - sc[s0 + 1], 0.f)) : 0.f;
+          const float dec0 = dec[(hh * WB + i) * 2 + 0], dec1 = dec[(hh * WB + i) * 2 + 1];
           const uint32_t off = sw128(R, cg * WB + i) + 4 * cq;
           *reinterpret_cast<uint32_t*>(smem + B_OFF_PD + off) =
               PK::pack(dec0 * __uint_as_float(pr[4 * i + 2 * hh]), dec1 * __uint_as_float(pr[4 * i + 2 * hh + 1]));
@@ -475,7 +507,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       }
     }
+    SL_TOCK(20)
     fence_async_smem();
+    SL_TOCK(17)
     tc_fence_before_sync();
     bar_sync(3, NT);
     bar_arrive(4, NT + 32);
@@ -483,24 +517,35 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     SL_TOCK(8)
 
     // ---- MMA group 2 (issued by the look-ahead warp, one commit per accumulator set) ------------------
+    // operands of epilogues 3 and 2 (this thread's cells of the C, B and Q tiles and its row's scalars),
+    // fetched while the products are still running
+    uint4 cvv[ZC / 8], bvv[ZC / 8], qvv[ZC / 8];
+#pragma unroll
+    for (int ch = 0; ch < ZC / 8; ++ch) {
+      const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
+      cvv[ch] = *reinterpret_cast<const uint4*>(tC + off);
+      bvv[ch] = *reinterpret_cast<const uint4*>(tB + off);
+      qvv[ch] = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
+    }
+    const float sig = sw[1 * 64 + row];
+    const float wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
+    const float phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
+    const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
     if (live && !mbar_wait(&bar_mma[1], it & 1)) { report_timeout(13); s_abort = 1; live = false; }
     tc_fence_after_sync();
     SL_TOCK(10)
 
-    const float sig = sw[1 * 64 + row];
     // ---- epilogue 3 (first): dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
     if (live) {
-      const float wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
-      const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];
       float rr = 0.f, ri = 0.f;
-#pragma unroll 1
+      uint32_t xall[ZC];
+      tmem_ld_16x32bx2<ZC, 64>(tmem + lane_base + 256 + d0, xall);
+      tmem_ld_wait();
+#pragma unroll
       for (int ch = 0; ch < ZC / 8; ++ch) {
-        uint32_t xa[8];
-        tmem_ld_16x32bx2<8, 64>(tmem + lane_base + 256 + d0 + 8 * ch, xa);
-        tmem_ld_wait();
+        const uint32_t* xa = xall + 8 * ch;
         const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
-        const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
-        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint4 cv = cvv[ch], bv = bvv[ch];
         const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
         uint32_t o[4];
 #pragma unroll
@@ -530,17 +575,15 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     tc_fence_after_sync();
     // ---- epilogue 2: dQ -> dC, <q,dq> ------------------------------------------------------------------
     if (live) {
-      const float phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
-      const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
       float ar = 0.f, ai = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < ZC / 8; ++ch) {   // a real loop: keeps the kernel's code inside the instruction cache
-        uint32_t qa[8];
-        tmem_ld_16x32bx2<8, 64>(tmem + lane_base + 128 + d0 + 8 * ch, qa);
-        tmem_ld_wait();
+      uint32_t qall[ZC];
+      tmem_ld_16x32bx2<ZC, 64>(tmem + lane_base + 128 + d0, qall);
+      tmem_ld_wait();
+#pragma unroll
+      for (int ch = 0; ch < ZC / 8; ++ch) {
+        const uint32_t* qa = qall + 8 * ch;
         const uint32_t off = hf * TILE + sw128(row, d0 / 8 + ch);
-        const uint4 qv = *reinterpret_cast<const uint4*>(smem + B_OFF_Q + off);
-        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint4 qv = qvv[ch], bv = bvv[ch];
         const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
         uint32_t o[4];
 #pragma unroll
@@ -565,6 +608,17 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     __syncwarp();
     if (lane == 0) mbar_arrive(&bar_st[1]);
     SL_TOCK(12)
+    // operands of epilogue 4: this thread's cells of the dY tile and its rows' scalars
+    uint32_t dyc[2 * WB];
+    float e4s[4];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int R = hh ? rowB : rowA;
+      e4s[2 * hh] = sw[0 * 64 + R]; e4s[2 * hh + 1] = sw[2 * 64 + R];
+#pragma unroll
+      for (int i = 0; i < WB; ++i)
+        dyc[hh * WB + i] = *reinterpret_cast<const uint32_t*>(tDY + sw128(R, cg * WB + i) + 4 * cq);
+    }
     if (live && !mbar_wait(&bar_mma[3], it & 1)) { report_timeout(15); s_abort = 1; live = false; }
     tc_fence_after_sync();
     // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
@@ -576,11 +630,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const int R = hh ? rowB : rowA;
-        const float ee = sw[0 * 64 + R], dgv = sw[2 * 64 + R];
+        const float ee = e4s[2 * hh], dgv = e4s[2 * hh + 1];
 #pragma unroll
         for (int i = 0; i < WB; ++i) {
           uint32_t* cell = reinterpret_cast<uint32_t*>(tDY + sw128(R, cg * WB + i) + 4 * cq);
-          const float2 d2 = PK::unpack(*cell);
+          const float2 d2 = PK::unpack(dyc[hh * WB + i]);
           *cell = PK::pack(__uint_as_float(ua[4 * i + 2 * hh]) + ee * __uint_as_float(ub[4 * i + 2 * hh]) + dgv * d2.x,
                            __uint_as_float(ua[4 * i + 2 * hh + 1]) + ee * __uint_as_float(ub[4 * i + 2 * hh + 1]) + dgv * d2.y);   // dU over dY, in place
         }

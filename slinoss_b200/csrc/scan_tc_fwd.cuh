@@ -302,6 +302,27 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       // chunk is finished ---------------------------------------------------------------------------------
       if (c > 0) output_epilogue(c - 1, live);
       live = live && s_abort == 0;
+      // The wait and the TMEM load below are compiler barriers: what the scores epilogue reads from
+      // shared memory (and the exponentials of it) is computed BEFORE the wait it would otherwise
+      // queue behind.
+      float dfac[4 * SB], dg2[2];   // decay factors of this thread's cells [hh][i][q]; diagonal values
+      {
+        float ls[2 * SB];
+#pragma unroll
+        for (int i = 0; i < SB; ++i) {
+          const float2 l2 = *reinterpret_cast<const float2*>(sc + cg * SC + 8 * i + 2 * cq);
+          ls[2 * i] = l2.x; ls[2 * i + 1] = l2.y;
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int R = hh ? rowB : rowA;
+          const float lt = sc[R];
+          dg2[hh] = s_diag[R];
+#pragma unroll
+          for (int k = 0; k < 2 * SB; ++k) dfac[hh * 2 * SB + k] = __expf(fminf(lt - ls[k], 0.f));
+        }
+      }
+      const float et_next[2] = {sc[1 * 64 + rowA], sc[1 * 64 + rowB]};
       if (live && !mbar_wait(&bar_mma[0], c & 1)) { report_timeout(2); s_abort = 1; live = false; }
       tc_fence_after_sync();
       SL_TICK(4)
@@ -311,19 +332,19 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         uint32_t r[4 * SB];
         tmem_ld_16x256<SB>(tmem + lane_base + 128 * (c & 1) + cg * SC, r);
         tmem_ld_wait();
-        et_keep[0] = sc[1 * 64 + rowA]; et_keep[1] = sc[1 * 64 + rowB];
+        et_keep[0] = et_next[0]; et_keep[1] = et_next[1];
         uint8_t* tS = smem + OFF_S + 4 * cq;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int R = hh ? rowB : rowA;
-          const float lt = sc[R], dgv = s_diag[R];
+          const float dgv = dg2[hh];
 #pragma unroll
           for (int i = 0; i < SB; ++i) {
             float v2[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
               const int s = cg * SC + 8 * i + 2 * cq + q;
-              float v = __uint_as_float(r[4 * i + 2 * hh + q]) * __expf(fminf(lt - sc[s], 0.f));
+              float v = __uint_as_float(r[4 * i + 2 * hh + q]) * dfac[hh * 2 * SB + 2 * i + q];
               v = s < R ? v : (s == R ? dgv : 0.f);
               v2[q] = v;
             }
