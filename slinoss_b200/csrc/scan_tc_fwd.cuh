@@ -257,17 +257,28 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       uint8_t* tB = st + (1 + 2 * half) * TILE;
       uint8_t* tC = st + (5 + half) * TILE;
       uint8_t* tK = smem + OFF_KPP + half * TILE;
+      // All loads of this thread's rows first, then the arithmetic and the (in place) stores, then the
+      // row sums of all rows side by side: the compiler cannot move a load above an earlier store to
+      // the same tiles, nor interleave the shuffle chains of different rows, by itself.
+      constexpr int RK = 64 / RSTEP;
+      uint4 cvk[RK], bvk[RK];
+      float dgk[RK];
 #pragma unroll
-      for (int k = 0; k < 64 / RSTEP; ++k) {
+      for (int k = 0; k < RK; ++k) {
+        const uint32_t off = sw128(rrow0 + RSTEP * k, ch);
+        cvk[k] = make_uint4(0u, 0u, 0u, 0u);
+        if (!STATES_ONLY) cvk[k] = *reinterpret_cast<const uint4*>(tC + off);
+        bvk[k] = *reinterpret_cast<const uint4*>(tB + off);
+      }
+#pragma unroll
+      for (int k = 0; k < RK; ++k) {
         const int r = rrow0 + RSTEP * k;
         const uint32_t off = sw128(r, ch);
         const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
         const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
         const float vr = sc[6 * 64 + r], vi = sc[7 * 64 + r];
         const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
-        uint4 cv = make_uint4(0u, 0u, 0u, 0u);
-        if (!STATES_ONLY) cv = *reinterpret_cast<const uint4*>(tC + off);
-        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+        const uint4 cv = cvk[k], bv = bvk[k];
         const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
         uint32_t qo[4], ko[4], vo[4];
         float dg = 0.f;
@@ -280,13 +291,22 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
           const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
           dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
         }
+        dgk[k] = dg;
         *reinterpret_cast<uint4*>(tK + off) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
         if (!STATES_ONLY) {
           *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
           *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+        }
+      }
+      if (!STATES_ONLY) {
 #pragma unroll
-          for (int o = 8; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
-          if (rcol == 0) s_diag[r] = dg;
+        for (int o = 8; o > 0; o >>= 1) {
+#pragma unroll
+          for (int k = 0; k < RK; ++k) dgk[k] += __shfl_xor_sync(0xffffffffu, dgk[k], o);
+        }
+        if (rcol == 0) {
+#pragma unroll
+          for (int k = 0; k < RK; ++k) s_diag[rrow0 + RSTEP * k] = dgk[k];
         }
       }
     }
