@@ -12,8 +12,9 @@ JSON line:
                         ranks) with inputs resident in HBM, through the C ABI launchers
   e2e                   the same step through the public op with HOST (pinned) buffers:
                         host->device copies of all inputs and device->host copies of Y and
-                        all gradients are inside the timed region (the batch is fed in slices on
-                        three streams so that the two copy directions and the kernels overlap)
+                        all gradients are inside the timed region (the batch is fed in slices of one
+                        batch entry x half the heads on a copy-in stream, two op streams and a
+                        copy-out stream, so that both copy directions and the kernels overlap)
   roofline              the dominant kernel (the backward sweep): its algorithmic bytes / its
                         CUDA-event time vs the measured HBM copy bandwidth of this pool
                         (MEASURED_PEAKS.json); "step" and "fwd" give the same figure for the
@@ -176,6 +177,10 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="T=512 variant for profiler captures")
+    ap.add_argument("--e2e-head-parts", type=int, default=2,
+                    help="end-to-end leg: slices per batch entry along heads (pipeline granularity)")
+    ap.add_argument("--e2e-op-streams", type=int, default=2,
+                    help="end-to-end leg: streams the op runs on, slices alternate between them")
     ap.add_argument("--tc-warps", type=int, default=0, help="development knob: warps per TMEM quadrant")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -264,21 +269,25 @@ def main():
     h_in = [pin(t) for t in (case_h.U, case_h.M, case_h.K, case_h.B, case_h.C, case_h.dY)]
     h2d = sum(t.numel() * t.element_size() for t in h_in)
     d_in = [torch.empty_like(t, device=dev) for t in h_in]
-    n_slices = c["batch"]   # one batch entry per slice: short pipeline fill and drain
-    bs = c["batch"] // n_slices
+    # one slice = one batch entry x a block of heads: short pipeline fill and drain
+    hp = max(1, min(args.e2e_head_parts, c["heads"]))
+    hs = c["heads"] // hp
+    slices = [(slice(b, b + 1), slice(h * hs, (h + 1) * hs if h + 1 < hp else c["heads"]))
+              for b in range(c["batch"]) for h in range(hp)]
     out_shapes = [(case_h.U.shape, torch.bfloat16), (case_h.U.shape, torch.bfloat16),
                   (case_h.M.shape, torch.float32), (case_h.K.shape, torch.float32),
                   (case_h.B.shape, torch.bfloat16), (case_h.C.shape, torch.bfloat16)]   # Y, dU, dM, dK, dB, dC
     h_out = [torch.empty(s, dtype=dt).pin_memory() for s, dt in out_shapes]
     d2h = sum(t.numel() * t.element_size() for t in h_out)
-    s_in, s_op, s_out = (torch.cuda.Stream(dev) for _ in range(3))
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_ops = [torch.cuda.Stream(dev) for _ in range(max(1, args.e2e_op_streams))]
     main_stream = torch.cuda.current_stream(dev)
 
     def step_e2e():
-        for s in (s_in, s_op, s_out):
+        for s in (s_in, s_out, *s_ops):
             s.wait_stream(main_stream)
-        for i in range(n_slices):
-            sl = slice(i * bs, (i + 1) * bs)
+        for i, sl in enumerate(slices):
+            s_op = s_ops[i % len(s_ops)]
             with torch.cuda.stream(s_in):
                 for d, h in zip(d_in, h_in):
                     d[sl].copy_(h[sl], non_blocking=True)
@@ -295,7 +304,7 @@ def main():
                 for h, o in zip(h_out, outs):
                     o.record_stream(s_out)
                     h[sl].copy_(o, non_blocking=True)
-        for s in (s_in, s_op, s_out):
+        for s in (s_in, s_out, *s_ops):
             main_stream.wait_stream(s)
 
     e2e_steps = max(2, min(args.steps, 5))
