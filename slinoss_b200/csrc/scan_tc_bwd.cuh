@@ -405,25 +405,15 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     // ---- pass 2 over B, C: Q, K', diagonal pieces ------------------------------------------------------
     if (live) {
       const uint32_t half = rcol >> 3, ch = rcol & 7;
-      // all loads first, then the arithmetic and stores, then the row sums of all rows side by side
-      // (the compiler neither hoists a load above an earlier shared-memory store nor interleaves the
-      // shuffle chains of different rows by itself)
-      constexpr int RK = 64 / RSTEP;
-      uint4 cvk[RK], bvk[RK];
-      float cbrk[RK], cbik[RK];
-#pragma unroll
-      for (int k = 0; k < RK; ++k) {
-        const uint32_t off = half * TILE + sw128(rrow0 + RSTEP * k, ch);
-        cvk[k] = *reinterpret_cast<const uint4*>(tC + off);
-        bvk[k] = *reinterpret_cast<const uint4*>(tB + off);
-      }
-#pragma unroll
-      for (int k = 0; k < RK; ++k) {
+#pragma unroll 1
+      for (int k = 0; k < 64 / RSTEP; ++k) {
         const int r = rrow0 + RSTEP * k;
         const uint32_t off = half * TILE + sw128(r, ch);
         const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
         const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
-        const uint4 cv = cvk[k], bv = bvk[k];
+        const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
+        const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
+        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
         const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
         uint32_t qo[4], ko[4];
         float cbr = 0.f, cbi = 0.f;
@@ -435,26 +425,15 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           cbr += cc.x * bb.x + cc.y * bb.y;                                       // c conj(b)
           cbi += cc.y * bb.x - cc.x * bb.y;
         }
-        cbrk[k] = cbr; cbik[k] = cbi;
         *reinterpret_cast<uint4*>(smem + B_OFF_Q + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
         *reinterpret_cast<uint4*>(smem + B_OFF_KP + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
-      }
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) {
-#pragma unroll
-        for (int k = 0; k < RK; ++k) {
-          cbrk[k] += __shfl_xor_sync(0xffffffffu, cbrk[k], o);
-          cbik[k] += __shfl_xor_sync(0xffffffffu, cbik[k], o);
+        for (int o = 8; o > 0; o >>= 1) {
+          cbr += __shfl_xor_sync(0xffffffffu, cbr, o);
+          cbi += __shfl_xor_sync(0xffffffffu, cbi, o);
         }
-      }
-      if (rcol == 0) {
-#pragma unroll
-        for (int k = 0; k < RK; ++k) {
-          const int r = rrow0 + RSTEP * k;
-          // diagonal term Re sum conj(c) kc b = Re(kc conj(sum c conj(b)))
-          sw[2 * 64 + r] = sc[8 * 64 + r] * cbrk[k] + sc[9 * 64 + r] * cbik[k];
-          sw[3 * 64 + r] = cbrk[k]; sw[4 * 64 + r] = cbik[k];
-        }
+        // diagonal term Re sum conj(c) kc b = Re(kc conj(sum c conj(b)))
+        if (rcol == 0) { sw[2 * 64 + r] = kr * cbr + ki * cbi; sw[3 * 64 + r] = cbr; sw[4 * 64 + r] = cbi; }
       }
     }
     SL_TOCK(4)
