@@ -287,15 +287,24 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           umma(tmem + 64, desc_adv(kDY, 32 * k), desc_adv(kU, 32 * k), ID_KK64, k > 0);
       } while (false);
       __syncwarp();
-      // (2) products of rotated tiles, once the workers' passes are done (Q, K', dYoff written)
-      bar_sync(2, NT + 64);
+      // (1b) the first four k-steps of P~, once the first column halves of Q and K' are rotated
+      bar_sync(5, NT + 32);
       if (go && s_abort == 0) {
         tc_fence_after_sync();
         // P~[t][s] = sum_d Q[t][d] K'[s][d]              A: Q K-major, B: K' K-major rows s
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t ko = (k >> 2) * TILE + (k & 3) * 32;
-          umma(tmem + 0, desc_adv(kQ, ko), desc_adv(kKP, ko), ID_KK64, k > 0);
+        for (int k = 0; k < 4; ++k)
+          umma(tmem + 0, desc_adv(kQ, k * 32), desc_adv(kKP, k * 32), ID_KK64, k > 0);
+      }
+      __syncwarp();
+      // (2) products of rotated tiles, once the workers' passes are done (Q, K', dYoff written)
+      bar_sync(2, NT + 64);
+      if (go && s_abort == 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 4; k < 8; ++k) {
+          const uint32_t ko = TILE + (k & 3) * 32;
+          umma(tmem + 0, desc_adv(kQ, ko), desc_adv(kKP, ko), ID_KK64, 1);
         }
         umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
         SL_TOCK_MMA(6)
@@ -403,37 +412,65 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     }
     SL_TOCK(3)
     // ---- pass 2 over B, C: Q, K', diagonal pieces ------------------------------------------------------
-    if (live) {
-      const uint32_t half = rcol >> 3, ch = rcol & 7;
-#pragma unroll 1
-      for (int k = 0; k < 64 / RSTEP; ++k) {
-        const int r = rrow0 + RSTEP * k;
-        const uint32_t off = half * TILE + sw128(r, ch);
-        const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
-        const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
-        const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
-        const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
-        const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
-        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-        uint32_t qo[4], ko[4];
-        float cbr = 0.f, cbi = 0.f;
+    // Two phases, one per 64-column half of the state dimension: P~ accumulates over that dimension, so
+    // the issue warp starts its first four k-steps (named barrier 5) while the workers rotate the second
+    // half.  A thread keeps its rows in both phases (8 threads per row), so the row sums stay in registers.
+    {
+      constexpr int IPT = 512 / NT;   // (row, piece) items per thread and phase
+      float cbrk[IPT], cbik[IPT];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
-          qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
-          ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
-          cbr += cc.x * bb.x + cc.y * bb.y;                                       // c conj(b)
-          cbi += cc.y * bb.x - cc.x * bb.y;
-        }
-        *reinterpret_cast<uint4*>(smem + B_OFF_Q + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
-        *reinterpret_cast<uint4*>(smem + B_OFF_KP + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+      for (int j = 0; j < IPT; ++j) { cbrk[j] = 0.f; cbik[j] = 0.f; }
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
-          cbr += __shfl_xor_sync(0xffffffffu, cbr, o);
-          cbi += __shfl_xor_sync(0xffffffffu, cbi, o);
+      for (int half = 0; half < 2; ++half) {
+        if (live) {
+#pragma unroll
+          for (int j = 0; j < IPT; ++j) {
+            const int item = tid + NT * j, r = item >> 3;
+            const uint32_t off = half * TILE + sw128(r, item & 7);
+            const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
+            const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
+            const uint4 cv = *reinterpret_cast<const uint4*>(tC + off);
+            const uint4 bv = *reinterpret_cast<const uint4*>(tB + off);
+            const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+            uint32_t qo[4], ko[4];
+            float cbr = 0.f, cbi = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
+              qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
+              ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
+              cbr += cc.x * bb.x + cc.y * bb.y;                                       // c conj(b)
+              cbi += cc.y * bb.x - cc.x * bb.y;
+            }
+            cbrk[j] += cbr; cbik[j] += cbi;
+            *reinterpret_cast<uint4*>(smem + B_OFF_Q + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+            *reinterpret_cast<uint4*>(smem + B_OFF_KP + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+          }
         }
-        // diagonal term Re sum conj(c) kc b = Re(kc conj(sum c conj(b)))
-        if (rcol == 0) { sw[2 * 64 + r] = kr * cbr + ki * cbi; sw[3 * 64 + r] = cbr; sw[4 * 64 + r] = cbi; }
+        if (half == 0) {   // first halves of Q and K' are complete: P~ may start
+          fence_async_smem();
+          tc_fence_before_sync();
+          bar_arrive(5, NT + 32);
+        }
+      }
+      if (live) {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+#pragma unroll
+          for (int j = 0; j < IPT; ++j) {
+            cbrk[j] += __shfl_xor_sync(0xffffffffu, cbrk[j], o);
+            cbik[j] += __shfl_xor_sync(0xffffffffu, cbik[j], o);
+          }
+        }
+        if ((tid & 7) == 0) {
+#pragma unroll
+          for (int j = 0; j < IPT; ++j) {
+            const int r = (tid + NT * j) >> 3;
+            // diagonal term Re sum conj(c) kc b = Re(kc conj(sum c conj(b)))
+            sw[2 * 64 + r] = sc[8 * 64 + r] * cbrk[j] + sc[9 * 64 + r] * cbik[j];
+            sw[3 * 64 + r] = cbrk[j]; sw[4 * 64 + r] = cbik[j];
+          }
+        }
       }
     }
     SL_TOCK(4)

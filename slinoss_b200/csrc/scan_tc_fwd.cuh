@@ -191,18 +191,25 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       // waiting and move on.
       const uint64_t bU = make_desc(smem_u32(st), 8192, 1024);
       const uint32_t tSY = tmem + 128 * (c & 1), tYD = tmem + 256 + 64 * (c & 1), tINC = tmem + 384;
+      // scores and off-term: [S | Yoff] = Q [K' ; Zv]^T, accumulated over the state dimension
+      const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);       // [K'_h ; Zv_h], h = k >> 2
+      const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
+      bar_sync(5, NT + 32);   // first column halves of Q and K' rotated (the Zv tile is the previous chunk's)
+      if (!STATES_ONLY && lane == 0 && s_abort == 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma(tSY, desc_adv(bC, k * 32), desc_adv(bB, k * 32), ID_S, k > 0);
+      }
+      __syncwarp();
       bar_sync(2, NT + 64);   // rotation done: Q, K', K'' written; U landed; Zv tile stored by the previous chunk
       const bool go = lane == 0 && s_abort == 0;
       if (go) {
         tc_fence_after_sync();
         if (!STATES_ONLY) {
-          // scores and off-term: [S | Yoff] = Q [K' ; Zv]^T
-          const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);       // [K'_h ; Zv_h], h = k >> 2
-          const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma(tSY, desc_adv(bC, (k >> 2) * TILE + (k & 3) * 32),
-                 desc_adv(bB, (k >> 2) * 2 * TILE + (k & 3) * 32), ID_S, k > 0);
+          for (int k = 4; k < 8; ++k)
+            umma(tSY, desc_adv(bC, TILE + (k & 3) * 32), desc_adv(bB, 2 * TILE + (k & 3) * 32), ID_S, 1);
           umma_commit(&bar_mma[0]);
         }
         // Inc = U^T K''
@@ -252,61 +259,74 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     SL_TICK(1)
 
     // ---- rotation: C -> Q, B -> K' (both in place), K'' ; diagonal scores --------------------
-    if (live) {
-      const uint32_t half = rcol >> 3, ch = rcol & 7;
-      uint8_t* tB = st + (1 + 2 * half) * TILE;
-      uint8_t* tC = st + (5 + half) * TILE;
-      uint8_t* tK = smem + OFF_KPP + half * TILE;
-      // All loads of this thread's rows first, then the arithmetic and the (in place) stores, then the
-      // row sums of all rows side by side: the compiler cannot move a load above an earlier store to
-      // the same tiles, nor interleave the shuffle chains of different rows, by itself.
-      constexpr int RK = 64 / RSTEP;
-      uint4 cvk[RK], bvk[RK];
-      float dgk[RK];
+    // Two phases, one per 64-column half of the state dimension: the score products accumulate over
+    // that dimension, so the issue warp starts their first four k-steps (named barrier 5) while the
+    // workers still rotate the second half.  A thread keeps its rows in both phases (8 threads per
+    // row, one 16-byte piece each), so the diagonal sums stay in registers until the end.
+    {
+      constexpr int IPT = 512 / NT;   // (row, piece) items per thread and phase
+      float dgk[IPT];
 #pragma unroll
-      for (int k = 0; k < RK; ++k) {
-        const uint32_t off = sw128(rrow0 + RSTEP * k, ch);
-        cvk[k] = make_uint4(0u, 0u, 0u, 0u);
-        if (!STATES_ONLY) cvk[k] = *reinterpret_cast<const uint4*>(tC + off);
-        bvk[k] = *reinterpret_cast<const uint4*>(tB + off);
+      for (int j = 0; j < IPT; ++j) dgk[j] = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (live) {
+          uint8_t* tB = st + (1 + 2 * half) * TILE;
+          uint8_t* tC = st + (5 + half) * TILE;
+          uint8_t* tK = smem + OFF_KPP + half * TILE;
+          uint4 cvk[IPT], bvk[IPT];
+#pragma unroll
+          for (int j = 0; j < IPT; ++j) {   // all loads first: the stores below are in place
+            const int item = tid + NT * j;
+            const uint32_t off = sw128(item >> 3, item & 7);
+            cvk[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (!STATES_ONLY) cvk[j] = *reinterpret_cast<const uint4*>(tC + off);
+            bvk[j] = *reinterpret_cast<const uint4*>(tB + off);
+          }
+#pragma unroll
+          for (int j = 0; j < IPT; ++j) {
+            const int item = tid + NT * j, r = item >> 3;
+            const uint32_t off = sw128(r, item & 7);
+            const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
+            const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
+            const float vr = sc[6 * 64 + r], vi = sc[7 * 64 + r];
+            const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
+            const uint4 cv = cvk[j], bv = bvk[j];
+            const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+            uint32_t qo[4], ko[4], vo[4];
+            float dg = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
+              qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
+              ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
+              vo[e] = PK::pack(vr * bb.x - vi * bb.y, -(vr * bb.y + vi * bb.x));      // conj(v b)
+              const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
+              dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
+            }
+            dgk[j] += dg;
+            *reinterpret_cast<uint4*>(tK + off) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
+            if (!STATES_ONLY) {
+              *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+              *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+            }
+          }
+        }
+        if (half == 0) {   // first halves of Q and K' are complete: the score products may start
+          fence_async_smem();
+          tc_fence_before_sync();
+          bar_arrive(5, NT + 32);
+        }
       }
+      if (live && !STATES_ONLY) {
 #pragma unroll
-      for (int k = 0; k < RK; ++k) {
-        const int r = rrow0 + RSTEP * k;
-        const uint32_t off = sw128(r, ch);
-        const float phr = sc[2 * 64 + r], phi = sc[3 * 64 + r];
-        const float wr = sc[4 * 64 + r], wi = sc[5 * 64 + r];
-        const float vr = sc[6 * 64 + r], vi = sc[7 * 64 + r];
-        const float kr = sc[8 * 64 + r], ki = sc[9 * 64 + r];
-        const uint4 cv = cvk[k], bv = bvk[k];
-        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-        uint32_t qo[4], ko[4], vo[4];
-        float dg = 0.f;
+        for (int o = 4; o > 0; o >>= 1) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 cc = PK::unpack(cw[e]), bb = PK::unpack(bw[e]);
-          qo[e] = PK::pack(cc.x * phr + cc.y * phi, cc.x * phi - cc.y * phr);     // conj(c) phi
-          ko[e] = PK::pack(wr * bb.x - wi * bb.y, -(wr * bb.y + wi * bb.x));      // conj(w b)
-          vo[e] = PK::pack(vr * bb.x - vi * bb.y, -(vr * bb.y + vi * bb.x));      // conj(v b)
-          const float xr = kr * bb.x - ki * bb.y, xi = kr * bb.y + ki * bb.x;     // kc b
-          dg += cc.x * xr + cc.y * xi;                                            // Re(conj(c) kc b)
+          for (int j = 0; j < IPT; ++j) dgk[j] += __shfl_xor_sync(0xffffffffu, dgk[j], o);
         }
-        dgk[k] = dg;
-        *reinterpret_cast<uint4*>(tK + off) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
-        if (!STATES_ONLY) {
-          *reinterpret_cast<uint4*>(tC + off) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
-          *reinterpret_cast<uint4*>(tB + off) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
-        }
-      }
-      if (!STATES_ONLY) {
+        if ((tid & 7) == 0) {
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
-#pragma unroll
-          for (int k = 0; k < RK; ++k) dgk[k] += __shfl_xor_sync(0xffffffffu, dgk[k], o);
-        }
-        if (rcol == 0) {
-#pragma unroll
-          for (int k = 0; k < RK; ++k) s_diag[rrow0 + RSTEP * k] = dgk[k];
+          for (int j = 0; j < IPT; ++j) s_diag[(tid + NT * j) >> 3] = dgk[j];
         }
       }
     }
