@@ -476,8 +476,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     SL_TOCK(4)
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(3, NT);             // workers only ...
-    bar_arrive(2, NT + 64);      // ... the scalar and issue warps are told without being waited for
+    // no barrier among the workers here or at the end of the gap below: what a warp does next (epilogue 5
+    // of the previous chunk, dWv, the decay factors) touches nothing the passes of another warp read or
+    // write; the workers meet at the end of epilogue 1
+    bar_arrive(2, NT + 64);      // the scalar and issue warps are told without being waited for
     live = s_abort == 0;
     SL_TOCK(5)
     // ---- in the shadow of the P~ MMAs: epilogue 5 of the previous iteration, then this chunk's dWv ------
@@ -488,7 +490,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     em_keep = sc[1 * 64 + 63];
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(3, NT);
     bar_arrive(6, NT + 32);      // dWv written, the previous dZ accumulator and Zv tiles released
     bar_arrive(7, NT + 32);      // anchor partial sums written: the scalar warp adds them up and stores
     SL_TOCK(22)
