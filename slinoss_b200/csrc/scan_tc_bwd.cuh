@@ -373,6 +373,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         if (!mbar_wait(&bar_st[2], it & 1)) { report_timeout(19); s_abort = 1; break; }
         tma_store_3d(&p.tmdU, tDY, 0, t0, bh);
         tma_store_commit();
+        // The next iteration's passes overwrite the dYoff and Q tiles that the dZ products (issued after
+        // everything the workers wait for in this iteration) read: this lane sees them complete before it
+        // joins the barrier that ends the iteration.
+        if (!mbar_wait(&bar_mma[4], it & 1)) { report_timeout(21); s_abort = 1; break; }
       } while (false);
       __syncwarp();
     } else {

@@ -332,8 +332,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     }
     fence_async_smem();
     tc_fence_before_sync();
-    bar_sync(3, NT);             // workers only ...
-    bar_arrive(2, NT + 64);      // ... the scalar and issue warps are told without being waited for
+    // no barrier among the workers here: what a warp does next (the previous chunk's output, its decay
+    // factors) touches nothing the rotation of another warp reads or writes; the diagonal values of
+    // other warps are read after the score products' barrier, which all rotations precede
+    bar_arrive(2, NT + 64);      // the scalar and issue warps are told without being waited for
     live = s_abort == 0;
     SL_TICK(2)
 
@@ -357,7 +359,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         for (int hh = 0; hh < 2; ++hh) {
           const int R = hh ? rowB : rowA;
           const float lt = sc[R];
-          dg2[hh] = s_diag[R];
 #pragma unroll
           for (int k = 0; k < 2 * SB; ++k) dfac[hh * 2 * SB + k] = __expf(fminf(lt - ls[k], 0.f));
         }
@@ -373,6 +374,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         tmem_ld_16x256<SB>(tmem + lane_base + 128 * (c & 1) + cg * SC, r);
         tmem_ld_wait();
         et_keep[0] = et_next[0]; et_keep[1] = et_next[1];
+        dg2[0] = s_diag[rowA]; dg2[1] = s_diag[rowB];
         uint8_t* tS = smem + OFF_S + 4 * cq;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -394,8 +396,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       }
       fence_async_smem();
       tc_fence_before_sync();
-      bar_sync(3, NT);
-      bar_arrive(4, NT + 32);   // the issue warp now issues Y_diag = S U
+      bar_arrive(4, NT + 32);   // the issue warp now issues Y_diag = S U (no barrier among the workers)
       live = s_abort == 0;
       SL_TICK(5)
     }
