@@ -47,7 +47,7 @@ METRIC = "v2x2ssd fwd+bwd tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the backward sweep at this exact
 # workload, from the committed ncu capture (a profiler figure, not measured live by this script)
-NCU_TRAFFIC_BWD_BYTES = 549_593_856 + 312_372_480
+NCU_TRAFFIC_BWD_BYTES = 549_817_344 + 312_087_040
 NCU_TRAFFIC_SOURCE = "profiles/scan_tc_fwd_bwd_config1.md (ncu --set full, one launch)"
 
 
