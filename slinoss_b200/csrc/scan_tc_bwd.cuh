@@ -101,7 +101,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
 
-  auto issue_loads = [&](int c, int it) {   // one thread
+  // The stage of chunk c is filled in two batches: the six input tiles as soon as the output stores of the
+  // chunk that used the stage before have read it (top of the previous iteration), the two state tiles once
+  // that chunk's deferred epilogue 5 has read them (a chunk ahead was not enough for the whole stage any more:
+  // the workers were seen waiting 1000+ clk for the data).
+  auto issue_loads_inputs = [&](int c, int it) {   // one thread; also arms the barrier for the whole stage
     uint8_t* st = smem + (it & 1) * B_STAGE;
     uint64_t* bar = &bar_tma[it & 1];
     mbar_expect_tx(bar, B_STAGE);
@@ -111,10 +115,14 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bh);
     tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bh);
     tma_load_3d(st + 5 * TILE, &p.tmdY, bar, 0, c * L, bh);
+  };
+  auto issue_loads_states = [&](int c, int it) {   // one thread
+    uint8_t* st = smem + (it & 1) * B_STAGE;
+    uint64_t* bar = &bar_tma[it & 1];
     tma_load_3d(st + 6 * TILE, &p.tmZ, bar, 0, c * 64, bh);
     tma_load_3d(st + 7 * TILE, &p.tmZ, bar, 64, c * 64, bh);
   };
-  if (tid == 0) issue_loads(nC - 1, 0);
+  if (tid == 0) { issue_loads_inputs(nC - 1, 0); issue_loads_states(nC - 1, 0); }
 
   auto block_sum2 = [&](float a, float b, float& oa, float& ob) {
     a = warp_sum(a); b = warp_sum(b);   // workers only
@@ -285,6 +293,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         for (int k = 0; k < 4; ++k)
           // dS[t][s] = sum_p dY[t][p] U[s][p]            A: dY K-major, B: U K-major rows s
           umma(tmem + 64, desc_adv(kDY, 32 * k), desc_adv(kU, 32 * k), ID_KK64, k > 0);
+        if (it + 1 < nC) {   // next chunk's input tiles
+          tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
+          issue_loads_inputs(c - 1, it + 1);
+        }
       } while (false);
       __syncwarp();
       // (1b) the first four k-steps of P~, once the first column halves of Q and K' are rotated
@@ -319,10 +331,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       bar_sync(6, NT + 32);
       if (go && s_abort == 0) {
         tc_fence_after_sync();
-        if (it + 1 < nC) {   // next chunk's tiles
-          tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
-          issue_loads(c - 1, it + 1);
-        }
+        if (it + 1 < nC) issue_loads_states(c - 1, it + 1);   // next chunk's state tiles
         SL_TOCK_MMA(18)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
