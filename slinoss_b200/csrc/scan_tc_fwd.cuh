@@ -194,6 +194,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       // scores and off-term: [S | Yoff] = Q [K' ; Zv]^T, accumulated over the state dimension
       const uint64_t bB = make_desc(smem_u32(st + TILE), 16, 1024);       // [K'_h ; Zv_h], h = k >> 2
       const uint64_t bC = make_desc(smem_u32(st + 5 * TILE), 16, 1024);   // Q
+      if (lane == 0 && s_abort == 0 && c + 1 < p.nchunks) {
+        // Next chunk's tiles, a whole iteration ahead (half an iteration was not always enough for the data
+        // to arrive).  The stage being refilled held chunk c-1, whose last reader is its Y_diag MMA.
+        if (!STATES_ONLY && c > 0 && !mbar_wait(&bar_mma[2], (c - 1) & 1)) { report_timeout(8); s_abort = 1; }
+        else issue_loads(c + 1);
+      }
+      __syncwarp();
       bar_sync(5, NT + 32);   // first column halves of Q and K' rotated (the Zv tile is the previous chunk's)
       if (!STATES_ONLY && lane == 0 && s_abort == 0) {
         tc_fence_after_sync();
@@ -219,11 +226,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
           umma(tINC, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
         umma_commit(&bar_mma[1]);
         SL_TICK_MMA(3)
-        if (c + 1 < p.nchunks) {   // next chunk's tiles, after the workers' burst
-          // the stage being refilled held chunk c-1, whose last reader is its Y_diag MMA
-          if (!STATES_ONLY && c > 0 && !mbar_wait(&bar_mma[2], (c - 1) & 1)) { report_timeout(8); s_abort = 1; }
-          issue_loads(c + 1);
-        }
         if (p.states16) {   // the 16-bit state tile of this chunk is exactly what the backward wants
           tma_store_3d(&p.tmS, st + 2 * TILE, 0, c * 64, bh);
           tma_store_3d(&p.tmS, st + 4 * TILE, 64, c * 64, bh);
