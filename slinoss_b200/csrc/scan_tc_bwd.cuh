@@ -101,10 +101,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
 
-  // The stage of chunk c is filled in two batches: the six input tiles as soon as the output stores of the
-  // chunk that used the stage before have read it (top of the previous iteration), the two state tiles once
-  // that chunk's deferred epilogue 5 has read them (a chunk ahead was not enough for the whole stage any more:
-  // the workers were seen waiting 1000+ clk for the data).
+  // The stage of chunk c is requested at the top of the previous iteration, as soon as the output stores of
+  // the chunk that used the stage before have read it (half an iteration ahead was not enough any more: the
+  // workers were seen waiting 1000+ clk for the data).  That chunk's deferred epilogue 5 works on a register
+  // copy of its Zv cells.
   auto issue_loads_inputs = [&](int c, int it) {   // one thread; also arms the barrier for the whole stage
     uint8_t* st = smem + (it & 1) * B_STAGE;
     uint64_t* bar = &bar_tma[it & 1];
@@ -183,13 +183,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   // ---- epilogue 5 of the chunk of iteration itp (run one iteration late): dz <- e^{l_end} dWv + dZ,
   // and the anchor S = <dz, z> of the boundary below that chunk ------------------------------------------
   float em_keep = 0.f;   // e^{l_end} of the chunk whose epilogue 5 is pending
+  uint4 zv_keep[ZC / 8];  // and this thread's cells of its Zv tiles
+#pragma unroll
+  for (int ch = 0; ch < ZC / 8; ++ch) zv_keep[ch] = make_uint4(0u, 0u, 0u, 0u);
   auto epilogue5 = [&](int itp, bool live) {
     const int cp = nC - 1 - itp;
-    const uint8_t* tZp = smem + (itp & 1) * B_STAGE + 6 * TILE;
-    uint4 zvv[ZC / 8];   // this thread's cells of the Zv tiles, fetched ahead of the wait (a compiler barrier)
-#pragma unroll
-    for (int ch = 0; ch < ZC / 8; ++ch)
-      zvv[ch] = *reinterpret_cast<const uint4*>(tZp + hf * TILE + sw128(row, d0 / 8 + ch));
+    // (this thread's cells of that chunk's Zv tiles were copied to zv_keep at the end of its iteration, so
+    // that the whole stage can be refilled at the top of the next one)
     if (live && !mbar_wait(&bar_mma[4], itp & 1)) { report_timeout(16); s_abort = 1; live = false; }
     tc_fence_after_sync();
     const float em = em_keep;
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < PC / 8; ++ch) {
-          const uint4 zv4 = zvv[(PC / 8) * part + ch];
+          const uint4 zv4 = zv_keep[(PC / 8) * part + ch];
           const uint32_t zw[4] = {zv4.x, zv4.y, zv4.z, zv4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -296,6 +296,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         if (it + 1 < nC) {   // next chunk's input tiles
           tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
           issue_loads_inputs(c - 1, it + 1);
+          issue_loads_states(c - 1, it + 1);
         }
       } while (false);
       __syncwarp();
@@ -331,7 +332,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       bar_sync(6, NT + 32);
       if (go && s_abort == 0) {
         tc_fence_after_sync();
-        if (it + 1 < nC) issue_loads_states(c - 1, it + 1);   // next chunk's state tiles
         SL_TOCK_MMA(18)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
@@ -698,6 +698,9 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     SL_TOCK(13)
     // (epilogue 5 of this chunk - the update of dz - runs in the next iteration, in the shadow of the
     // P~ MMAs; its inputs, the dZ accumulator and the Zv tiles of this stage, stay untouched until then)
+#pragma unroll
+    for (int ch = 0; ch < ZC / 8; ++ch)   // for the deferred epilogue 5 of this chunk
+      zv_keep[ch] = *reinterpret_cast<const uint4*>(tZ + hf * TILE + sw128(row, d0 / 8 + ch));
     bar_sync(1, NT);   // the partial sums written by epilogues 2 and 3 are read by other threads below
     // the proxy fence for this iteration's shared-memory accesses goes BEFORE the global stores
     // below (the code after them touches no tile)
