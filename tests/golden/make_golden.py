@@ -183,6 +183,96 @@ def golden_mixer(slinoss):
     np.savez_compressed(HERE / "mixer.npz", **d)
 
 
+def golden_scanprep_fp64(slinoss):
+    """The reference's scan preparation evaluated in float64 (module and inputs cast to double):
+    the exact value of the same formulas, which the float32 evaluation reaches only to its own
+    round-off (the tap quotients cancel for small |z|)."""
+    # The reference's coefficient code casts to float32 in two helpers (principal_angle and
+    # _pack_complex, slinoss/ops/scanprep/reference.py:11-22); they are replaced here, for this call
+    # only, by the same two formulas without the cast, so that its own code runs in float64 throughout.
+    import slinoss.layers.scanprep as lsp
+    import slinoss.ops.scanprep.reference as osr
+    two_pi = 2.0 * math.pi
+    keep = (lsp.principal_angle, osr._pack_complex, lsp._pack_complex)
+    lsp.principal_angle = lambda th: torch.remainder(th + math.pi, two_pi) - math.pi
+    osr._pack_complex = lsp._pack_complex = lambda x: torch.view_as_real(x).contiguous()
+    try:
+        _golden_scanprep_fp64(slinoss)
+    finally:
+        lsp.principal_angle, osr._pack_complex, lsp._pack_complex = keep
+
+
+def _golden_scanprep_fp64(slinoss):
+    m = _mixer_module(slinoss, bc_groups=2).double()
+    sp = m.scanprep
+    g = torch.Generator().manual_seed(2)
+    b, T = 2, 12
+    value = torch.randn(b, T, m.d_inner, generator=g).double().requires_grad_(True)
+    params = torch.randn(b, T, m.param_proj_dim, generator=g).double().requires_grad_(True)
+    bc = torch.randn(b, T, m.bc_groups, 4, m.d_state, generator=g).double().requires_grad_(True)
+    from slinoss.layers.backend import ScanPrepInputs
+    si = sp._prepare_inputs_reference(ScanPrepInputs(value=value, params=params, bc=bc))
+    outs = [si.U, si.M, si.K, si.B, si.C]
+    assert all(o.dtype == torch.float64 for o in (si.M, si.K)), [o.dtype for o in outs]
+    cots = [torch.randn(o.shape, generator=g).double() for o in outs]
+    wrt = [value, params, bc, sp.dt_bias, sp.alpha_bias, sp.theta_mod_bias, sp.theta_bias]
+    grads = torch.autograd.grad(outs, wrt, cots)
+    d = dict(value=_np(value), params=_np(params), bc=_np(bc))
+    d.update({k: _np(getattr(sp, k)) for k in ("dt_bias", "alpha_bias", "theta_mod_bias",
+                                               "theta_bias", "theta_sign")})
+    d.update({k: _np(o) for k, o in zip(("U", "M", "K", "B", "C"), outs)})
+    d.update({"cot_" + k: _np(o) for k, o in zip(("U", "M", "K", "B", "C"), cots)})
+    d.update({"d_" + k: _np(gr) for k, gr in zip(("value", "params", "bc", "dt_bias", "alpha_bias",
+                                                  "theta_mod_bias", "theta_bias"), grads)})
+    d["dims"] = np.array([m.n_heads, m.bc_groups, m.d_state, m.d_head])
+    np.savez_compressed(HERE / "scanprep_fp64.npz", **d)
+
+
+def golden_tail_fp64(slinoss):
+    """The reference's mixer tail in float64 on the inputs of the float32 fixture."""
+    from slinoss.ops.mixer.tail import _mixer_tail_forward
+    t = dict(np.load(HERE / "tail.npz"))
+    leaf = lambda k: torch.from_numpy(t[k]).double().requires_grad_(True)
+    Y, U, gate, d_skip, nw, pw = (leaf(k) for k in ("Y", "U", "gate", "d_skip", "norm_weight",
+                                                    "proj_weight"))
+    out = _mixer_tail_forward(Y, gate, nw, float(t["eps"]), pw, None, skip_input=U, d_skip=d_skip)
+    grads = torch.autograd.grad(out, [Y, gate, U, d_skip, nw, pw], torch.from_numpy(t["cot"]).double())
+    d = {"out": _np(out)}
+    d.update({"d_" + k: _np(gr) for k, gr in zip(("Y", "gate", "U", "d_skip", "norm_weight",
+                                                  "proj_weight"), grads)})
+    np.savez_compressed(HERE / "tail_fp64.npz", **d)
+
+
+def golden_stack(slinoss):
+    """Two-block stack (mixer + gelu FFN, final norm): forward, gradients and three decode steps."""
+    import slinoss.blocks as rb
+    torch.manual_seed(7)
+    cfg = rb.SLinOSSStackConfig.uniform(
+        rb.SLinOSSBlockConfig(d_model=32, mixer=rb.SLinOSSMixerConfig(d_state=8, d_head=16, chunk_size=8),
+                              ffn=rb.SLinOSSMLPConfig(kind="gelu", expand=2.0, multiple_of=8)), n_layers=2)
+    stack = rb.SLinOSSStack(cfg)
+    with torch.no_grad():
+        for n, p in stack.named_parameters():
+            if "scanprep" in n or "norm" in n:
+                p.add_(0.2 * torch.randn_like(p))
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(2, 19, 32, generator=g, requires_grad=True)
+    out = stack(x)
+    cot = torch.randn(out.shape, generator=g)
+    names = [n for n, _ in stack.named_parameters()]
+    grads = torch.autograd.grad(out, [x, *stack.parameters()], cot)
+    d = {"sd_" + k: _np(v) for k, v in stack.state_dict().items()}
+    d.update(x=_np(x), out=_np(out), cot=_np(cot), d_x=_np(grads[0]))
+    d.update({"dp_" + n: _np(gr) for n, gr in zip(names, grads[1:])})
+    with torch.no_grad():
+        state, steps = None, []
+        for t in range(3):
+            y, state = stack.step(x[:, t], state)
+            steps.append(y)
+        d["out_steps"] = _np(torch.stack(steps, 1))
+    np.savez_compressed(HERE / "stack.npz", **d)
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <path of a checkout of the reference (slinoss)>")
@@ -199,6 +289,9 @@ def main():
     golden_conv(slinoss)
     golden_tail(slinoss)
     golden_mixer(slinoss)
+    golden_scanprep_fp64(slinoss)
+    golden_tail_fp64(slinoss)
+    golden_stack(slinoss)
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)
 

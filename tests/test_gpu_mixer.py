@@ -102,6 +102,31 @@ def test_scanprep_against_reference_golden(golden):
             (name, rel(gr, g["d_" + name]))
 
 
+def test_scanprep_against_the_reference_evaluated_in_float64(golden):
+    """The strict bar for the coefficient kernels: the reference's own scan preparation run in
+    float64 (tests/golden/make_golden.py, golden_scanprep_fp64).  M, K and the gradients that flow
+    through the taps and the saturating sigmoids agree to 1e-5; the looser bounds against the
+    float32 golden above are the reference's float32 round-off, not the kernels'."""
+    g = golden("scanprep_fp64")
+    H, G, N, P = map(int, g["dims"])
+    sp = sb.SLinOSSScanPrep(n_heads=H, bc_groups=G, d_state=N, d_head=P).to(DEV)
+    with torch.no_grad():
+        for k in ("dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias"):
+            getattr(sp, k).copy_(torch.from_numpy(g[k]).float())
+    t = lambda k: torch.from_numpy(g[k]).float().to(DEV).requires_grad_(True)
+    value, params, bc = t("value"), t("params"), t("bc")
+    out = sp(value, params, bc)
+    for name in "UMKBC":
+        assert rel(getattr(out, name), g[name]) <= 1e-5, (name, rel(getattr(out, name), g[name]))
+    grads = torch.autograd.grad([out.U, out.M, out.K, out.B, out.C],
+                                [value, params, bc, sp.dt_bias, sp.alpha_bias, sp.theta_mod_bias,
+                                 sp.theta_bias],
+                                [torch.from_numpy(g["cot_" + k]).float().to(DEV) for k in "UMKBC"])
+    for name, gr in zip(("value", "params", "bc", "dt_bias", "alpha_bias", "theta_mod_bias",
+                         "theta_bias"), grads):
+        assert rel(gr, g["d_" + name]) <= 1e-5, (name, rel(gr, g["d_" + name]))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dims", [(2, 11, 64, 4, True), (1, 2, 40, 4, True), (3, 70, 96, 3, False),
                                   (2, 33, 8, 2, True), (1, 5, 16, 1, False)])
@@ -163,6 +188,17 @@ def test_tail_forward_backward(dims, dtype):
         assert rel(a, w_) <= (tol(dtype) if dtype == torch.bfloat16 else 1e-4), (name, rel(a, w_))
 
 
+def test_tail_against_the_reference_evaluated_in_float64(golden):
+    g, g64 = golden("tail"), golden("tail_fp64")
+    t = lambda k: torch.from_numpy(g[k]).to(DEV).requires_grad_(True)
+    Y, U, gate, ds, nw, pw = t("Y"), t("U"), t("gate"), t("d_skip"), t("norm_weight"), t("proj_weight")
+    out = torch.nn.functional.linear(mixer_gated_norm(Y, gate, nw, float(g["eps"]), skip_input=U, d_skip=ds), pw)
+    assert rel(out, g64["out"]) <= 1e-5
+    grads = torch.autograd.grad(out, [Y, gate, U, ds, nw, pw], torch.from_numpy(g["cot"]).to(DEV))
+    for name, gr in zip(("Y", "gate", "U", "d_skip", "norm_weight", "proj_weight"), grads):
+        assert rel(gr, g64["d_" + name]) <= 1e-5, (name, rel(gr, g64["d_" + name]))
+
+
 def _load_mixer(g, dtype=torch.float32, **kw):
     m = sb.SLinOSSMixer(32, d_state=8, expand=2, d_head=16, d_conv=4, chunk_size=8, bc_groups=2, **kw)
     m.load_state_dict({k[3:]: torch.from_numpy(v) for k, v in g.items() if k.startswith("sd_")})
@@ -190,6 +226,35 @@ def test_mixer_against_reference_golden(golden):
         state, ys = None, []
         for t in range(3):
             y, state = m.step(x[:, t], state)
+            ys.append(y)
+        assert rel(torch.stack(ys, 1), g["out_steps"]) <= 5e-5
+
+
+def test_stack_against_reference_golden(golden):
+    """Two blocks (mixer + gelu FFN, final norm) with the reference's weights: forward, every
+    gradient and three decode steps against the reference's own float32 results.  The bounds are
+    those of the mixer golden: the GEMMs run in cuBLAS here and in the CPU BLAS there (different
+    summation order), and the scan-preparation bias gradients of the golden carry the reference's
+    float32 round-off."""
+    g = golden("stack")
+    cfg = sb.SLinOSSStackConfig.uniform(
+        sb.SLinOSSBlockConfig(d_model=32, mixer=sb.SLinOSSMixerConfig(d_state=8, d_head=16, chunk_size=8),
+                              ffn=sb.SLinOSSMLPConfig(kind="gelu", expand=2.0, multiple_of=8)), n_layers=2)
+    stack = sb.SLinOSSStack(cfg)
+    stack.load_state_dict({k[3:]: torch.from_numpy(v) for k, v in g.items() if k.startswith("sd_")})
+    stack = stack.to(DEV)
+    x = torch.from_numpy(g["x"]).to(DEV).requires_grad_(True)
+    out = stack(x)
+    assert rel(out, g["out"]) <= 5e-5, rel(out, g["out"])
+    grads = torch.autograd.grad(out, [x, *stack.parameters()], torch.from_numpy(g["cot"]).to(DEV))
+    assert rel(grads[0], g["d_x"]) <= 1e-4
+    for (name, _), gr in zip(stack.named_parameters(), grads[1:]):
+        t = 5e-2 if ".scanprep." in name else 2e-4
+        assert rel(gr, g["dp_" + name]) <= t, (name, rel(gr, g["dp_" + name]))
+    with torch.no_grad():
+        state, ys = None, []
+        for t in range(3):
+            y, state = stack.step(x[:, t], state)
             ys.append(y)
         assert rel(torch.stack(ys, 1), g["out_steps"]) <= 5e-5
 

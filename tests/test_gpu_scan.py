@@ -193,6 +193,28 @@ def test_full_size_config1_properties():
     assert rel(torch.cat([Ya, Yb], 2), Y) <= 2e-2 and rel(fb, fin) <= 2e-2
 
 
+def test_full_size_config1_forward_and_backward_of_whole_streams():
+    """The configuration the benchmark times (batch 8, heads 16, T 4096, bf16, 128 CTAs x 64 chunks):
+    Y and all five gradients of three whole (batch, head) streams from different batch entries
+    against the float64 oracle, which handles single streams of that length in seconds."""
+    case = make_scan_case(8, 16, 4096, 64, 64, dtype=torch.bfloat16, seed=0)
+    c = case.to(DEV)
+    leaves = [t.clone().requires_grad_(True) for t in c.tensors()]
+    Y = v2x2ssd_cute(*leaves, chunk_size=64)
+    grads = torch.autograd.grad(Y, leaves, c.dY)
+    from slinoss_b200 import _C
+    assert _C.device_status() == 0
+    for (b, h) in ((0, 0), (3, 5), (7, 15)):
+        sl = lambda t: t[b:b + 1, h:h + 1].contiguous()
+        args = [n64(sl(t)) for t in case.tensors()]
+        wY = scan_np.v2x2ssm(*args)[0]
+        want = scan_np.v2x2ssd_bwd(*args, n64(sl(case.dY)))
+        assert rel(sl(Y), wY) <= 2e-2, (b, h, rel(sl(Y), wY))
+        for name, gr in zip("UMKBC", grads):
+            assert torch.isfinite(sl(gr)).all(), (b, h, name)
+            assert rel(sl(gr), want[name]) <= 2e-2, (b, h, name, rel(sl(gr), want[name]))
+
+
 # ---- tensor-core (tcgen05) path: P = 64, N = 64, 16-bit operands -------------------------------
 TC_SHAPES = [
     (1, 1, 1, 64, False, False),
@@ -236,6 +258,8 @@ def test_tensor_core_path_agrees_with_exact_path_on_reference_test_distribution(
     a = v2x2ssd(U, M, K, B, C, chunk_size=64, path="tc", output_dtype=torch.float32)
     e = v2x2ssd(U, M, K, B, C, chunk_size=64, path="simt", output_dtype=torch.float32)
     assert rel(a[0], e[0]) <= 2e-2 and rel(a[1], e[1]) <= 2e-2
+    wY, wfin, _, _ = scan_np.v2x2ssm(*[n64(t) for t in (U, M, K, B, C)])
+    assert rel(a[0], wY) <= 2e-2 and rel(a[1], wfin) <= 2e-2
 
 
 def test_auto_path_prefers_tensor_cores_and_falls_back_for_float32():
@@ -301,6 +325,9 @@ def test_backward_tensor_core_agrees_with_exact_path_at_strong_decay():
         res[path] = torch.autograd.grad(Y, lv, dY)
     for name, a, e in zip("UMKBC", res["tc"], res["simt"]):
         assert rel(a, e) <= 2e-2, (name, rel(a, e))
+    want = scan_np.v2x2ssd_bwd(*[n64(t) for t in (U, M, K, B, C)], n64(dY))
+    for name, a in zip("UMKBC", res["tc"]):
+        assert rel(a, want[name]) <= 2e-2, (name, rel(a, want[name]))
 
 
 def test_saved_chunk_states_and_recompute_give_the_same_gradients():

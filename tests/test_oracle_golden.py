@@ -141,3 +141,76 @@ def test_tail_forward_and_gradients(golden):
     grads = torch.autograd.grad(out, [Y, gate, U, ds, nw, pw], torch.from_numpy(g["cot"]))
     for name, gr in zip(("Y", "gate", "U", "d_skip", "norm_weight", "proj_weight"), grads):
         assert rel(gr.numpy(), g["d_" + name]) < 1e-5, name
+
+
+def test_scanprep_float64_branch_is_the_reference_in_float64(golden):
+    """The float64 evaluation of scan preparation (``coeff_dtype=float64``) against the reference's
+    own code run in float64: this is what the CUDA kernels' float64 tap arithmetic is held to."""
+    g = golden("scanprep_fp64")
+    t = lambda k, rg=False: torch.from_numpy(g[k]).double().requires_grad_(rg)
+    H, G, N, P = map(int, g["dims"])
+    value, params, bc = t("value", True), t("params", True), t("bc", True)
+    biases = [t(k, True) for k in ("dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias")]
+    # M and K as float64 straight from the coefficient stage (the packing casts them to float32)
+    bsz, T, _ = params.shape
+    p4 = params.view(bsz, T, H, 3).permute(0, 2, 1, 3) + torch.stack(biases[:3], -1).view(1, H, 1, 3)
+    cfg = _cfg()
+    dt = cfg["dt_min"] + (cfg["dt_max"] - cfg["dt_min"]) * torch.sigmoid(p4[..., 0])
+    alpha = cfg["alpha_min"] + (cfg["alpha_max"] - cfg["alpha_min"]) * torch.sigmoid(p4[..., 1])
+    span = cfg["theta_init_max"] - cfg["theta_init_min"]
+    theta_u = torch.sigmoid(biases[3].view(1, H, 1) + cfg["theta_mod_scale"] * torch.tanh(p4[..., 2]))
+    theta = mt._wrap_angle(t("theta_sign").view(1, H, 1) * (cfg["theta_init_min"] + span * theta_u))
+    r = cfg["r_min"] + (cfg["r_max"] - cfg["r_min"]) * torch.exp(-alpha)
+    rho = torch.polar(r, theta)
+    kp, kc = mt.foh_taps(dt, torch.log(r), theta, rho, cfg["eps"])
+    M = torch.view_as_real(rho)
+    K = torch.stack((torch.view_as_real(kp), torch.view_as_real(kc)), dim=-2)
+    assert rel(M.detach().numpy(), g["M"]) < 1e-12 and rel(K.detach().numpy(), g["K"]) < 1e-12
+    grads = torch.autograd.grad([M, K], [params, *biases], [t("cot_M"), t("cot_K")])
+    for name, gr in zip(("params", "dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias"), grads):
+        # (the reference rounds the params gradient to float32 on its way back through its input cast)
+        assert rel(gr.numpy(), g["d_" + name]) < (1e-7 if name == "params" else 1e-10), name
+    # ... and the packed call agrees with it to the float32 rounding of its outputs
+    outs = mt.scanprep(value.float(), params.float(), bc.float(), cfg, *[b.float() for b in biases],
+                       t("theta_sign").float(), P, coeff_dtype=torch.float64)
+    assert rel(outs[1].detach().numpy(), g["M"]) < 1e-7 and rel(outs[2].detach().numpy(), g["K"]) < 1e-7
+
+
+def test_tail_float64_against_the_reference_in_float64(golden):
+    g, g64 = golden("tail"), golden("tail_fp64")
+    t = lambda k: torch.from_numpy(g[k]).double().requires_grad_(True)
+    Y, U, gate, ds, nw, pw = t("Y"), t("U"), t("gate"), t("d_skip"), t("norm_weight"), t("proj_weight")
+    out = torch.nn.functional.linear(mt.gated_rmsnorm(Y, gate, nw, float(g["eps"]), U, ds), pw)
+    assert rel(out.detach().numpy(), g64["out"]) < 1e-12
+    grads = torch.autograd.grad(out, [Y, gate, U, ds, nw, pw], torch.from_numpy(g["cot"]).double())
+    for name, gr in zip(("Y", "gate", "U", "d_skip", "norm_weight", "proj_weight"), grads):
+        assert rel(gr.numpy(), g64["d_" + name]) < 1e-10, name
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 2, 70, 64, 64, True, True), (2, 4, 2, 43, 16, 8, True, True),
+                                   (1, 3, 3, 130, 8, 5, False, False)])
+def test_c_port_of_the_scan_matches_the_numpy_oracle(shape, golden):
+    """oracle/csrc/v2x2ssd_cpu.c is what ``bench.py --impl reference`` and ``cpu_baseline`` time."""
+    from oracle import scan_c
+    b, h, g_, T, P, N, streaming, init = shape
+    case = make_scan_case(b, h, T, P, N, groups=g_, seed=5 * T, streaming=streaming, with_init=init)
+    n = lambda x: None if x is None else x.numpy()
+    args = [n(x) for x in case.tensors()]
+    kw = dict(initial_states=n(case.initial_states), B_prev=n(case.B_prev), U_prev=n(case.U_prev))
+    wY, wfin, _, _ = scan_np.v2x2ssm(*args, **kw)
+    Y, fin = scan_c.forward(*args, **kw)
+    assert rel(Y, wY) < 1e-5 and rel(fin, wfin) < 1e-5
+    dfin = np.random.default_rng(0).standard_normal(wfin.shape).astype(np.float32)
+    want = scan_np.v2x2ssd_bwd(*args, n(case.dY), d_final_state=dfin, **kw)
+    got = scan_c.backward(*args, n(case.dY), d_final_state=dfin, **kw)
+    for name in want:
+        assert rel(got[name], want[name]) < 2e-5, name
+    # the reference's own golden (grouped, streaming, ragged, float64 autograd)
+    gg = golden("scan_grad")
+    kw = dict(initial_states=gg["initial_states"], B_prev=gg["B_prev"], U_prev=gg["U_prev"])
+    ins = [gg[k] for k in "UMKBC"]
+    Y, fin = scan_c.forward(*ins, **kw)
+    assert rel(Y, gg["Y"]) < 1e-5 and rel(fin, gg["final_state"]) < 1e-5
+    got = scan_c.backward(*ins, gg["dY"], d_final_state=gg["d_final_state"], **kw)
+    for name, val in got.items():
+        assert rel(val, gg["d" + name]) < 2e-5, name
