@@ -75,11 +75,20 @@ SL_API int sl_version(void);
  * (monotonic; used by benchmarks to report their launch count). */
 SL_API unsigned long long sl_kernel_launches(void);
 
-/* First error recorded by a kernel of this library on the current device since load
- * (0 = none; a bounded device-side wait that expired reports its site here).  The
- * entry points are asynchronous, so such errors surface here, not in their return
- * value.  Synchronises with the device. */
+/* SL_OK, or SL_ERR_DEVICE_TIMEOUT when a kernel of this library on the current device gave up a
+ * bounded device-side wait since load (or since the last sl_device_status_reset).  Such a kernel
+ * returns early, after draining what it had in flight, and leaves its outputs incomplete; the
+ * entry points are asynchronous, so the condition surfaces here, not in their return value.
+ * Check it where the host synchronises anyway (end of a step, before results are trusted).
+ * Synchronises with the device.  The limit is about a second of SM clocks; the environment
+ * variable SLINOSS_B200_WAIT_CLOCKS, read at every launch, overrides it (diagnostics only).
+ * No reference counterpart (the reference's kernels have no device-side waits). */
 SL_API int sl_device_status(void);
+
+/* Returns the site code of the first expired wait (0 = none; it identifies the wait in the kernel
+ * source) and clears the record, so that one expiry does not mark every later query.
+ * Synchronises with the device. */
+SL_API int sl_device_status_reset(void);
 
 /* Static, human readable text of a status code. */
 SL_API const char* sl_status_string(int status);

@@ -42,6 +42,7 @@ _PROTOTYPES = {
     "sl_version": (c_int, []),
     "sl_kernel_launches": (ctypes.c_ulonglong, []),
     "sl_device_status": (c_int, []),
+    "sl_device_status_reset": (c_int, []),
     "sl_status_string": (ctypes.c_char_p, [c_int]),
     "sl_last_cuda_error": (ctypes.c_char_p, []),
     "sl_workspace_bytes": (c_size_t, [c_int] * 10),
@@ -91,8 +92,14 @@ def kernel_launches() -> int:
 
 
 def device_status() -> int:
-    """First device-side error recorded by the kernels (0 = none); synchronises."""
+    """0, or the status code SL_ERR_DEVICE_TIMEOUT (7) if a kernel gave up a bounded wait since
+    the last reset; synchronises."""
     return int(lib().sl_device_status())
+
+
+def device_status_reset() -> int:
+    """Site code of the first expired wait (0 = none); clears the record; synchronises."""
+    return int(lib().sl_device_status_reset())
 
 
 def check(status: int, what: str) -> None:

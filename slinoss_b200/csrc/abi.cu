@@ -26,8 +26,7 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
                 float* dinit, void* dBprev, void* dUprev, const ScanDims& d, int io_dtype,
                 int dy_dtype, void* ws, size_t ws_bytes, cudaStream_t st);
 
-int scan_tc_device_status();
-void scan_tc_set_warps(int nw);
+int scan_tc_device_status(bool reset);
 
 namespace {
 
@@ -58,11 +57,11 @@ extern "C" unsigned long long sl_kernel_launches(void) {
   return sl::g_launches.load(std::memory_order_relaxed);
 }
 
-// Development knob (not part of the documented ABI): warps per TMEM lane quadrant of the
-// tensor-core scan kernels.
-extern "C" SL_API void sl_tune_tc_warps(int nw) { sl::scan_tc_set_warps(nw); }
+extern "C" int sl_device_status(void) {
+  return sl::scan_tc_device_status(false) != 0 ? SL_ERR_DEVICE_TIMEOUT : SL_OK;
+}
 
-extern "C" int sl_device_status(void) { return sl::scan_tc_device_status(); }
+extern "C" int sl_device_status_reset(void) { return sl::scan_tc_device_status(true); }
 
 extern "C" const char* sl_last_cuda_error(void) {
   return cudaGetErrorString((cudaError_t)sl::g_cuda_error.load(std::memory_order_relaxed));

@@ -20,15 +20,17 @@
 // chunk_scan policy (slinoss/ops/v2x2ssd/reference.py:498-523, 1224-1261); phases are
 // applied to the 16-bit operands, decays to float32 accumulators.
 //
-// One CTA (128 threads) walks the chunks of one (batch, head) in order.  U/B/C tiles
-// arrive by TMA (128B swizzle, one chunk ahead), the state lives in registers (float32,
-// 64 per thread), the MMAs use M = 64 accumulators split into two column halves that
-// sit in the two 16-lane halves of every TMEM lane quadrant, so that thread
-// (warp j, lane i) owns row 16j + (i & 15) and column half (i >> 4) of every result.
+// One CTA of 18 warps walks the chunks of one (batch, head) in order: 16 worker warps (4 TMEM
+// lane quadrants x 4 column groups: rotation passes and every epilogue), one warp that computes
+// the per-chunk scalars one chunk ahead, and one warp whose lane 0 issues every TMA load / store
+// and every tcgen05.mma.  U/B/C tiles arrive by TMA (128B swizzle, one chunk ahead), the state
+// lives in the workers' registers (float32), the MMAs have M = 64 (rows in lanes 0..15 of every
+// TMEM lane quadrant); scan_tc_fwd.cuh and scan_tc_bwd.cuh describe the thread-to-data mappings.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -51,10 +53,6 @@ constexpr uint32_t SMEM_BYTES = OFF_SCAL + 2 * NSCAL * 64 * 4 + 64 + 1024;
 constexpr uint32_t TMEM_COLS = 512;
 
 __device__ int g_tc_status = 0;
-#ifdef SL_TC_TIMING
-__device__ long long g_tc_timing[24];
-__device__ int g_tc_exp;   // timing experiments only
-#endif           // first device-side error (bounded wait expired)
 
 struct alignas(64) TcFwdParams {
   CUtensorMap tmU, tmB, tmC;
@@ -68,6 +66,7 @@ struct alignas(64) TcFwdParams {
   float* zfinal;
   void* states16;       // optional (batch*heads, nchunks, 64, 128) 16-bit: conjugated start state of every chunk
   int heads, groups, T, nchunks;
+  long long wait_limit;  // SM clocks a wait of the main loop may take before the kernel gives up
 };
 
 template <typename T> struct Pack2;
@@ -93,6 +92,17 @@ template <> struct Pack2<__half> {
 };
 
 __device__ __forceinline__ void report_timeout(int code) { atomicCAS(&g_tc_status, 0, code); }
+
+// Limit of the kernels' bounded waits in SM clocks: about a second by default; the environment
+// variable SLINOSS_B200_WAIT_CLOCKS (read at every launch) overrides it, which is how the test of
+// the unwind path makes a wait expire without anything being wrong.
+static long long wait_limit_clocks() {
+  if (const char* e = getenv("SLINOSS_B200_WAIT_CLOCKS")) {
+    const long long v = atoll(e);
+    if (v > 0) return v;
+  }
+  return tc::WAIT_CLOCKS_DEFAULT;
+}
 
 // Per-chunk scalars, computed by warp 0 (two tokens per lane) with shuffle scans.
 //  sc[0] l_t        sc[1] exp(l_t)     sc[2],sc[3] phi_t
@@ -203,21 +213,16 @@ size_t scan_tc_bwd_workspace(const ScanDims& d) {
   return std::max(scan_simt_bwd_workspace(d), tc_bwd_layout(d).total);
 }
 
-int g_tc_nw = 4;   // warps per TMEM lane quadrant (tuning knob: 2 or 4)
+constexpr int NW = 4;   // worker warps per TMEM lane quadrant
 
-template <typename TIn, typename TY, bool STATES_ONLY, int NW>
-static int launch_tc_fwd_nw(const TcFwdParams& p, int grid, cudaStream_t st) {
+template <typename TIn, typename TY, bool STATES_ONLY>
+static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
   auto k = scan_tc_fwd_kernel<TIn, TY, STATES_ONLY, NW>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess)
     return SL_ERR_LAUNCH_FAILED;
   k<<<grid, 128 * NW + 64, SMEM_BYTES, st>>>(p);
   note_launches(1);
   return launch_status();
-}
-template <typename TIn, typename TY, bool STATES_ONLY>
-static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
-  if (g_tc_nw == 2) return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 2>(p, grid, st);
-  return launch_tc_fwd_nw<TIn, TY, STATES_ONLY, 4>(p, grid, st);
 }
 
 // Y == nullptr runs the state pre-sweep only (chunk-start states + final state).
@@ -234,6 +239,7 @@ int scan_tc_fwd_impl(const void* U, const float* M, const float* K, const void* 
   p.M = M; p.K = K; p.z0 = z0; p.Bprev = Bprev; p.Uprev = Uprev; p.Y = Y; p.zfinal = zfinal;
   p.states16 = states16;
   p.heads = d.heads; p.groups = d.groups; p.T = d.T; p.nchunks = (d.T + L - 1) / L;
+  p.wait_limit = wait_limit_clocks();
   if (Y && y_dtype != SL_F32 && !tc::make_tmap_3d(&p.tmY, Y, 64, d.T, BH, 64, y_dtype == SL_BF16))
     return SL_ERR_LAUNCH_FAILED;
   if (states16 && !tc::make_tmap_3d(&p.tmS, states16, 128, (uint64_t)p.nchunks * 64, BH, 64, bf))
@@ -264,7 +270,7 @@ int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, co
   return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, states_out, d, io_dtype, y_dtype, st);
 }
 
-template <typename TIn, int NW>
+template <typename TIn>
 static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
   auto k = scan_tc_bwd_kernel<TIn, NW>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)B_SMEM_BYTES) != cudaSuccess)
@@ -312,34 +318,24 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
   p.dkcd = reinterpret_cast<float2*>(w + lay.dkcd); p.anchor = reinterpret_cast<float2*>(w + lay.anchor);
   p.dinit = dinit; p.T = d.T; p.nchunks = nC;
+  p.wait_limit = wait_limit_clocks();
   int rc = SL_ERR_UNSUPPORTED;
-  if (bf) {
-    rc = g_tc_nw == 2 ? launch_tc_bwd<__nv_bfloat16, 2>(p, (int)BH, st)
-                      : launch_tc_bwd<__nv_bfloat16, 4>(p, (int)BH, st);
-  } else {
-    rc = g_tc_nw == 2 ? launch_tc_bwd<__half, 2>(p, (int)BH, st)
-                      : launch_tc_bwd<__half, 4>(p, (int)BH, st);
-  }
+  rc = bf ? launch_tc_bwd<__nv_bfloat16>(p, (int)BH, st) : launch_tc_bwd<__half>(p, (int)BH, st);
   if (rc != SL_OK) return rc;
   scan_tc_bwd_finish_kernel<<<dim3((unsigned)BH, (unsigned)((nC + 3) / 4)), 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
   note_launches(2);
   return launch_status();
 }
 
-#ifdef SL_TC_TIMING
-extern "C" __attribute__((visibility("default"))) void sl_dbg_set_exp(int v) {
-  cudaMemcpyToSymbol(g_tc_exp, &v, sizeof(int));
-}
-extern "C" __attribute__((visibility("default"))) void sl_dbg_timing(long long* out) {
-  cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(long long) * 24);
-}
-#endif
 
-void scan_tc_set_warps(int nw) { g_tc_nw = nw == 2 ? 2 : 4; }
-
-int scan_tc_device_status() {
+// The site code of the first expired wait on the current device since the last reset (0 = none).
+int scan_tc_device_status(bool reset) {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+  if (reset && v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  }
   return v;
 }
 

@@ -45,6 +45,7 @@ struct alignas(64) TcBwdParams {
   float2 *dg, *sterm, *dkcd, *anchor;   // per token / per chunk scalars (workspace)
   float* dinit;          // (BH, 64, 128) adjoint of the carried start state, or null
   int T, nchunks;
+  long long wait_limit;  // SM clocks a wait of the main loop may take before the kernel gives up
 };
 
 // Per-token table: rows 0..10 as written by chunk_scalars, then
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t bar_tma[2], bar_mma[5];   // bar_mma: P~,dS | dX | dQ | dU | dZ (all earlier MMAs)
-  __shared__ uint64_t bar_st[3];               // output tiles staged in shared memory: dB | dC | dU
+  __shared__ uint64_t bar_st[3], bar_drain;    // output tiles staged in shared memory: dB | dC | dU
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ float s_red[8 * NW + 2];
@@ -84,11 +85,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   const float* Mb = p.M + (size_t)bh * T * 2;
   const float* Kb = p.K + (size_t)bh * T * 4;
   const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
+  const long long wl = p.wait_limit;   // limit of the main loop's waits (the drain waits keep the default)
 
   if (tid == 0) {
     mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
     for (int i = 0; i < 5; ++i) mbar_init(&bar_mma[i], 1);
     for (int i = 0; i < 3; ++i) mbar_init(&bar_st[i], 4 * NW);   // one arrival per worker warp
+    mbar_init(&bar_drain, 1);
     fence_barrier_init();
     s_abort = 0;
     tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
@@ -172,13 +175,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
                  aDP = smem_u32(smem + B_OFF_DP), aDW = smem_u32(smem + B_OFF_DW),
                  aUE = smem_u32(smem + B_OFF_UE);
   bool ok = true;
-#ifdef SL_TC_TIMING
-#define SL_TOCK(i) if (bh == 0 && tid == 0 && it == 8) g_tc_timing[i] = clock64();
-#define SL_TOCK_MMA(i) if (bh == 0 && it == 8) g_tc_timing[i] = clock64();
-#else
-#define SL_TOCK(i)
-#define SL_TOCK_MMA(i)
-#endif
+  int issued_it = 0;   // issue lane: the last iteration whose loads were requested (iteration 0 by thread 0 above)
 
   // ---- epilogue 5 of the chunk of iteration itp (run one iteration late): dz <- e^{l_end} dWv + dZ,
   // and the anchor S = <dz, z> of the boundary below that chunk ------------------------------------------
@@ -190,7 +187,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     const int cp = nC - 1 - itp;
     // (this thread's cells of that chunk's Zv tiles were copied to zv_keep at the end of its iteration, so
     // that the whole stage can be refilled at the top of the next one)
-    if (live && !mbar_wait(&bar_mma[4], itp & 1)) { report_timeout(16); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[4], itp & 1, wl)) { report_timeout(16); s_abort = 1; live = false; }
     tc_fence_after_sync();
     const float em = em_keep;
     float ar = 0.f, ai = 0.f;
@@ -252,7 +249,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
 
   for (int it = 0; it < nC && ok; ++it) {
     const int c = nC - 1 - it, t0 = c * L;
-    SL_TOCK(0)
     uint8_t* st = smem + (it & 1) * B_STAGE;
     uint8_t *tU = st, *tB = st + TILE, *tC = st + 3 * TILE, *tDY = st + 5 * TILE, *tZ = st + 6 * TILE;
     float* sc = sc_tab + (it & 1) * (11 * 64);
@@ -287,7 +283,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       bool go = lane == 0 && s_abort == 0;
       if (go) do {
         // (1) products of raw tiles, as soon as the stage has landed
-        if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(20); s_abort = 1; go = false; break; }
+        if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1, wl)) { report_timeout(20); s_abort = 1; go = false; break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 4; ++k)
@@ -297,6 +293,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           tma_store_wait_read();   // the stores of the previous chunk read the stage being refilled
           issue_loads_inputs(c - 1, it + 1);
           issue_loads_states(c - 1, it + 1);
+          issued_it = it + 1;
         }
       } while (false);
       __syncwarp();
@@ -320,7 +317,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           umma(tmem + 0, desc_adv(kQ, ko), desc_adv(kKP, ko), ID_KK64, 1);
         }
         umma_commit(&bar_mma[0]);   // P~ and dS: epilogue 1 may start
-        SL_TOCK_MMA(6)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           // dQ[t][d] = sum_p dYoff[t][p] Zv[p][d] (+ dP K' below)   A: dYoff K-major, B: Zv MN-major (rows = p)
@@ -332,7 +328,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       bar_sync(6, NT + 32);
       if (go && s_abort == 0) {
         tc_fence_after_sync();
-        SL_TOCK_MMA(18)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           // dX[s][d] = sum_p (e^{l_end-l_s} U[s][p]) dWv[p][d] (+ dP^T Q below)   A: Uee K-major, B: dWv MN-major
@@ -370,30 +365,26 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
           // dZ[p][d]  = sum_t dYoff[t][p] Q[t][d]      A: dYoff MN-major, B: Q MN-major
           umma(tmem + 384, desc_adv(mDYO, 2048 * k), desc_adv(mQ, 2048 * k), ID_MM128, k > 0);
         umma_commit(&bar_mma[4]);   // dZ
-        SL_TOCK_MMA(9)
         // (4) output tiles: the workers overwrite dead operand tiles of this stage in place (C with dB,
         // B with dC, dY with dU) and signal; one TMA store per tile writes full 128-byte rows.
-        if (!mbar_wait(&bar_st[0], it & 1)) { report_timeout(17); s_abort = 1; break; }
+        if (!mbar_wait(&bar_st[0], it & 1, wl)) { report_timeout(17); s_abort = 1; break; }
         tma_store_3d(&p.tmdB, tC, 0, t0, bh); tma_store_3d(&p.tmdB, tC + TILE, 64, t0, bh);
         tma_store_commit();
-        if (!mbar_wait(&bar_st[1], it & 1)) { report_timeout(18); s_abort = 1; break; }
+        if (!mbar_wait(&bar_st[1], it & 1, wl)) { report_timeout(18); s_abort = 1; break; }
         tma_store_3d(&p.tmdC, tB, 0, t0, bh); tma_store_3d(&p.tmdC, tB + TILE, 64, t0, bh);
         tma_store_commit();
-        if (!mbar_wait(&bar_st[2], it & 1)) { report_timeout(19); s_abort = 1; break; }
+        if (!mbar_wait(&bar_st[2], it & 1, wl)) { report_timeout(19); s_abort = 1; break; }
         tma_store_3d(&p.tmdU, tDY, 0, t0, bh);
         tma_store_commit();
         // The next iteration's passes overwrite the dYoff and Q tiles that the dZ products (issued after
         // everything the workers wait for in this iteration) read: this lane sees them complete before it
         // joins the barrier that ends the iteration.
-        if (!mbar_wait(&bar_mma[4], it & 1)) { report_timeout(21); s_abort = 1; break; }
+        if (!mbar_wait(&bar_mma[4], it & 1, wl)) { report_timeout(21); s_abort = 1; break; }
       } while (false);
       __syncwarp();
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
-    SL_TOCK(16)
-    if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1)) { report_timeout(11); s_abort = 1; live = false; }
-    SL_TOCK(1)
-    SL_TOCK(2)
+    if (!mbar_wait(&bar_tma[it & 1], (it >> 1) & 1, wl)) { report_timeout(11); s_abort = 1; live = false; }
 
     // ---- pass 1 over dY, U: sigma_t = <dy_t, u_t>, dYoff = e^{l_t} dY -------------------------------
     if (live) {
@@ -423,7 +414,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       if (ch == 0) sw[1 * 64 + r] = sg;
     }
     }
-    SL_TOCK(3)
     // ---- pass 2 over B, C: Q, K', diagonal pieces ------------------------------------------------------
     // Two phases, one per 64-column half of the state dimension: P~ accumulates over that dimension, so
     // the issue warp starts its first four k-steps (named barrier 5) while the workers rotate the second
@@ -486,7 +476,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       }
     }
-    SL_TOCK(4)
     fence_async_smem();
     tc_fence_before_sync();
     // no barrier among the workers here or at the end of the gap below: what a warp does next (epilogue 5
@@ -494,18 +483,15 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     // write; the workers meet at the end of epilogue 1
     bar_arrive(2, NT + 64);      // the scalar and issue warps are told without being waited for
     live = s_abort == 0;
-    SL_TOCK(5)
     // ---- in the shadow of the P~ MMAs: epilogue 5 of the previous iteration, then this chunk's dWv ------
     if (it > 0) epilogue5(it - 1, live);
     live = live && s_abort == 0;
     if (live) make_dwv(sc);
-    SL_TOCK(21)
     em_keep = sc[1 * 64 + 63];
     fence_async_smem();
     tc_fence_before_sync();
     bar_arrive(6, NT + 32);      // dWv written, the previous dZ accumulator and Zv tiles released
     bar_arrive(7, NT + 32);      // anchor partial sums written: the scalar warp adds them up and stores
-    SL_TOCK(22)
 
     // ---- MMA group 1 (issued by the look-ahead warp): P~ = Q K'^T, dS = dY U^T ------------------------
     // The waits and TMEM loads below are compiler barriers, so everything an epilogue reads from shared
@@ -533,9 +519,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       }
     }
-    if (live && !mbar_wait(&bar_mma[0], it & 1)) { report_timeout(12); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[0], it & 1, wl)) { report_timeout(12); s_abort = 1; live = false; }
     tc_fence_after_sync();
-    SL_TOCK(7)
 
     // ---- epilogue 1: decayed, strictly causal Pdec and dP as 16-bit tiles -------------------------------
     if (live) {
@@ -543,7 +528,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       tmem_ld_16x256<WB>(tmem + lane_base + 0 + cg * WC, pr);
       tmem_ld_16x256<WB>(tmem + lane_base + 64 + cg * WC, ds);
       tmem_ld_wait();
-      SL_TOCK(19)
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const int R = hh ? rowB : rowA;
@@ -558,14 +542,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
         }
       }
     }
-    SL_TOCK(20)
     fence_async_smem();
-    SL_TOCK(17)
     tc_fence_before_sync();
     bar_sync(3, NT);
     bar_arrive(4, NT + 32);
     live = s_abort == 0;
-    SL_TOCK(8)
 
     // ---- MMA group 2 (issued by the look-ahead warp, one commit per accumulator set) ------------------
     // operands of epilogues 3 and 2 (this thread's cells of the C, B and Q tiles and its row's scalars),
@@ -582,9 +563,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     const float wr = sc[4 * 64 + row], wi = sc[5 * 64 + row];
     const float phr = sc[2 * 64 + row], phi = sc[3 * 64 + row];
     const float skr = sig * sc[8 * 64 + row], ski = sig * sc[9 * 64 + row];   // sigma kc
-    if (live && !mbar_wait(&bar_mma[1], it & 1)) { report_timeout(13); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[1], it & 1, wl)) { report_timeout(13); s_abort = 1; live = false; }
     tc_fence_after_sync();
-    SL_TOCK(10)
 
     // ---- epilogue 3 (first): dX -> dB, R = sum conj(b) dX ---------------------------------------------------------
     if (live) {
@@ -621,8 +601,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     fence_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(&bar_st[0]);
-    SL_TOCK(11)
-    if (live && !mbar_wait(&bar_mma[2], it & 1)) { report_timeout(14); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[2], it & 1, wl)) { report_timeout(14); s_abort = 1; live = false; }
     tc_fence_after_sync();
     // ---- epilogue 2: dQ -> dC, <q,dq> ------------------------------------------------------------------
     if (live) {
@@ -658,7 +637,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     fence_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(&bar_st[1]);
-    SL_TOCK(12)
     // operands of epilogue 4: this thread's cells of the dY tile and its rows' scalars
     uint32_t dyc[2 * WB];
     float e4s[4];
@@ -670,7 +648,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       for (int i = 0; i < WB; ++i)
         dyc[hh * WB + i] = *reinterpret_cast<const uint32_t*>(tDY + sw128(R, cg * WB + i) + 4 * cq);
     }
-    if (live && !mbar_wait(&bar_mma[3], it & 1)) { report_timeout(15); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[3], it & 1, wl)) { report_timeout(15); s_abort = 1; live = false; }
     tc_fence_after_sync();
     // ---- epilogue 4: dU ---------------------------------------------------------------------------------------
     if (live) {
@@ -695,7 +673,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     fence_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(&bar_st[2]);
-    SL_TOCK(13)
     // (epilogue 5 of this chunk - the update of dz - runs in the next iteration, in the shadow of the
     // P~ MMAs; its inputs, the dZ accumulator and the Zv tiles of this stage, stay untouched until then)
 #pragma unroll
@@ -705,7 +682,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     // the proxy fence for this iteration's shared-memory accesses goes BEFORE the global stores
     // below (the code after them touches no tile)
     fence_async_smem();
-    SL_TOCK(14)
     // ---- per-token scalars of this chunk ---------------------------------------------------------------------
     if (live && tid < 64 && t0 + tid < T) {
       const int t = tid;
@@ -725,7 +701,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     tc_fence_before_sync();
     }  // worker
     __syncthreads();
-    SL_TOCK(15)
     if (s_abort) { ok = false; break; }
   }
 
@@ -738,10 +713,17 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
       *reinterpret_cast<float4*>(dst + 4 * j) =
           make_float4(dz[4 * j], -dz[4 * j + 1], dz[4 * j + 2], -dz[4 * j + 3]);
   }
-  if (!ok && tid == 0) {
-    for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);
+  // Unwind: nothing of this CTA may still be in flight when shared memory and TMEM are released.  The
+  // issue lane started every asynchronous operation (but for the loads of the first iteration), so it
+  // drains them: after an expired wait the loads of the last two requested iterations (their barriers,
+  // default long limit) and, always, every tcgen05.mma issued so far (one more commit) and its TMA stores.
+  if (warp == 4 * NW + 1 && lane == 0) {
+    if (s_abort)
+      for (int ii = issued_it > 0 ? issued_it - 1 : 0; ii <= issued_it; ++ii) mbar_wait(&bar_tma[ii & 1], (ii >> 1) & 1);
+    umma_commit(&bar_drain);
+    mbar_wait(&bar_drain, 0);
+    tma_store_wait_all();
   }
-  if (warp == 4 * NW + 1 && lane == 0) tma_store_wait_all();   // output stores of the issue thread
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, B_TMEM_COLS);

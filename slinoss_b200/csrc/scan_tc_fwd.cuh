@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   constexpr int RSTEP = NT / 16;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ uint64_t bar_tma[2], bar_mma[3];   // bar_mma: [S|Yoff] | Inc | Ydiag
+  __shared__ uint64_t bar_tma[2], bar_mma[3], bar_drain;   // bar_mma: [S|Yoff] | Inc | Ydiag
   __shared__ uint64_t bar_st;                  // Y tile staged in shared memory (16-bit outputs)
   constexpr bool Y_TMA = !STATES_ONLY && sizeof(TY) == 2;
   __shared__ uint32_t tmem_slot;
@@ -41,11 +41,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   const int T = p.T;
   const float* Mb = p.M + (size_t)bh * T * 2;
   const float* Kb = p.K + (size_t)bh * T * 4;
+  const long long wl = p.wait_limit;   // limit of the main loop's waits (the drain waits keep the default)
 
   if (tid == 0) {
     mbar_init(&bar_tma[0], 1); mbar_init(&bar_tma[1], 1);
     for (int i = 0; i < 3; ++i) mbar_init(&bar_mma[i], 1);
     mbar_init(&bar_st, 4 * NW);   // one arrival per worker warp
+    mbar_init(&bar_drain, 1);
     fence_barrier_init();
     s_abort = 0;
     tma_prefetch_desc(&p.tmU); tma_prefetch_desc(&p.tmB); tma_prefetch_desc(&p.tmC);
@@ -128,19 +130,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   constexpr uint32_t ID_Z = make_idesc(64, 128, PK::fmt, 1, 1);    // MN-major x MN-major Inc
   const uint32_t aKPP = smem_u32(smem + OFF_KPP), aS = smem_u32(smem + OFF_S);
   bool ok = true;
-#ifdef SL_TC_TIMING
-#define SL_TICK(i) if (bh == 0 && tid == 0 && c == 8) g_tc_timing[i] = clock64();
-#define SL_TICK_MMA(i) if (bh == 0 && c == 8) g_tc_timing[i] = clock64();
-#else
-#define SL_TICK(i)
-#define SL_TICK_MMA(i)
-#endif
+  int issued_hi = 0;   // issue lane: the last chunk whose loads were requested (chunk 0 by thread 0 above)
 
   // ---- output epilogue of chunk cp: y = Y_diag + exp(l_t) Y_off.  It runs one iteration late, in the gap
   // while the [S | Yoff] MMAs of the next chunk execute (their accumulators alternate by chunk parity).
   float et_keep[2] = {0.f, 0.f};   // exp(l_t) of this thread's two rows in the chunk whose output is pending
   auto output_epilogue = [&](int cp, bool live) {
-    if (live && !mbar_wait(&bar_mma[2], cp & 1)) { report_timeout(4); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[2], cp & 1, wl)) { report_timeout(4); s_abort = 1; live = false; }
     tc_fence_after_sync();
     if (live) {
       const int t0p = cp * L;
@@ -173,7 +169,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   };
 
   for (int c = 0; c < p.nchunks && ok; ++c) {
-    SL_TICK(0)
     const int t0 = c * L;
     uint8_t* st = smem + (c & 1) * STAGE;
     float* sc = sc_tab + (c & 1) * (NSCAL * 64);
@@ -197,8 +192,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       if (lane == 0 && s_abort == 0 && c + 1 < p.nchunks) {
         // Next chunk's tiles, a whole iteration ahead (half an iteration was not always enough for the data
         // to arrive).  The stage being refilled held chunk c-1, whose last reader is its Y_diag MMA.
-        if (!STATES_ONLY && c > 0 && !mbar_wait(&bar_mma[2], (c - 1) & 1)) { report_timeout(8); s_abort = 1; }
-        else issue_loads(c + 1);
+        if (!STATES_ONLY && c > 0 && !mbar_wait(&bar_mma[2], (c - 1) & 1, wl)) { report_timeout(8); s_abort = 1; }
+        else { issue_loads(c + 1); issued_hi = c + 1; }
       }
       __syncwarp();
       bar_sync(5, NT + 32);   // first column halves of Q and K' rotated (the Zv tile is the previous chunk's)
@@ -225,14 +220,13 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         for (int k = 0; k < 4; ++k)
           umma(tINC, desc_adv(bU, 2048 * k), desc_adv(bK, 2048 * k), ID_Z, k > 0);
         umma_commit(&bar_mma[1]);
-        SL_TICK_MMA(3)
         if (p.states16) {   // the 16-bit state tile of this chunk is exactly what the backward wants
           tma_store_3d(&p.tmS, st + 2 * TILE, 0, c * 64, bh);
           tma_store_3d(&p.tmS, st + 4 * TILE, 64, c * 64, bh);
           tma_store_commit();
         }
         if (Y_TMA && c > 0) {   // the workers stage the Y tile of the PREVIOUS chunk while the MMAs above run
-          if (mbar_wait(&bar_st, (c - 1) & 1)) {
+          if (mbar_wait(&bar_st, (c - 1) & 1, wl)) {
             tma_store_3d(&p.tmY, smem + OFF_Y, 0, t0 - L, bh);
             tma_store_commit();
           } else { report_timeout(5); s_abort = 1; }
@@ -248,7 +242,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
           for (int k = 0; k < 4; ++k)   // Y_diag = S U
             umma(tYD, desc_adv(bS, 32 * k), desc_adv(bU, 2048 * k), ID_Y, k > 0);
           umma_commit(&bar_mma[2]);
-          SL_TICK_MMA(6)
         }
         // the state tiles and the Y tile stored in this iteration are overwritten by the workers in
         // the next one: their stores must have read them by then (they were issued long ago)
@@ -257,8 +250,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       __syncwarp();
     } else {
     bool live = true;   // cleared when a bounded wait expired: the rest of the chunk is skipped
-    if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1)) { report_timeout(1); s_abort = 1; live = false; }
-    SL_TICK(1)
+    if (!mbar_wait(&bar_tma[c & 1], (c >> 1) & 1, wl)) { report_timeout(1); s_abort = 1; live = false; }
 
     // ---- rotation: C -> Q, B -> K' (both in place), K'' ; diagonal scores --------------------
     // Two phases, one per 64-column half of the state dimension: the score products accumulate over
@@ -339,7 +331,6 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
     // other warps are read after the score products' barrier, which all rotations precede
     bar_arrive(2, NT + 64);      // the scalar and issue warps are told without being waited for
     live = s_abort == 0;
-    SL_TICK(2)
 
     if (!STATES_ONLY) {
       // ---- [S | Yoff] and Inc MMAs are issued by the issue warp; meanwhile the output of the previous
@@ -366,9 +357,8 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         }
       }
       const float et_next[2] = {sc[1 * 64 + rowA], sc[1 * 64 + rowB]};
-      if (live && !mbar_wait(&bar_mma[0], c & 1)) { report_timeout(2); s_abort = 1; live = false; }
+      if (live && !mbar_wait(&bar_mma[0], c & 1, wl)) { report_timeout(2); s_abort = 1; live = false; }
       tc_fence_after_sync();
-      SL_TICK(4)
 
       // ---- scores epilogue: decay, causal mask, diagonal -> 16-bit S tile ------------------------
       if (live) {
@@ -400,13 +390,11 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       tc_fence_before_sync();
       bar_arrive(4, NT + 32);   // the issue warp now issues Y_diag = S U (no barrier among the workers)
       live = s_abort == 0;
-      SL_TICK(5)
     }
 
     // ---- state update (hides the Y_diag MMAs; the output epilogue follows in the next iteration) ---------
-    if (live && !mbar_wait(&bar_mma[1], c & 1)) { report_timeout(3); s_abort = 1; live = false; }
+    if (live && !mbar_wait(&bar_mma[1], c & 1, wl)) { report_timeout(3); s_abort = 1; live = false; }
     tc_fence_after_sync();
-    SL_TICK(7)
     // ---- state update: zv = conj(Pi_end) zv + Inc ---------------------------------------------------
     if (live) {
       const float pr = sc[10 * 64 + 0], pi = sc[10 * 64 + 1];
@@ -424,21 +412,18 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       }
       store_zv_tile(c + 1);
     }
-    SL_TICK(8)
-    SL_TICK(9)
     fence_async_smem();
     tc_fence_before_sync();
     }  // worker
     __syncthreads();
     if (s_abort) { ok = false; break; }
-    SL_TICK(10)
   }
 
   if (!STATES_ONLY && ok) {
     if (worker) {
       output_epilogue(p.nchunks - 1, true);
     } else if (Y_TMA && warp == 4 * NW + 1 && lane == 0) {
-      if (mbar_wait(&bar_st, (p.nchunks - 1) & 1)) {
+      if (mbar_wait(&bar_st, (p.nchunks - 1) & 1, wl)) {
         tma_store_3d(&p.tmY, smem + OFF_Y, 0, (p.nchunks - 1) * L, bh);
         tma_store_commit();
       } else { report_timeout(5); s_abort = 1; }
@@ -452,11 +437,17 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
       *reinterpret_cast<float2*>(p.zfinal + ((size_t)bh * 64 + rowB) * 128 + d) = make_float2(zv[4 * i + 2], -zv[4 * i + 3]);
     }
   }
-  // unwind: nothing of ours may still be in flight when shared memory / TMEM are released
-  if (!ok && tid == 0) {
-    for (int s = 0; s < 2; ++s) mbar_wait(&bar_tma[s], 0);   // bounded; best effort drain
+  // Unwind: nothing of this CTA may still be in flight when shared memory and TMEM are released.  Every
+  // asynchronous operation was started by the issue lane (but for the loads of chunk 0), so it drains them:
+  // after an expired wait the loads of the last two requested chunks (their barriers, default long limit),
+  // every tcgen05.mma issued so far (one more commit) and, always, its TMA stores.
+  if (warp == 4 * NW + 1 && lane == 0) {
+    if (s_abort)
+      for (int cc = issued_hi > 0 ? issued_hi - 1 : 0; cc <= issued_hi; ++cc) mbar_wait(&bar_tma[cc & 1], (cc >> 1) & 1);
+    umma_commit(&bar_drain);
+    mbar_wait(&bar_drain, 0);
+    tma_store_wait_all();
   }
-  if (warp == 4 * NW + 1 && lane == 0) tma_store_wait_all();   // Y / state stores of the issue thread
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);

@@ -52,13 +52,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false when the barrier did not flip within ~2e9 SM clocks
-// (about a second); the caller then records an error and unwinds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: returns false when the barrier did not flip within `limit` SM clocks (default: about a
+// second); the caller then records an error and unwinds.  The kernels pass their launch parameter for
+// the waits of their main loops and keep the default for the waits that drain work in flight.
+constexpr long long WAIT_CLOCKS_DEFAULT = 2000000000LL;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = WAIT_CLOCKS_DEFAULT) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > 2000000000LL) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }

@@ -14,69 +14,71 @@ def _contig(name: str, x: torch.Tensor) -> None:
         raise ValueError(f"{name} must be contiguous; got strides {x.stride()}.")
 
 
+def _require(cond: bool, message: str) -> None:
+    if not cond:
+        raise ValueError(message)
+
+
 def validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev):
-    """Shape / device / layout contract of the scan; same conditions and messages as
-    the reference's ``_validate_inputs`` (slinoss/ops/v2x2ssd/reference.py:152-234).
+    """Shape / device / layout contract of the scan.  The conditions and the messages are the
+    reference's (``_validate_inputs``, slinoss/ops/v2x2ssd/reference.py:152-234), since callers
+    match on them; the checks are grouped here as: the five operands as a set, the per-operand
+    rank table, cross-operand extents, then the optional carried tensors.
     Returns ``(batch, heads, T, N, P)``."""
-    tensors = (U, M, K, B, C)
-    if not all(torch.is_floating_point(t) for t in tensors):
-        raise ValueError("U, M, K, B, and C must be floating-point tensors.")
-    if not all(t.device == U.device for t in tensors):
-        raise ValueError(
-            f"All inputs must be on the same device. Got {[t.device for t in tensors]}.")
-    for name, t in zip("UMKBC", tensors):
+    operands = {"U": U, "M": M, "K": K, "B": B, "C": C}
+    values = tuple(operands.values())
+    _require(all(torch.is_floating_point(t) for t in values),
+             "U, M, K, B, and C must be floating-point tensors.")
+    _require(all(t.device == U.device for t in values),
+             f"All inputs must be on the same device. Got {[t.device for t in values]}.")
+    for name, t in operands.items():
         _contig(name, t)
-    if U.ndim != 4:
-        raise ValueError(f"U must be (batch,heads,T,P). Got {tuple(U.shape)}.")
-    if M.ndim != 4 or M.shape[-1] != 2:
-        raise ValueError(f"M must be (batch,heads,T,2). Got {tuple(M.shape)}.")
-    if K.ndim != 5 or K.shape[-2:] != (2, 2):
-        raise ValueError(f"K must be (batch,heads,T,2,2). Got {tuple(K.shape)}.")
-    if B.ndim != 4:
-        raise ValueError(f"B must be (batch,groups,T,2N). Got {tuple(B.shape)}.")
-    if C.ndim != 4:
-        raise ValueError(f"C must be (batch,groups,T,2N). Got {tuple(C.shape)}.")
+
+    # rank (and fixed trailing extents) of every operand
+    layout = {"U": (4, (), "(batch,heads,T,P)"), "M": (4, (2,), "(batch,heads,T,2)"),
+              "K": (5, (2, 2), "(batch,heads,T,2,2)"), "B": (4, (), "(batch,groups,T,2N)"),
+              "C": (4, (), "(batch,groups,T,2N)")}
+    for name, (rank, tail, text) in layout.items():
+        t = operands[name]
+        ok = t.ndim == rank and (not tail or tuple(t.shape[-len(tail):]) == tail)
+        _require(ok, f"{name} must be {text}. Got {tuple(t.shape)}.")
+
     batch, heads, T, P = map(int, U.shape)
-    if M.shape[:3] != (batch, heads, T):
-        raise ValueError("Leading (batch,heads,T) dims of M must match U.")
-    if K.shape[:3] != (batch, heads, T):
-        raise ValueError("Leading (batch,heads,T) dims of K must match U.")
-    if B.shape[0] != batch or B.shape[2] != T:
-        raise ValueError("B must match U on batch/time dims.")
-    if C.shape[0] != batch or C.shape[2] != T:
-        raise ValueError("C must match U on batch/time dims.")
-    D = int(B.shape[-1])
-    if D % 2 != 0:
-        raise ValueError(f"B/C 2N dim must be divisible by 2. Got {D}.")
-    groups = int(B.shape[1])
-    if groups <= 0:
-        raise ValueError("B/C must have a positive group dimension.")
-    if heads % groups != 0:
-        raise ValueError(
-            f"B/C group dimension must divide heads. Got heads={heads}, groups={groups}.")
-    if tuple(C.shape) != (batch, groups, T, D):
-        raise ValueError("C must match grouped B exactly.")
-    if (B_prev is None) ^ (U_prev is None):
-        raise ValueError("B_prev and U_prev must be passed together (or both omitted).")
+    for name in ("M", "K"):
+        _require(tuple(operands[name].shape[:3]) == (batch, heads, T),
+                 f"Leading (batch,heads,T) dims of {name} must match U.")
+    for name in ("B", "C"):
+        t = operands[name]
+        _require(t.shape[0] == batch and t.shape[2] == T, f"{name} must match U on batch/time dims.")
+    D, groups = int(B.shape[-1]), int(B.shape[1])
+    _require(D % 2 == 0, f"B/C 2N dim must be divisible by 2. Got {D}.")
+    _require(groups > 0, "B/C must have a positive group dimension.")
+    _require(heads % groups == 0,
+             f"B/C group dimension must divide heads. Got heads={heads}, groups={groups}.")
+    _require(tuple(C.shape) == (batch, groups, T, D), "C must match grouped B exactly.")
+
+    # carried tensors
+    _require((B_prev is None) == (U_prev is None),
+             "B_prev and U_prev must be passed together (or both omitted).")
+    carried = []
     if initial_states is not None:
-        if initial_states.shape != (batch, heads, P, D):
-            raise ValueError(
-                "initial_states must be (batch,heads,P,2N) "
-                f"={(batch, heads, P, D)}. Got {tuple(initial_states.shape)}.")
-        _contig("initial_states", initial_states)
-        if initial_states.device != U.device:
-            raise ValueError("initial_states must be on the same device as inputs.")
+        carried.append(("initial_states", initial_states, (batch, heads, P, D),
+                        "initial_states must be (batch,heads,P,2N) "
+                        f"={(batch, heads, P, D)}. Got {tuple(initial_states.shape)}.",
+                        "initial_states must be on the same device as inputs."))
     if B_prev is not None:
-        if B_prev.shape != (batch, groups, D):
-            raise ValueError(
-                f"B_prev must be (batch,groups,2N)={(batch, groups, D)}. Got {tuple(B_prev.shape)}.")
-        if U_prev.shape != (batch, heads, P):
-            raise ValueError(
-                f"U_prev must be (batch,heads,P)={(batch, heads, P)}. Got {tuple(U_prev.shape)}.")
-        _contig("B_prev", B_prev)
-        _contig("U_prev", U_prev)
-        if B_prev.device != U.device or U_prev.device != U.device:
-            raise ValueError("B_prev and U_prev must be on the same device as inputs.")
+        both = "B_prev and U_prev must be on the same device as inputs."
+        carried.append(("B_prev", B_prev, (batch, groups, D),
+                        f"B_prev must be (batch,groups,2N)={(batch, groups, D)}. "
+                        f"Got {tuple(B_prev.shape)}.", both))
+        carried.append(("U_prev", U_prev, (batch, heads, P),
+                        f"U_prev must be (batch,heads,P)={(batch, heads, P)}. "
+                        f"Got {tuple(U_prev.shape)}.", both))
+    for name, t, shape, shape_msg, _ in carried:
+        _require(tuple(t.shape) == shape, shape_msg)
+    for name, t, _, _, device_msg in carried:
+        _contig(name, t)
+        _require(t.device == U.device, device_msg)
     return batch, heads, T, D // 2, P
 
 

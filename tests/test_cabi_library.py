@@ -22,9 +22,17 @@ def lib():
 def test_header_symbols_are_exported(lib):
     header = (ROOT / "include" / "slinoss_b200.h").read_text()
     declared = re.findall(r"SL_API\s+[\w\s\*]+?\b(sl_\w+)\s*\(", header)
-    assert len(declared) == 15 and set(declared) == set(_C.EXPORTED_SYMBOLS)
+    assert len(declared) == len(set(declared)) == 16 and set(declared) == set(_C.EXPORTED_SYMBOLS)
     for name in declared:
         assert getattr(lib, name) is not None
+    # ... and nothing else: every dynamic `sl_*` symbol of the library is declared in the header
+    import shutil
+    import subprocess
+    if shutil.which("nm"):
+        out = subprocess.run(["nm", "-D", "--defined-only", str(_C.lib_path())], capture_output=True,
+                             text=True, check=True).stdout
+        exported = {ln.split()[-1] for ln in out.splitlines() if ln.split() and ln.split()[-1].startswith("sl_")}
+        assert exported == set(declared), exported ^ set(declared)
 
 
 def test_version_and_status_strings(lib):

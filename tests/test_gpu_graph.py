@@ -114,30 +114,3 @@ def test_decode_steps_replay_from_a_graph_and_update_the_state_in_place():
     assert torch.equal(ys, want)
     assert torch.equal(state, eager_state)
     assert not torch.equal(state, state0)
-
-
-def test_two_warps_per_quadrant_variant_matches_the_default():
-    """``sl_tune_tc_warps(2)`` selects the kernels with 8 worker warps (twice the columns per
-    thread, wider TMEM loads); they must give the default variant's results."""
-    case = make_scan_case(2, 3, 300, 64, 64, dtype=torch.bfloat16, seed=21, with_init=True).to(DEV)
-
-    def step():
-        Y, fin, st = _C.scan_fwd(case.U, case.M, case.K, case.B, case.C, case.initial_states, None, None,
-                                 chunk_size=64, y_dtype=torch.bfloat16, want_final=True, path="tc",
-                                 save_states=True)
-        grads = _C.scan_bwd(case.U, case.M, case.K, case.B, case.C, case.initial_states, None, None,
-                            case.dY, None, chunk_size=64, path="tc", saved=(st, fin))
-        torch.cuda.synchronize()
-        return (Y, fin) + tuple(g for g in grads if g is not None)
-
-    want = step()
-    try:
-        _C.lib().sl_tune_tc_warps(2)
-        got = step()
-    finally:
-        _C.lib().sl_tune_tc_warps(4)
-    assert _C.device_status() == 0
-    for i, (g, w) in enumerate(zip(got, want)):
-        assert torch.isfinite(g.float()).all(), i
-        # same arithmetic per element; only the summation order of a few per-token scalars differs
-        assert rel(g, w) <= 2e-3, (i, rel(g, w))

@@ -175,17 +175,19 @@ def test_tail_forward_backward(dims, dtype):
     Y, U, gate = mk(bsz, H, T, P), mk(bsz, H, T, P), mk(bsz, T, H * P)
     ds, nw = torch.randn(H, generator=gen), (1 + 0.2 * torch.randn(H * P, generator=gen)).to(dtype)
     cot = mk(bsz, T, H * P)
-    lv = lambda v: v.clone().requires_grad_(True)
+    # float32 inputs: the oracle runs in float64 (its own float32 evaluation is exact to ~1e-4 only)
+    odt = torch.float64 if dtype == torch.float32 else dtype
+    lv = lambda v: v.to(odt if v.dtype == dtype or v.dtype == torch.float32 else v.dtype).clone().requires_grad_(True)
     oY, oU, og, ods, onw = lv(Y), lv(U), lv(gate), lv(ds), lv(nw)
     want = mt.gated_rmsnorm(oY, og, onw, 1e-5, oU, ods)
-    wg = torch.autograd.grad(want, [oY, og, oU, ods, onw], cot)
+    wg = torch.autograd.grad(want, [oY, og, oU, ods, onw], cot.to(want.dtype))
     gl = lambda v: v.to(DEV).requires_grad_(True)
     gY, gU, gg, gds, gnw = gl(Y), gl(U), gl(gate), gl(ds), gl(nw)
     got = mixer_gated_norm(gY, gg, gnw, 1e-5, skip_input=gU, d_skip=gds)
     assert rel(got, want) <= tol(dtype)
     ggr = torch.autograd.grad(got, [gY, gg, gU, gds, gnw], cot.to(DEV))
     for name, a, w_ in zip(("Y", "gate", "U", "d_skip", "norm_weight"), ggr, wg):
-        assert rel(a, w_) <= (tol(dtype) if dtype == torch.bfloat16 else 1e-4), (name, rel(a, w_))
+        assert rel(a, w_) <= tol(dtype), (name, rel(a, w_))
 
 
 def test_tail_against_the_reference_evaluated_in_float64(golden):
