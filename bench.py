@@ -16,14 +16,19 @@ JSON line:
                         batch entry x half the heads on a copy-in stream, two op streams and a
                         copy-out stream, so that both copy directions and the kernels overlap)
   roofline              the dominant kernel (the backward sweep): its algorithmic bytes / its
-                        CUDA-event time vs the measured HBM copy bandwidth of this pool
+                        CUDA-event time vs the measured HBM copy bandwidth
                         (MEASURED_PEAKS.json); "step" and "fwd" give the same figure for the
                         whole step and for the forward kernel
   cpu_baseline          the C/OpenMP port of the reference's sequential scan (oracle/),
                         timed on the host cores on a bounded sample (N=1, rank 0 only)
+  others                the other configurations of the hot path, measured on rank 0's GPU after the
+                        headline legs: config 3 (decode of 1024 consecutive tokens, eager and as
+                        one CUDA graph) and config 2 (the mixer layer forward+backward and its four
+                        row-kernel calls; under --gpus N every rank owns batch 8/N of it)
 
-``--impl reference`` times only that CPU port (all host threads) and prints the same
-line with ``"impl": "reference"``.
+``--impl reference`` times only that CPU port on WHOLE steps of the same workload with all host
+threads (set explicitly: a launcher may export OMP_NUM_THREADS=1) and prints the same line with
+``"impl": "reference"``.  Its metric is a throughput, so the figure does not depend on --gpus.
 """
 
 from __future__ import annotations
@@ -45,10 +50,29 @@ sys.path.insert(0, str(ROOT))
 CFG = dict(batch=8, heads=16, T=4096, P=64, N=64, chunk=64)
 METRIC = "v2x2ssd fwd+bwd tokens/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the backward sweep at this exact
-# workload, from the committed ncu capture (a profiler figure, not measured live by this script)
-NCU_TRAFFIC_BWD_BYTES = 549_817_344 + 312_087_040
-NCU_TRAFFIC_SOURCE = "profiles/scan_tc_fwd_bwd_config1.md (ncu --set full, one launch)"
+TRAFFIC_FILE = ROOT / "profiles" / "scan_tc_bwd_traffic.json"
+
+
+def kernel_source_digest() -> str:
+    """sha256 over the tensor-core scan sources: ties a profiler figure to the kernels it was taken on."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in ("scan_tc.cu", "scan_tc_fwd.cuh", "scan_tc_bwd.cuh", "tc_common.cuh"):
+        h.update((ROOT / "slinoss_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the backward sweep at this
+    workload, as recorded beside the ncu summary (a profiler figure, not measured live here).
+    Null when the kernels have changed since the capture."""
+    try:
+        rec = json.loads(TRAFFIC_FILE.read_text())
+    except Exception:
+        return None, None
+    if rec.get("kernel_source_digest") != kernel_source_digest():
+        return None, f"{TRAFFIC_FILE.name}: taken on other kernel sources ({rec.get('kernel_source_digest')})"
+    return int(rec["dram_bytes_per_launch"]), f"{TRAFFIC_FILE.name}: {rec.get('how', '')}"
 
 
 def algorithmic_bytes(c) -> dict:
@@ -121,6 +145,7 @@ def cpu_baseline(sample_heads: int = 16, repeats: int = 1) -> dict:
     from oracle import scan_c
     from slinoss_b200.synthetic import make_scan_case
     c = CFG
+    scan_c.set_num_threads(os.cpu_count() or 1)   # explicit: a launcher may have exported OMP_NUM_THREADS=1
     case = make_scan_case(1, sample_heads, c["T"], c["P"], c["N"], dtype=torch.bfloat16, seed=0)
     arrs = [t.float().numpy() for t in case.tensors()]
     dY = case.dY.float().numpy()
@@ -141,20 +166,41 @@ def cpu_baseline(sample_heads: int = 16, repeats: int = 1) -> dict:
 
 
 def run_reference_arm(args, rank):
+    """The reference's CPU path for this workload = the C/OpenMP port of its sequential scan
+    (forward + analytic backward), on WHOLE steps of config 1 with every host core.  The number
+    of steps is capped so that the run ends within a few minutes; the line says how many ran."""
     if rank != 0:
         return
-    base = cpu_baseline(sample_heads=8, repeats=1)
-    times = [base["sample_seconds"]]
-    for _ in range(max(0, args.steps - 1)):
-        times.append(cpu_baseline(sample_heads=8)["sample_seconds"])
-    scale = CFG["batch"] * CFG["heads"] / 8
-    step_s = statistics.mean(times) * scale
-    value = CFG["batch"] * CFG["T"] / step_s
-    base["value"] = value
+    from oracle import scan_c
+    from slinoss_b200.synthetic import make_scan_case
+    c = CFG
+    cores = scan_c.set_num_threads(os.cpu_count() or 1)
+    case = make_scan_case(c["batch"], c["heads"], c["T"], c["P"], c["N"], dtype=torch.bfloat16, seed=0)
+    arrs = [t.float().numpy() for t in case.tensors()]
+    dY = case.dY.float().numpy()
+    budget_s, times = 150.0, []
+    t_begin = time.perf_counter()
+    for i in range(max(1, args.warmup // 3) + max(2, args.steps)):
+        t0 = time.perf_counter()
+        scan_c.forward(*arrs)
+        scan_c.backward(*arrs, dY)
+        dt = time.perf_counter() - t0
+        if i >= max(1, args.warmup // 3):
+            times.append(dt)            # (the first pass warms caches and the thread pool)
+        if len(times) >= 2 and time.perf_counter() - t_begin + dt > budget_s:
+            break
+    step_s = statistics.mean(times)
+    value = c["batch"] * c["T"] / step_s
+    base = {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{len(times)} whole steps (batch {c['batch']} x {c['heads']} heads x T {c['T']}), "
+                      f"{step_s:.2f} s each, not scaled"}
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": len(times), "warmup": 0, "ms_per_step": step_s * 1e3,
+            "n_gpus": args.gpus, "steps": len(times), "steps_requested": args.steps, "warmup": 1,
+            "ms_per_step": step_s * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": workload_config(args.gpus),
+            "note": "host throughput of one whole step; a throughput does not grow with --gpus, so at "
+                    "N > 1 compare it with the GPU arm's value / N",
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -176,12 +222,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--small", action="store_true", help="T=512 variant for profiler captures")
-    ap.add_argument("--e2e-head-parts", type=int, default=2,
-                    help="end-to-end leg: slices per batch entry along heads (pipeline granularity)")
+    ap.add_argument("--T", type=int, default=0, help="override the sequence length (smaller cases)")
+    ap.add_argument("--no-others", action="store_true", help="skip the config 2 / config 3 legs")
+    ap.add_argument("--e2e-head-parts", type=int, default=0,
+                    help="end-to-end leg: slices per batch entry along heads (0 = 2 on one GPU, 1 when "
+                         "several ranks share the host)")
     ap.add_argument("--e2e-op-streams", type=int, default=2,
                     help="end-to-end leg: streams the op runs on, slices alternate between them")
-    ap.add_argument("--tc-warps", type=int, default=0, help="development knob: warps per TMEM quadrant")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -189,8 +236,8 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
-    if args.small:
-        CFG["T"] = 512
+    if args.T > 0:
+        CFG["T"] = args.T
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path.")
     args.warmup = max(args.warmup, 3)
@@ -205,8 +252,6 @@ def main():
     from slinoss_b200.ops.v2x2ssd import v2x2ssd_cute
     from slinoss_b200.synthetic import make_scan_case
 
-    if args.tc_warps:
-        _C.lib().sl_tune_tc_warps(args.tc_warps)
     c = CFG
     case_h = make_scan_case(c["batch"], c["heads"], c["T"], c["P"], c["N"], dtype=torch.bfloat16,
                             seed=shard.rank_seed(0, rank))
@@ -270,7 +315,8 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in h_in)
     d_in = [torch.empty_like(t, device=dev) for t in h_in]
     # one slice = one batch entry x a block of heads: short pipeline fill and drain
-    hp = max(1, min(args.e2e_head_parts, c["heads"]))
+    hp = args.e2e_head_parts if args.e2e_head_parts > 0 else (2 if world == 1 else 1)
+    hp = max(1, min(hp, c["heads"]))
     hs = c["heads"] // hp
     slices = [(slice(b, b + 1), slice(h * hs, (h + 1) * hs if h + 1 < hp else c["heads"]))
               for b in range(c["batch"]) for h in range(hp)]
@@ -283,27 +329,45 @@ def main():
     s_ops = [torch.cuda.Stream(dev) for _ in range(max(1, args.e2e_op_streams))]
     main_stream = torch.cuda.current_stream(dev)
 
+    # per-slice views and autograd leaves are built once, outside the step
+    views = [([d[sl] for d in d_in], [h[sl] for h in h_in], [h[sl] for h in h_out]) for sl in slices]
+    leaves_of = [[v.detach().requires_grad_(True) for v in dv[:5]] for dv, _, _ in views]
+
+    def copy_only():
+        """The same bytes over the same streams without the op: the host-link bound of the step."""
+        for s in (s_in, s_out):
+            s.wait_stream(main_stream)
+        for dv, hv, ho in views:
+            with torch.cuda.stream(s_in):
+                for d, h in zip(dv, hv):
+                    d.copy_(h, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                for h, d in zip(ho, (dv[0], dv[0], dv[1], dv[2], dv[3], dv[4])):
+                    h.copy_(d, non_blocking=True)
+        for s in (s_in, s_out):
+            main_stream.wait_stream(s)
+
     def step_e2e():
         for s in (s_in, s_out, *s_ops):
             s.wait_stream(main_stream)
-        for i, sl in enumerate(slices):
+        for i, (dv, hv, ho) in enumerate(views):
             s_op = s_ops[i % len(s_ops)]
             with torch.cuda.stream(s_in):
-                for d, h in zip(d_in, h_in):
-                    d[sl].copy_(h[sl], non_blocking=True)
+                for d, h in zip(dv, hv):
+                    d.copy_(h, non_blocking=True)
                 ev_in = torch.cuda.Event(); ev_in.record(s_in)
             with torch.cuda.stream(s_op):
                 s_op.wait_event(ev_in)
-                leaves = [d[sl].detach().requires_grad_(True) for d in d_in[:5]]
+                leaves = leaves_of[i]
                 Y = v2x2ssd_cute(*leaves, chunk_size=c["chunk"], path=args.path)
-                grads = torch.autograd.grad(Y, leaves, d_in[5][sl])
+                grads = torch.autograd.grad(Y, leaves, dv[5])
                 outs = (Y.detach(), *grads)
                 ev_op = torch.cuda.Event(); ev_op.record(s_op)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_op)
-                for h, o in zip(h_out, outs):
+                for h, o in zip(ho, outs):
                     o.record_stream(s_out)
-                    h[sl].copy_(o, non_blocking=True)
+                    h.copy_(o, non_blocking=True)
         for s in (s_in, s_out, *s_ops):
             main_stream.wait_stream(s)
 
@@ -318,9 +382,36 @@ def main():
     barrier()
     e2e_ms = t_start.elapsed_time(t_end)
     clocks = sampler.stop() if rank == 0 else None   # sampled over the device-timed and the end-to-end loops
+    copy_only()
+    barrier()
+    t_start.record()
+    for _ in range(e2e_steps):
+        copy_only()
+    t_end.record()
+    barrier()
+    copy_ms = t_start.elapsed_time(t_end)
+
+    # ---- the other configurations of the hot path (rank-local figures; rank 0's are reported) ----
+    others = None
+    if not args.no_others and args.path != "simt" and args.T == 0:
+        del d_in, h_in, h_out, views, leaves_of
+        torch.cuda.empty_cache()
+        from slinoss_b200 import measure
+        measure.PRINT_LINES = False
+        bshare = max(1, 8 // world)
+        others = {
+            "config3_decode": measure.measure_decode_sequence(0, dev, steps=1024, batch=256),
+            "config2_mixer": measure.measure_mixer(12, dev, batch=bshare)
+                             + measure.measure_scanprep(10, dev, batch=bshare)
+                             + measure.measure_tail(10, dev, batch=bshare),
+            "note": "config 3: 1024 consecutive tokens, fresh inputs per token; config 2: batch "
+                    f"{bshare} per GPU (8 sharded over {world} rank(s)); figures of rank 0's GPU",
+        }
+        barrier()
 
     # the job is as slow as its slowest rank: MAX over ranks of every device-timed figure
-    total_ms, e2e_ms, fwd_ms, bwd_ms = (shard.reduce_step_ms(v, dev) for v in (total_ms, e2e_ms, fwd_ms, bwd_ms))
+    total_ms, e2e_ms, fwd_ms, bwd_ms, copy_ms = (shard.reduce_step_ms(v, dev)
+                                                 for v in (total_ms, e2e_ms, fwd_ms, bwd_ms, copy_ms))
     if rank == 0:
         tokens_step = world * c["batch"] * c["T"]
         ms_step = total_ms / args.steps
@@ -328,8 +419,7 @@ def main():
         peak, peak_kind = measured_peak()
         achieved = ab["total"] / (ms_step * 1e-3) / 1e9
         bwd_gbs = ab["bwd"] / (bwd_ms * 1e-3) / 1e9
-        full_tc = args.path != "simt" and not args.small
-        traffic = NCU_TRAFFIC_BWD_BYTES if full_tc else None
+        traffic, traffic_source = ncu_traffic() if (args.path != "simt" and args.T == 0) else (None, None)
         line = {
             "metric": METRIC, "value": tokens_step / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -337,11 +427,14 @@ def main():
             "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": tokens_step / (e2e_ms / e2e_steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / e2e_steps},
+                    "ms_per_step": e2e_ms / e2e_steps, "slices": len(slices),
+                    "copy_only_ms_per_step": copy_ms / e2e_steps,
+                    "note": "copy_only = the same host<->device bytes over the same streams without the op: "
+                            "the host-link bound of this step on this box"},
             "gpu_launches": launches_timed,
             "roofline": {"bound": "hbm", "kernel": "backward sweep (scan_tc_bwd_kernel + its scalar finish)",
                          "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
-                         "traffic": traffic, "traffic_source": NCU_TRAFFIC_SOURCE if traffic else None,
+                         "traffic": traffic, "traffic_source": traffic_source,
                          "peak_source": peak_kind, "algorithmic_bytes": ab["bwd"], "ms": bwd_ms,
                          "share_of_step": bwd_ms / (fwd_ms + bwd_ms),
                          "step": {"ms": ms_step, "algorithmic_bytes": ab["total"], "achieved": achieved,
@@ -352,6 +445,8 @@ def main():
             "clocks": clocks,
             "kernel_path": args.path,
         }
+        if others is not None:
+            line["others"] = others
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_heads=8)
         print(json.dumps(line), flush=True)

@@ -22,6 +22,11 @@
 #include <omp.h>
 #endif
 
+/* torchrun exports OMP_NUM_THREADS=1: callers that want all cores say so explicitly */
+void oracle_set_num_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

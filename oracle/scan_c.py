@@ -32,6 +32,12 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Threads the OpenMP loops use from now on (an explicit call overrides OMP_NUM_THREADS)."""
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def _c(x):
     return None if x is None else np.ascontiguousarray(x, dtype=np.float32)
 

@@ -1,0 +1,120 @@
+"""Training step of the stacked language model, data parallel over the GPUs of one node.
+
+    python -m slinoss_b200.lm_bench --steps 5 --warmup 3                      # one GPU
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
+        -m slinoss_b200.lm_bench --steps 5 --warmup 3                         # eight GPUs
+
+Model: token embedding -> ``SLinOSSStack`` (24 blocks of mixer + GELU MLP 4x, RMSNorm, d_model 2048,
+32 heads x 64, N 64) -> tied head, vocabulary 32000, random init (std 0.02), bf16 parameters.
+Data: uniform random token ids, 4 sequences of 4096 tokens PER GPU (global batch 32 on 8 GPUs).
+Every rank runs forward, backward, gradient all-reduce (NCCL, buckets started from autograd hooks
+on a side stream so that they run behind the rest of the backward pass), clipping and AdamW.
+
+Rank 0 prints one JSON line: tokens/s of the whole job, step time (MAX over ranks, CUDA events), the
+same step without the all-reduce, and their difference = the EXPOSED part of the collective.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import shard
+from .lm import DataParallelTrainer, SLinOSSLM, lm_stack_config
+
+
+def timed_steps(trainer, ids, steps, warmup, barrier):
+    losses = []
+    for _ in range(warmup):
+        losses.append(trainer.step(ids))
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        losses.append(trainer.step(ids))
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / steps, [float(x) for x in losses]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=0, help="informational; the launcher sets WORLD_SIZE")
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--d-model", type=int, default=2048)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--batch-per-gpu", type=int, default=4)
+    ap.add_argument("--bucket-mb", type=int, default=32)
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("slinoss_b200.lm_bench needs CUDA devices: the kernels have no CPU path.")
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    torch.manual_seed(0)                         # identical replicas on every rank
+    cfg = lm_stack_config(args.d_model, args.layers)
+    model = SLinOSSLM(args.vocab, cfg, device=dev, dtype=torch.bfloat16)
+    n_params = sum(p.numel() for p in model.parameters())
+    g = torch.Generator(device=dev).manual_seed(shard.rank_seed(1, rank))
+    ids = torch.randint(0, args.vocab, (args.batch_per_gpu, args.seq), generator=g, device=dev)
+
+    trainer = DataParallelTrainer(model, bucket_bytes=args.bucket_mb << 20, reduce=world > 1)
+    ms, losses = timed_steps(trainer, ids, args.steps, args.warmup, barrier)
+    ms = shard.reduce_step_ms(ms, dev)
+    ms_plain = None
+    if world > 1:                                # the same step with the collective taken out
+        trainer.reducer.remove()
+        n_buckets = len(trainer.reducer.buckets)
+        trainer.reducer = None
+        ms_plain, _ = timed_steps(trainer, ids, args.steps, 1, barrier)
+        ms_plain = shard.reduce_step_ms(ms_plain, dev)
+    else:
+        n_buckets = 0
+    mem_gb = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    if rank == 0:
+        tokens = world * args.batch_per_gpu * args.seq
+        line = {
+            "what": "stacked-LM training step (forward, backward, gradient all-reduce, clip, AdamW)",
+            "config": {"layers": args.layers, "d_model": args.d_model, "heads": args.d_model // 64,
+                       "d_state": 64, "vocab": args.vocab, "seq": args.seq,
+                       "batch_per_gpu": args.batch_per_gpu, "global_batch": world * args.batch_per_gpu,
+                       "dtype": "bf16", "parameters": n_params, "data": "synthetic uniform ids"},
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
+            "ms_per_step_without_allreduce": ms_plain,
+            "exposed_allreduce_ms": None if ms_plain is None else ms - ms_plain,
+            "allreduce": {"buckets": n_buckets, "bucket_mb": args.bucket_mb,
+                          "bytes": 2 * n_params, "backend": "nccl" if world > 1 else None},
+            "loss_first": losses[0], "loss_last": losses[args.warmup + args.steps - 1],
+            "peak_memory_gb": mem_gb,
+        }
+        text = json.dumps(line)
+        print(text, flush=True)
+        if args.out:
+            with open(args.out, "w") as f:
+                f.write(text + "\n")
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

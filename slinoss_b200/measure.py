@@ -1,6 +1,6 @@
 """Device timing of every C-ABI entry point at the sizes of the reference's configs.
 
-    python -m slinoss_b200.measure [--what decode,scanprep,tail,mixer,scan] [--iters 20]
+    python -m slinoss_b200.measure [--what decode,decode_sequence,scanprep,tail,mixer,scan] [--iters 20]
 
 Prints one JSON line per measured call: CUDA-event time (mean of ``iters`` back-to-back
 launches after warm-up, on the launching stream), the call's algorithmic bytes (every
@@ -50,6 +50,15 @@ def time_ms(fn, iters: int, warmup: int = 3) -> float:
     return e0.elapsed_time(e1) / iters
 
 
+PRINT_LINES = True   # `python -m slinoss_b200.measure` prints; bench.py collects the returned lines instead
+
+
+def emit(line):
+    if PRINT_LINES:
+        print(json.dumps(line), flush=True)
+    return line
+
+
 def report(name, ms, algo_bytes, config, extra=None):
     peak, kind = hbm_peak()
     gbs = algo_bytes / (ms * 1e-3) / 1e9
@@ -57,12 +66,11 @@ def report(name, ms, algo_bytes, config, extra=None):
             "peak_gbs": peak, "peak_source": kind, "frac": gbs / peak, "config": config}
     if extra:
         line.update(extra)
-    print(json.dumps(line), flush=True)
-    return line
+    return emit(line)
 
 
 # ---------------------------------------------------------------------------------------
-def measure_decode(iters, dev):
+def measure_decode(iters, dev, batch=None):
     """Config 3: batch 256, heads 32, P 64, N 64, bf16 vectors, float32 state."""
     from . import _C
     g = torch.Generator().manual_seed(0)
@@ -87,8 +95,8 @@ def measure_decode(iters, dev):
         _C.scan_decode(U, M, K, Bv, Cv, state, Bp, Up, y_dtype=torch.bfloat16, state_out=state)
 
     algo = nbytes(state, state2, U, Bv, Cv, M, K, Bp, Up) + nbytes(U)
-    report("sl_v2x2ssd_decode (state out of place)", time_ms(out_of_place, iters), algo, cfg)
-    report("sl_v2x2ssd_decode (state in place)", time_ms(in_place, iters), algo, cfg)
+    lines = [report("sl_v2x2ssd_decode (state out of place)", time_ms(out_of_place, iters), algo, cfg),
+             report("sl_v2x2ssd_decode (state in place)", time_ms(in_place, iters), algo, cfg)]
 
     # the same call as a serving loop would issue it: 16 tokens captured once in a CUDA graph
     # (state ping-pongs between two buffers), then replayed
@@ -110,8 +118,69 @@ def measure_decode(iters, dev):
     with torch.cuda.graph(graph):
         loop()
     ms = time_ms(graph.replay, max(2, iters // 4)) / tokens
-    report("sl_v2x2ssd_decode (CUDA-graph replay of 16 tokens, per token)", ms, algo, cfg,
-           {"us_per_sequence_token": ms * 1e3 / b, "tokens_per_s": b / (ms * 1e-3)})
+    lines.append(report("sl_v2x2ssd_decode (CUDA-graph replay of 16 tokens, per token)", ms, algo, cfg,
+                        {"us_per_sequence_token": ms * 1e3 / b, "tokens_per_s": b / (ms * 1e-3)}))
+    return lines
+
+
+def measure_decode_sequence(iters, dev, steps=1024, batch=256):
+    """Config 3 as the reference's decode harness runs it (scripts/perf/_training_decode.py:182-214):
+    ``steps`` CONSECUTIVE tokens with fresh per-token inputs over the carried float32 state, one pair
+    of CUDA events around all of them; eager launches, then the whole sequence replayed from one CUDA
+    graph.  Per-token inputs are drawn on the device (5.3 MB per token)."""
+    from . import _C
+    h, P, N = 32, 64, 64
+    g = torch.Generator(device=dev).manual_seed(3)
+    r = lambda *s: torch.randn(*s, generator=g, device=dev)
+    U = r(steps, batch, h, P).to(torch.bfloat16)
+    Bv = (r(steps, batch, h, 2 * N) / N ** 0.5).to(torch.bfloat16)
+    Cv = (r(steps, batch, h, 2 * N) / N ** 0.5).to(torch.bfloat16)
+    rad = torch.clamp(torch.exp(-torch.nn.functional.softplus(r(steps, batch, h))), 0.9, 0.999)
+    th = (torch.rand(steps, batch, h, generator=g, device=dev) * 2 - 1) * torch.pi
+    M = torch.stack([rad * torch.cos(th), rad * torch.sin(th)], -1).contiguous()
+    K = 0.05 * r(steps, batch, h, 2, 2)
+    state0 = 0.1 * r(batch, h, P, 2 * N)
+    state = state0.clone()
+    zeroB, zeroU = torch.zeros_like(Bv[0]), torch.zeros_like(U[0])
+    Y = torch.empty(steps, batch, h, P, dtype=torch.bfloat16, device=dev)
+
+    def sequence():
+        for t in range(steps):      # the carried taps are the previous token's B and U
+            bp, up = (zeroB, zeroU) if t == 0 else (Bv[t - 1], U[t - 1])
+            y, _ = _C.scan_decode(U[t], M[t], K[t], Bv[t], Cv[t], state, bp, up,
+                                  y_dtype=torch.bfloat16, state_out=state)
+            Y[t].copy_(y)
+
+    algo = 2 * nbytes(state) + nbytes(U[0], Bv[0], Cv[0], M[0], K[0], zeroB, zeroU) + nbytes(U[0])
+    cfg = f"config 3: batch {batch} x heads 32 x P 64 x N 64, {steps} consecutive tokens, fresh inputs per token"
+    lines = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sequence()                     # warm-up pass
+    torch.cuda.synchronize()
+    state.copy_(state0)
+    e0.record(); sequence(); e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    extra = lambda m: {"us_per_step": m * 1e3, "tokens_per_s": batch / (m * 1e-3), "steps": steps}
+    lines.append(report("decode sequence, eager launches (per step; includes the copy of y)", ms, algo, cfg, extra(ms)))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sequence()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sequence()
+    state.copy_(state0)
+    graph.replay()
+    torch.cuda.synchronize()
+    state.copy_(state0)
+    e0.record(); graph.replay(); e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    lines.append(report("decode sequence, one CUDA graph of all steps (per step)", ms, algo, cfg, extra(ms)))
+    return lines
 
 
 def _mixer_tensors(dev, batch=8, T=2048, heads=32, P=64, N=64):
@@ -127,65 +196,67 @@ def _mixer_tensors(dev, batch=8, T=2048, heads=32, P=64, N=64):
     return gate, value, params, bc, w, bias
 
 
-def measure_scanprep(iters, dev):
+def measure_scanprep(iters, dev, batch=8):
     """Config 2 sizes: batch 8, T 2048, heads 32, P 64, N 64, conv width 4, bf16."""
     from . import _C
     from .layers import SLinOSSScanPrep
     heads, P, N = 32, 64, 64
-    gate, value, params, bc, w, bias = _mixer_tensors(dev)
+    gate, value, params, bc, w, bias = _mixer_tensors(dev, batch=batch)
     owner = SLinOSSScanPrep(n_heads=heads, d_state=N, d_head=P, device=dev)
     biases = tuple(getattr(owner, k).detach().float().contiguous()
                    for k in ("dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias", "theta_sign"))
     cfg = _C.make_config(owner)
-    name = "config 2: batch 8 x T 2048 x heads 32 x P 64 x N 64, conv width 4, bf16"
+    name = f"config 2: batch {batch} x T 2048 x heads 32 x P 64 x N 64, conv width 4, bf16"
     outs = _C.scanprep_conv_fwd(value, w, bias, None, params, bc, biases, cfg, heads=heads, P=P,
                                 want_state=True)
     U, M, K, Bo, Co, nstate = outs
     vbytes = value.shape[0] * value.shape[1] * value.shape[2] * 2
     algo_f = vbytes + nbytes(params, bc, w, bias, U, M, K, Bo, Co, nstate)
-    report("sl_scanprep_conv_fwd (conv + SiLU + scan preparation, 3 kernels)",
-           time_ms(lambda: _C.scanprep_conv_fwd(value, w, bias, None, params, bc, biases, cfg,
-                                                heads=heads, P=P, want_state=True), iters),
-           algo_f, name)
+    lines = [report("sl_scanprep_conv_fwd (conv + SiLU + scan preparation, 3 kernels)",
+                    time_ms(lambda: _C.scanprep_conv_fwd(value, w, bias, None, params, bc, biases, cfg,
+                                                         heads=heads, P=P, want_state=True), iters),
+                    algo_f, name)]
     dU, dM, dK = torch.randn_like(U), torch.randn_like(M), torch.randn_like(K)
     dB, dC = torch.randn_like(Bo), torch.randn_like(Co)
     res = _C.scanprep_conv_bwd(value, w, bias, None, params, bc, biases, cfg, dU, dM, dK, dB, dC,
                                heads=heads, P=P)
     algo_b = vbytes + nbytes(params, bc, w, bias, dU, dM, dK, dB, dC, res["d_value"], res["d_params"],
                              res["d_bc"])
-    report("sl_scanprep_conv_bwd (3 kernels; includes zeroing of the float32 accumulators)",
-           time_ms(lambda: _C.scanprep_conv_bwd(value, w, bias, None, params, bc, biases, cfg, dU, dM,
-                                                dK, dB, dC, heads=heads, P=P), iters),
-           algo_b, name)
+    lines.append(report("sl_scanprep_conv_bwd (3 kernels; includes zeroing of the float32 accumulators)",
+                        time_ms(lambda: _C.scanprep_conv_bwd(value, w, bias, None, params, bc, biases, cfg,
+                                                             dU, dM, dK, dB, dC, heads=heads, P=P), iters),
+                        algo_b, name))
+    return lines
 
 
-def measure_tail(iters, dev):
+def measure_tail(iters, dev, batch=8):
     from . import _C
     heads, P = 32, 64
-    gate, value, *_ = _mixer_tensors(dev)
+    gate, value, *_ = _mixer_tensors(dev, batch=batch)
     g = torch.Generator().manual_seed(1)
-    Y = torch.randn(8, heads, 2048, P, generator=g).to(torch.bfloat16).to(dev)
-    Uskip = torch.randn(8, heads, 2048, P, generator=g).to(torch.bfloat16).to(dev)
+    Y = torch.randn(batch, heads, 2048, P, generator=g).to(torch.bfloat16).to(dev)
+    Uskip = torch.randn(batch, heads, 2048, P, generator=g).to(torch.bfloat16).to(dev)
     d_skip = torch.ones(heads, device=dev)
     wn = torch.ones(heads * P, device=dev, dtype=torch.bfloat16)
-    name = "config 2: batch 8 x T 2048 x d_inner 2048 (32 heads x 64), bf16"
+    name = f"config 2: batch {batch} x T 2048 x d_inner 2048 (32 heads x 64), bf16"
     normed = _C.mixer_tail_fwd(Y, gate, Uskip, d_skip, wn, 1e-5)
     gbytes = gate.shape[0] * gate.shape[1] * gate.shape[2] * 2
-    report("sl_mixer_tail_fwd", time_ms(lambda: _C.mixer_tail_fwd(Y, gate, Uskip, d_skip, wn, 1e-5), iters),
-           nbytes(Y, Uskip, normed) + gbytes, name)
+    lines = [report("sl_mixer_tail_fwd", time_ms(lambda: _C.mixer_tail_fwd(Y, gate, Uskip, d_skip, wn, 1e-5), iters),
+                    nbytes(Y, Uskip, normed) + gbytes, name)]
     dn = torch.randn_like(normed)
     outs = _C.mixer_tail_bwd(Y, gate, Uskip, d_skip, wn, 1e-5, dn)
-    report("sl_mixer_tail_bwd (includes zeroing of the float32 accumulators)",
-           time_ms(lambda: _C.mixer_tail_bwd(Y, gate, Uskip, d_skip, wn, 1e-5, dn), iters),
-           nbytes(Y, Uskip, dn, outs[0], outs[1], outs[2]) + gbytes, name)
+    lines.append(report("sl_mixer_tail_bwd (includes zeroing of the float32 accumulators)",
+                        time_ms(lambda: _C.mixer_tail_bwd(Y, gate, Uskip, d_skip, wn, 1e-5, dn), iters),
+                        nbytes(Y, Uskip, dn, outs[0], outs[1], outs[2]) + gbytes, name))
+    return lines
 
 
-def measure_mixer(iters, dev):
+def measure_mixer(iters, dev, batch=8):
     """Whole mixer layer, forward + backward, config 2 (GEMMs are cuBLAS; tensor-pipe bound)."""
     import slinoss_b200 as sb
     torch.manual_seed(0)
     mixer = sb.SLinOSSMixer(1024, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(dev).to(torch.bfloat16)
-    x = torch.randn(8, 2048, 1024, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    x = torch.randn(batch, 2048, 1024, device=dev, dtype=torch.bfloat16, requires_grad=True)
 
     def step():
         out = mixer(x)
@@ -194,10 +265,10 @@ def measure_mixer(iters, dev):
         x.grad = None
 
     ms = time_ms(step, max(3, iters // 4))
-    flops = 3 * 2 * 8 * 2048 * 1024 * (12384 + 2048)    # in_proj + out_proj, fwd + 2x bwd
-    print(json.dumps({"call": "SLinOSSMixer forward+backward (config 2)", "ms": ms,
-                      "tokens_per_s": 8 * 2048 / (ms * 1e-3), "gemm_tflops_equivalent": flops / (ms * 1e-3) / 1e12,
-                      "config": "x (8, 2048, 1024) bf16, d_inner 2048, 32 heads x 64, N 64, d_conv 4"}), flush=True)
+    flops = 3 * 2 * batch * 2048 * 1024 * (12384 + 2048)    # in_proj + out_proj, fwd + 2x bwd
+    return [emit({"call": "SLinOSSMixer forward+backward (config 2)", "ms": ms,
+                  "tokens_per_s": batch * 2048 / (ms * 1e-3), "gemm_tflops_equivalent": flops / (ms * 1e-3) / 1e12,
+                  "config": f"x ({batch}, 2048, 1024) bf16, d_inner 2048, 32 heads x 64, N 64, d_conv 4"})]
 
 
 def measure_scan(iters, dev):
@@ -210,22 +281,22 @@ def measure_scan(iters, dev):
                               y_dtype=torch.bfloat16, want_final=False, save_states=True)
     _, fin, st = fwd()
     bht = 8 * 16 * 4096
-    report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name)
-    report("sl_v2x2ssd_bwd (saved chunk states)",
-           time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
-                                       chunk_size=64, saved=(st, fin)), iters), bht * 1456, name)
-    report("sl_v2x2ssd_bwd (recomputing chunk states)",
-           time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
-                                       chunk_size=64), iters), bht * 1456, name)
+    return [report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name),
+            report("sl_v2x2ssd_bwd (saved chunk states)",
+                   time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
+                                               chunk_size=64, saved=(st, fin)), iters), bht * 1456, name),
+            report("sl_v2x2ssd_bwd (recomputing chunk states)",
+                   time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
+                                               chunk_size=64), iters), bht * 1456, name)]
 
 
-WHAT = {"decode": measure_decode, "scanprep": measure_scanprep, "tail": measure_tail,
-        "mixer": measure_mixer, "scan": measure_scan}
+WHAT = {"decode": measure_decode, "decode_sequence": measure_decode_sequence,
+        "scanprep": measure_scanprep, "tail": measure_tail, "mixer": measure_mixer, "scan": measure_scan}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="decode,scanprep,tail,mixer,scan")
+    ap.add_argument("--what", default="decode,decode_sequence,scanprep,tail,mixer,scan")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():

@@ -8,7 +8,11 @@ path; the only collectives are the host-side ones here:
 * ``job_throughput``   - units of all ranks divided by that time;
 * ``allreduce_mean_``  - weight-gradient averaging when the mixer is *trained* data
   parallel (weights replicated, batch sharded), one flat bucket per dtype so that the
-  cost is launch-latency bound, not per-tensor bound.
+  cost is launch-latency bound, not per-tensor bound;
+* ``GradBucketReducer`` - the same averaging for a large model: gradients are packed into
+  buckets of a few tens of megabytes in the order the backward pass produces them and every
+  bucket's all-reduce starts from an autograd hook on a side stream as soon as its last
+  gradient exists, so the collective runs behind the rest of the backward pass.
 
 All functions take CPU or CUDA tensors and work with the ``gloo`` and ``nccl`` backends
 of ``torch.distributed``; with no process group they degrade to the single-process
@@ -112,3 +116,123 @@ def allreduce_mean_(grads: Iterable[Optional[torch.Tensor]], group=None) -> None
             k = g.numel()
             g.copy_(flat[off:off + k].view_as(g).to(dtype))
             off += k
+
+
+class GradBucketReducer:
+    """Bucketed, overlapped gradient averaging for data-parallel training (one process per GPU,
+    weights replicated, batch sharded): the collective of the stacked-LM training configuration.
+
+    Parameters are dealt into buckets of about ``bucket_bytes`` in REVERSE registration order,
+    which is the order in which the backward pass finishes their gradients.  A
+    ``post_accumulate_grad`` hook counts the gradients of a bucket; the last one packs the bucket
+    into its flat buffer on a side stream (ordered after the stream that produced the gradients)
+    and starts ``all_reduce(SUM)`` there without waiting.  ``finish()`` starts whatever is left
+    (a parameter that got no gradient counts as zeros, so that every rank issues the same
+    collectives), waits, writes ``sum / world`` back into every ``p.grad`` and orders the calling
+    stream after all of it.  With no process group the class does nothing (world size 1).
+
+    Works with ``nccl`` (CUDA tensors, real overlap) and ``gloo`` (CPU tensors)."""
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], *, bucket_bytes: int = 32 << 20,
+                 group=None, reduce_dtype: Optional[torch.dtype] = None) -> None:
+        self.group = group
+        self.params = [p for p in params if p.requires_grad]
+        self.reduce_dtype = reduce_dtype
+        self.buckets: list[dict] = []
+        self._bucket_of: dict[int, dict] = {}
+        self._hooks = []
+        self._stream = None
+        open_bucket: dict = {}
+        for p in reversed(self.params):
+            dt = reduce_dtype or p.dtype
+            key = (dt, p.device)
+            b = open_bucket.get(key)
+            nbytes = p.numel() * torch.empty((), dtype=dt).element_size()
+            if b is None or (b["bytes"] + nbytes > bucket_bytes and b["params"]):
+                b = {"params": [], "bytes": 0, "numel": 0, "dtype": dt, "device": p.device, "flat": None,
+                     "ready": 0, "handle": None}
+                self.buckets.append(b)
+                open_bucket[key] = b
+            b["params"].append(p)
+            b["bytes"] += nbytes
+            b["numel"] += p.numel()
+            self._bucket_of[id(p)] = b
+        if _active(group):
+            for p in self.params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    # -- hooks ------------------------------------------------------------------------------
+    def _on_grad(self, p: torch.Tensor) -> None:
+        b = self._bucket_of[id(p)]
+        b["ready"] += 1
+        if b["ready"] == len(b["params"]):
+            self._launch(b)
+
+    def _side_stream(self, device):
+        if device.type != "cuda":
+            return None
+        if self._stream is None:
+            self._stream = torch.cuda.Stream(device)
+        return self._stream
+
+    def _launch(self, b: dict) -> None:
+        if b["flat"] is None:
+            b["flat"] = torch.empty(b["numel"], dtype=b["dtype"], device=b["device"])
+        side = self._side_stream(b["device"])
+
+        def pack_and_start():
+            off = 0
+            for p in b["params"]:
+                n = p.numel()
+                dst = b["flat"][off:off + n]
+                if p.grad is None:
+                    dst.zero_()
+                else:
+                    dst.copy_(p.grad.reshape(-1))
+                off += n
+            b["handle"] = dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+        if side is None:
+            pack_and_start()
+        else:
+            side.wait_stream(torch.cuda.current_stream(b["device"]))
+            with torch.cuda.stream(side):
+                pack_and_start()
+
+    # -- end of the backward pass -----------------------------------------------------------
+    def finish(self) -> None:
+        """Call after ``backward()``: completes every bucket and leaves the averaged gradients
+        in ``p.grad``."""
+        if not _active(self.group):
+            return
+        n = dist.get_world_size(self.group)
+        for b in self.buckets:
+            if b["handle"] is None:
+                self._launch(b)
+        for b in self.buckets:
+            side = self._side_stream(b["device"])
+            ctx = torch.cuda.stream(side) if side is not None else _NullContext()
+            with ctx:
+                b["handle"].wait()
+                off = 0
+                for p in b["params"]:
+                    k = p.numel()
+                    if p.grad is not None:
+                        p.grad.copy_((b["flat"][off:off + k] / n).view_as(p.grad))
+                    off += k
+            b["handle"], b["ready"] = None, 0
+        if self._stream is not None:
+            torch.cuda.current_stream(self._stream.device).wait_stream(self._stream)
+
+    def remove(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+
+class _NullContext:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False

@@ -113,6 +113,56 @@ def test_two_ranks_average_the_mixer_weight_gradients(tmp_path):
 
 
 # ---------------------------------------------------------------------------------------
+def _lm_worker(rank, store_path, out_path):
+    """The stacked-LM step on two ranks: bucketed, hook-driven gradient averaging must give the
+    single-process full-batch gradients, and the same as the flat one-bucket averaging."""
+    _init(rank, store_path)
+    from slinoss_b200.lm import SLinOSSLM, lm_stack_config
+    try:
+        torch.manual_seed(5)
+        model = SLinOSSLM(50, lm_stack_config(d_model=16, n_layers=2, d_state=4, d_head=8, ffn_expand=2.0))
+        model.extra_unused = torch.nn.Parameter(torch.ones(3))     # never gets a gradient
+        ids = torch.randint(0, 50, (4, 12))
+
+        def grads_of(batch, reducer=None):
+            model.zero_grad(set_to_none=True)
+            model.loss(batch).backward()
+            if reducer is not None:
+                reducer.finish()
+            return [None if p.grad is None else p.grad.clone() for p in model.parameters()]
+
+        full = grads_of(ids)                                   # single-process answer
+        (mine,) = shard.shard_batch([ids], dist.get_world_size(), rank)
+        flat = grads_of(mine)
+        shard.allreduce_mean_(flat)
+        # buckets of 2 KB: the 2-block model spreads over dozens of them
+        reducer = shard.GradBucketReducer(model.parameters(), bucket_bytes=2048)
+        bucketed = grads_of(mine, reducer)
+        again = grads_of(mine, reducer)                        # the reducer is reusable step after step
+        reducer.remove()
+        pairs = [(a, b, c, d) for a, b, c, d in zip(bucketed, flat, full, again) if c is not None]
+        errs_flat = [_rel(a.numpy(), b.numpy()) for a, b, _, _ in pairs]
+        errs_full = [_rel(a.numpy(), c.numpy()) for a, _, c, _ in pairs]
+        errs_again = [_rel(a.numpy(), d.numpy()) for a, _, _, d in pairs]
+        if rank == 0:
+            np.savez(out_path, errs_flat=np.array(errs_flat), errs_full=np.array(errs_full),
+                     errs_again=np.array(errs_again), n_buckets=len(reducer.buckets))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bucketed_gradient_allreduce_equals_flat_averaging_and_the_full_batch(tmp_path):
+    store, out = tmp_path / "store", tmp_path / "out.npz"
+    mp.spawn(_lm_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
+    r = np.load(out)
+    assert int(r["n_buckets"]) > 10
+    assert r["errs_flat"].max() <= 1e-6, r["errs_flat"]       # same sums, same order of ranks
+    assert r["errs_again"].max() == 0.0
+    # equal shards: the mean of the ranks' mean-losses is the full-batch mean-loss
+    assert r["errs_full"].max() <= 2e-5, r["errs_full"]
+
+
+# ---------------------------------------------------------------------------------------
 def test_shard_bounds_cover_the_units_once():
     for n in (0, 1, 7, 8, 33):
         for world in (1, 2, 3, 8):
