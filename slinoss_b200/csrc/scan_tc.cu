@@ -191,7 +191,7 @@ bool scan_tc_supported(const ScanDims& d, int io_dtype) {
 size_t scan_tc_fwd_workspace(const ScanDims&) { return 0; }
 namespace {
 struct TcBwdLayout {
-  size_t states, zfinal, dg, sterm, dkcd, anchor, total;
+  size_t states, zfinal, dg, sterm, dkcd, anchor, dbh, dch, total;
 };
 TcBwdLayout tc_bwd_layout(const ScanDims& d) {
   const size_t BH = (size_t)d.batch * d.heads, nC = (d.T + L - 1) / L;
@@ -204,6 +204,10 @@ TcBwdLayout tc_bwd_layout(const ScanDims& d) {
   o.sterm = take(BH * d.T * 8);
   o.dkcd = take(BH * d.T * 8);
   o.anchor = take(BH * nC * 8);
+  if (d.groups != d.heads) {   // per-head dB / dC (16-bit) before the reduction over the heads of a group
+    o.dbh = take(BH * d.T * 128 * 2);
+    o.dch = take(BH * d.T * 128 * 2);
+  }
   o.total = off;
   return o;
 }
@@ -266,7 +270,7 @@ int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, co
                 void* states_out, const ScanDims& d, int io_dtype, int y_dtype, void*, size_t,
                 cudaStream_t st) {
   // chunk states are only meaningful for the cases the tensor-core backward covers
-  if (Bprev || d.groups != d.heads) states_out = nullptr;
+  if (Bprev) states_out = nullptr;
   return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, states_out, d, io_dtype, y_dtype, st);
 }
 
@@ -279,23 +283,26 @@ static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
   return launch_status();
 }
 
-// Tensor-core backward: state pre-sweep, reverse sweep, scalar finish.  Cases it does not
-// cover (grouped B/C, carried B_prev/U_prev, dY of another dtype or absent) take the exact
-// float32 sweeps.
+// Tensor-core backward: state pre-sweep (unless the forward saved its chunk states), reverse sweep,
+// scalar finish and, for grouped B/C, the reduction of dB / dC over the heads of a group.  Cases it
+// does not cover (carried B_prev/U_prev, dY of another dtype or absent) take the exact float32 sweeps.
 int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                 const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
                 const float* zfinal_in, const void* dY,
                 const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC, float* dinit,
                 void* dBprev, void* dUprev, const ScanDims& d, int io_dtype, int dy_dtype, void* ws,
                 size_t ws_bytes, cudaStream_t st) {
-  if (d.groups != d.heads || Bprev || !dY || dy_dtype != io_dtype)
+  if (Bprev || !dY || dy_dtype != io_dtype)
     return scan_simt_bwd(U, M, K, B, C, z0, Bprev, Uprev, dY, dfinal, dU, dM, dK, dB, dC, dinit, dBprev,
                          dUprev, d, io_dtype, dy_dtype, ws, ws_bytes, st);
   const TcBwdLayout lay = tc_bwd_layout(d);
   if (!ws || ws_bytes < lay.total) return SL_ERR_WORKSPACE_TOO_SMALL;
   uint8_t* w = reinterpret_cast<uint8_t*>(ws);
   const bool bf = io_dtype == SL_BF16;
-  const uint64_t BH = (uint64_t)d.batch * d.heads;
+  const uint64_t BH = (uint64_t)d.batch * d.heads, BG = (uint64_t)d.batch * d.groups;
+  const bool grouped = d.groups != d.heads;
+  void* dBh = grouped ? (void*)(w + lay.dbh) : dB;   // where the sweep stores dB / dC (per head)
+  void* dCh = grouped ? (void*)(w + lay.dch) : dC;
   const int nC = (d.T + L - 1) / L;
   const float* zfinal = zfinal_in;
   const void* states = states_in;
@@ -308,22 +315,34 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
     states = w + lay.states;
   }
   TcBwdParams p{};
-  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
+  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BG, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BG, 64, bf) || !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
       !tc::make_tmap_3d(&p.tmZ, states, 128, (uint64_t)nC * 64, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmdU, dU, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdB, dB, 128, d.T, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmdC, dC, 128, d.T, BH, 64, bf))
+      !tc::make_tmap_3d(&p.tmdU, dU, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdB, dBh, 128, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmdC, dCh, 128, d.T, BH, 64, bf))
     return SL_ERR_LAUNCH_FAILED;
   p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal;
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
   p.dkcd = reinterpret_cast<float2*>(w + lay.dkcd); p.anchor = reinterpret_cast<float2*>(w + lay.anchor);
-  p.dinit = dinit; p.T = d.T; p.nchunks = nC;
+  p.dinit = dinit; p.T = d.T; p.nchunks = nC; p.heads = d.heads; p.groups = d.groups;
   p.wait_limit = wait_limit_clocks();
   int rc = SL_ERR_UNSUPPORTED;
   rc = bf ? launch_tc_bwd<__nv_bfloat16>(p, (int)BH, st) : launch_tc_bwd<__half>(p, (int)BH, st);
   if (rc != SL_OK) return rc;
   scan_tc_bwd_finish_kernel<<<dim3((unsigned)BH, (unsigned)((nC + 3) / 4)), 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
   note_launches(2);
+  if (grouped) {
+    const size_t pieces = BG * (size_t)d.T * 16;
+    const unsigned blocks = (unsigned)((pieces + 255) / 256);
+    if (bf)
+      scan_tc_group_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+          (const __nv_bfloat16*)dBh, (const __nv_bfloat16*)dCh, (__nv_bfloat16*)dB, (__nv_bfloat16*)dC, d.heads,
+          d.groups, d.T, pieces);
+    else
+      scan_tc_group_reduce_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)dBh, (const __half*)dCh, (__half*)dB,
+                                                                 (__half*)dC, d.heads, d.groups, d.T, pieces);
+    note_launches(1);
+  }
   return launch_status();
 }
 

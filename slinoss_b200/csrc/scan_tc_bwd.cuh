@@ -45,6 +45,7 @@ struct alignas(64) TcBwdParams {
   float2 *dg, *sterm, *dkcd, *anchor;   // per token / per chunk scalars (workspace)
   float* dinit;          // (BH, 64, 128) adjoint of the carried start state, or null
   int T, nchunks;
+  int heads, groups;     // B and C are shared by the heads of a group; dB / dC leave per head
   long long wait_limit;  // SM clocks a wait of the main loop may take before the kernel gives up
 };
 
@@ -81,6 +82,7 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
   const int rcol = tid & 15, rrow0 = tid >> 4;
   const int d0 = cg * ZC;                    // first column (inside the half) of this thread
   const int bh = blockIdx.x;
+  const int bg = (bh / p.heads) * p.groups + (bh % p.heads) / (p.heads / p.groups);   // row of B and C
   const int T = p.T, nC = p.nchunks;
   const float* Mb = p.M + (size_t)bh * T * 2;
   const float* Kb = p.K + (size_t)bh * T * 4;
@@ -113,10 +115,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_bwd_kernel(const __g
     uint64_t* bar = &bar_tma[it & 1];
     mbar_expect_tx(bar, B_STAGE);
     tma_load_3d(st, &p.tmU, bar, 0, c * L, bh);
-    tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bh);
-    tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bh);
-    tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bh);
-    tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bh);
+    tma_load_3d(st + TILE, &p.tmB, bar, 0, c * L, bg);
+    tma_load_3d(st + 2 * TILE, &p.tmB, bar, 64, c * L, bg);
+    tma_load_3d(st + 3 * TILE, &p.tmC, bar, 0, c * L, bg);
+    tma_load_3d(st + 4 * TILE, &p.tmC, bar, 64, c * L, bg);
     tma_load_3d(st + 5 * TILE, &p.tmdY, bar, 0, c * L, bh);
   };
   auto issue_loads_states = [&](int c, int it) {   // one thread
@@ -777,5 +779,36 @@ __global__ void __launch_bounds__(128) scan_tc_bwd_finish_kernel(const float* __
       *dMo = make_float2(dmr - (qr * dkpr + qi * dkpi), dmi - (qr * dkpi - qi * dkpr));
       *reinterpret_cast<float4*>(dK + (bh * T + t) * 4) = make_float4(dkpr, dkpi, gc.x + kd.x, gc.y + kd.y);
     }
+  }
+}
+
+// Grouped B / C: the sweep leaves dB and dC per head (16-bit); here the heads of a group are added up in
+// float32 and cast once (the reference reduces in float32 as well:
+// slinoss/ops/v2x2ssd/cute/kernels/bwd/__init__.py:548-563).  One thread per 16-byte piece of an output row.
+template <typename TIn>
+__global__ void __launch_bounds__(256) scan_tc_group_reduce_kernel(const TIn* __restrict__ per_head_b,
+                                                                   const TIn* __restrict__ per_head_c,
+                                                                   TIn* __restrict__ dB, TIn* __restrict__ dC,
+                                                                   int heads, int groups, int T, size_t pieces) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // piece index over (batch*groups, T, 16)
+  if (i >= pieces) return;
+  const int hpg = heads / groups;
+  const size_t row = i >> 4, piece = i & 15;
+  const size_t bgi = row / T, t = row % T;
+  const size_t b = bgi / groups, g = bgi % groups;
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const TIn* src = which ? per_head_c : per_head_b;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int hh = 0; hh < hpg; ++hh) {
+      const size_t bh = b * heads + g * hpg + hh;
+      float v[8];
+      load16<TIn>(src + (bh * T + t) * 128 + piece * 8, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+    store16<TIn>((which ? dC : dB) + (bgi * T + t) * 128 + piece * 8, acc);
   }
 }

@@ -272,14 +272,18 @@ def test_auto_path_prefers_tensor_cores_and_falls_back_for_float32():
     assert rel(Y, _oracle_fwd(case)[0]) <= 1e-5
 
 
+# (batch, heads, T, initial state, gradient of the final state, groups of B/C)
 TC_BWD_SHAPES = [
-    (1, 1, 64, False, False),
-    (1, 2, 1, True, True),
-    (2, 2, 63, False, True),
-    (1, 3, 65, True, True),
-    (2, 4, 200, True, False),
-    (1, 2, 333, False, False),
-    (1, 2, 1024, True, True),
+    (1, 1, 64, False, False, 1),
+    (1, 2, 1, True, True, 2),
+    (2, 2, 63, False, True, 2),
+    (1, 3, 65, True, True, 3),
+    (2, 4, 200, True, False, 4),
+    (1, 2, 333, False, False, 2),
+    (1, 2, 1024, True, True, 2),
+    (2, 4, 200, True, True, 2),      # grouped B/C: two heads share a row of B and C
+    (1, 4, 333, False, False, 1),    # one group for all heads
+    (1, 6, 130, True, True, 3),
 ]
 
 
@@ -287,8 +291,8 @@ TC_BWD_SHAPES = [
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_backward_tensor_core_path(shape, dtype):
     from slinoss_b200 import _C
-    b, h, T, init, with_dfinal = shape
-    case = make_scan_case(b, h, T, 64, 64, dtype=dtype, seed=11 * T + h, with_init=init)
+    b, h, T, init, with_dfinal, g = shape
+    case = make_scan_case(b, h, T, 64, 64, groups=g, dtype=dtype, seed=11 * T + h, with_init=init)
     c = case.to(DEV)
     names = ["U", "M", "K", "B", "C"] + (["initial_states"] if init else [])
     leaves = {k: getattr(c, k).clone().requires_grad_(True) for k in names}
