@@ -167,7 +167,7 @@ def scan_fwd(U, M, K, B, C, z0, B_prev, U_prev, *, chunk_size, y_dtype, want_fin
     Y = torch.empty((batch, heads, T, P), dtype=y_dtype, device=dev)
     states = None
     with torch.cuda.device(dev):
-        if save_states and B_prev is None:
+        if save_states:
             sbytes = lib().sl_workspace_bytes(WS_SCAN_STATES, batch, heads, groups, T, P, N,
                                               chunk_size, io, pcode)
             if sbytes:

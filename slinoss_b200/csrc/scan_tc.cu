@@ -191,8 +191,10 @@ bool scan_tc_supported(const ScanDims& d, int io_dtype) {
 size_t scan_tc_fwd_workspace(const ScanDims&) { return 0; }
 namespace {
 struct TcBwdLayout {
-  size_t states, zfinal, dg, sterm, dkcd, anchor, dbh, dch, total;
+  size_t states, zfinal, dg, sterm, dkcd, anchor, dbh, dch, dstart, dgb, total;
 };
+// (the carried-tap regions are always reserved: the workspace query does not know whether the call
+// will carry B_prev / U_prev)
 TcBwdLayout tc_bwd_layout(const ScanDims& d) {
   const size_t BH = (size_t)d.batch * d.heads, nC = (d.T + L - 1) / L;
   TcBwdLayout o{};
@@ -208,6 +210,8 @@ TcBwdLayout tc_bwd_layout(const ScanDims& d) {
     o.dbh = take(BH * d.T * 128 * 2);
     o.dch = take(BH * d.T * 128 * 2);
   }
+  o.dstart = take(BH * 64 * 128 * 4);   // adjoint of the start state when the caller wants no d_initial
+  o.dgb = take(BH * 8);                 // gradient of the pending tap's coefficient
   o.total = off;
   return o;
 }
@@ -269,8 +273,6 @@ int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, co
                 const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
                 void* states_out, const ScanDims& d, int io_dtype, int y_dtype, void*, size_t,
                 cudaStream_t st) {
-  // chunk states are only meaningful for the cases the tensor-core backward covers
-  if (Bprev) states_out = nullptr;
   return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, states_out, d, io_dtype, y_dtype, st);
 }
 
@@ -284,15 +286,15 @@ static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
 }
 
 // Tensor-core backward: state pre-sweep (unless the forward saved its chunk states), reverse sweep,
-// scalar finish and, for grouped B/C, the reduction of dB / dC over the heads of a group.  Cases it
-// does not cover (carried B_prev/U_prev, dY of another dtype or absent) take the exact float32 sweeps.
+// the boundary terms of carried B_prev / U_prev, scalar finish and, for grouped B/C, the reduction of
+// dB / dC over the heads of a group.  A dY of another dtype (or none) takes the exact float32 sweeps.
 int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                 const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
                 const float* zfinal_in, const void* dY,
                 const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC, float* dinit,
                 void* dBprev, void* dUprev, const ScanDims& d, int io_dtype, int dy_dtype, void* ws,
                 size_t ws_bytes, cudaStream_t st) {
-  if (Bprev || !dY || dy_dtype != io_dtype)
+  if (!dY || dy_dtype != io_dtype)
     return scan_simt_bwd(U, M, K, B, C, z0, Bprev, Uprev, dY, dfinal, dU, dM, dK, dB, dC, dinit, dBprev,
                          dUprev, d, io_dtype, dy_dtype, ws, ws_bytes, st);
   const TcBwdLayout lay = tc_bwd_layout(d);
@@ -308,7 +310,7 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   const void* states = states_in;
   if (!states || !zfinal) {   // nothing saved by the forward: recompute with the state pre-sweep
     float* zf = reinterpret_cast<float*>(w + lay.zfinal);
-    if (int e = scan_tc_fwd_impl(U, M, K, B, nullptr, z0, nullptr, nullptr, nullptr, zf, w + lay.states, d,
+    if (int e = scan_tc_fwd_impl(U, M, K, B, nullptr, z0, Bprev, Uprev, nullptr, zf, w + lay.states, d,
                                  io_dtype, SL_F32, st))
       return e;
     zfinal = zf;
@@ -324,12 +326,26 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal;
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
   p.dkcd = reinterpret_cast<float2*>(w + lay.dkcd); p.anchor = reinterpret_cast<float2*>(w + lay.anchor);
-  p.dinit = dinit; p.T = d.T; p.nchunks = nC; p.heads = d.heads; p.groups = d.groups;
+  // with carried taps the adjoint of the start state is needed even when the caller asks for no d_initial
+  float* dstart = dinit ? dinit : (Bprev ? reinterpret_cast<float*>(w + lay.dstart) : nullptr);
+  float2* dgb = Bprev ? reinterpret_cast<float2*>(w + lay.dgb) : nullptr;
+  p.dinit = dstart; p.T = d.T; p.nchunks = nC; p.heads = d.heads; p.groups = d.groups;
   p.wait_limit = wait_limit_clocks();
   int rc = SL_ERR_UNSUPPORTED;
   rc = bf ? launch_tc_bwd<__nv_bfloat16>(p, (int)BH, st) : launch_tc_bwd<__half>(p, (int)BH, st);
   if (rc != SL_OK) return rc;
-  scan_tc_bwd_finish_kernel<<<dim3((unsigned)BH, (unsigned)((nC + 3) / 4)), 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dM, dK, d.T, nC);
+  if (Bprev) {
+    if (bf)
+      scan_tc_bwd_boundary_kernel<__nv_bfloat16><<<(unsigned)BG, 128, 0, st>>>(
+          dstart, (const __nv_bfloat16*)Bprev, (const __nv_bfloat16*)Uprev, M, K, (__nv_bfloat16*)dBprev,
+          (__nv_bfloat16*)dUprev, dgb, d.heads, d.groups, d.T);
+    else
+      scan_tc_bwd_boundary_kernel<__half><<<(unsigned)BG, 128, 0, st>>>(dstart, (const __half*)Bprev,
+                                                                       (const __half*)Uprev, M, K, (__half*)dBprev,
+                                                                       (__half*)dUprev, dgb, d.heads, d.groups, d.T);
+    note_launches(1);
+  }
+  scan_tc_bwd_finish_kernel<<<dim3((unsigned)BH, (unsigned)((nC + 3) / 4)), 128, 0, st>>>(M, K, p.dg, p.sterm, p.dkcd, p.anchor, dgb, dM, dK, d.T, nC);
   note_launches(2);
   if (grouped) {
     const size_t pieces = BG * (size_t)d.T * 16;

@@ -739,6 +739,7 @@ __global__ void __launch_bounds__(128) scan_tc_bwd_finish_kernel(const float* __
                                                                  const float2* __restrict__ sterm,
                                                                  const float2* __restrict__ dkcd,
                                                                  const float2* __restrict__ anchor,
+                                                                 const float2* __restrict__ dg_boundary,
                                                                  float* __restrict__ dM,
                                                                  float* __restrict__ dK, int T, int nC) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -768,7 +769,10 @@ __global__ void __launch_bounds__(128) scan_tc_bwd_finish_kernel(const float* __
       const float den = mr * mr + mi * mi;
       const float4 k4 = *reinterpret_cast<const float4*>(K + (bh * T + t) * 4);
       float2 gp = make_float2(0.f, 0.f);
+      // the prev-tap of token t belongs to the merged coefficient of token t-1; for t = 0 that is the
+      // pending tap of the token before the sequence (carried B_prev / U_prev), if there is one
       if (t > 0) gp = dg[bh * T + t - 1];
+      else if (dg_boundary) gp = dg_boundary[bh];
       const float2 gc = dg[bh * T + t], kd = dkcd[bh * T + t];
       // x / conj(m) = x m / |m|^2
       const float dmr = (Sr * mr - Si * mi) / den, dmi = (Sr * mi + Si * mr) / den;
@@ -811,4 +815,70 @@ __global__ void __launch_bounds__(256) scan_tc_group_reduce_kernel(const TIn* __
     }
     store16<TIn>((which ? dC : dB) + (bgi * T + t) * 128 + piece * 8, acc);
   }
+}
+
+// Carried taps: the sequence starts from  W_{-1} = z_{-1} + u_prev (x) (X b_prev),  X = kp_0 / m_0.  Given
+// D = the adjoint of W_{-1} (what the sweep leaves as d_initial), per (batch, head):
+//     v[n]      = sum_p u_prev[p] D[p,n]
+//     dB_prev  += conj(X) v            (summed over the heads of a group, float32, cast once)
+//     dU_prev[p] = Re sum_n conj(X b_prev[n]) D[p,n]
+//     dX        = sum_n conj(b_prev[n]) v[n]     -> scan_tc_bwd_finish_kernel turns it into dkp_0 and its part of dm_0
+// (reference: slinoss/ops/v2x2ssd/cute/autograd.py:269-276 returns these as dB_prev / dU_prev).
+// One CTA of 128 threads per (batch, group); thread j owns the interleaved lane j of B_prev.
+template <typename TIn>
+__global__ void __launch_bounds__(128) scan_tc_bwd_boundary_kernel(const float* __restrict__ D,
+                                                                   const TIn* __restrict__ Bprev,
+                                                                   const TIn* __restrict__ Uprev,
+                                                                   const float* __restrict__ M,
+                                                                   const float* __restrict__ K,
+                                                                   TIn* __restrict__ dBprev, TIn* __restrict__ dUprev,
+                                                                   float2* __restrict__ dg_boundary, int heads,
+                                                                   int groups, int T) {
+  __shared__ float s_v[128], s_b[128], s_u[64], s_red[8];
+  const int bg = blockIdx.x, b = bg / groups, g = bg % groups, hpg = heads / groups;
+  const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
+  s_b[j] = to_f32(Bprev[(size_t)bg * 128 + j]);
+  float acc_db = 0.f;   // this lane of dB_prev, summed over the heads of the group
+  for (int hh = 0; hh < hpg; ++hh) {
+    const size_t bh = (size_t)b * heads + g * hpg + hh;
+    const float* Dh = D + bh * 64 * 128;
+    const float mr = M[bh * T * 2], mi = M[bh * T * 2 + 1];
+    const float kr = K[bh * T * 4], ki = K[bh * T * 4 + 1];
+    const float den = mr * mr + mi * mi;
+    const float xr = (kr * mr + ki * mi) / den, xi = (ki * mr - kr * mi) / den;   // X = kp_0 / m_0
+    __syncthreads();   // s_u, s_v of the previous head are no longer read
+    if (j < 64) s_u[j] = to_f32(Uprev[bh * 64 + j]);
+    __syncthreads();
+    float v = 0.f;
+#pragma unroll 8
+    for (int p = 0; p < 64; ++p) v += s_u[p] * Dh[p * 128 + j];
+    s_v[j] = v;
+    __syncthreads();
+    // conj(X) v on the (re, im) pair this lane belongs to
+    const float vr = s_v[j & ~1], vi = s_v[j | 1];
+    acc_db += (j & 1) ? (xr * vi - xi * vr) : (xr * vr + xi * vi);
+    // dX = sum_n conj(b[n]) v[n]: lane pairs contribute (re: br vr + bi vi, im: br vi - bi vr)
+    float cr = 0.f, ci = 0.f;
+    if (!(j & 1)) {
+      const float br = s_b[j], bi = s_b[j + 1];
+      cr = br * vr + bi * vi;
+      ci = br * vi - bi * vr;
+    }
+    cr = warp_sum(cr); ci = warp_sum(ci);
+    if (lane == 0) { s_red[2 * warp] = cr; s_red[2 * warp + 1] = ci; }
+    // dU_prev[p] = Re sum_n conj(X b[n]) D[p,n]   (threads 0..63: one row each)
+    if (j < 64 && dUprev) {
+      float du = 0.f;
+      for (int n = 0; n < 64; ++n) {
+        const float yr = xr * s_b[2 * n] - xi * s_b[2 * n + 1], yi = xr * s_b[2 * n + 1] + xi * s_b[2 * n];   // X b
+        const float2 d2 = *reinterpret_cast<const float2*>(Dh + j * 128 + 2 * n);
+        du += yr * d2.x + yi * d2.y;
+      }
+      dUprev[bh * 64 + j] = from_f32<TIn>(du);
+    }
+    __syncthreads();
+    if (j == 0)
+      dg_boundary[bh] = make_float2(s_red[0] + s_red[2] + s_red[4] + s_red[6], s_red[1] + s_red[3] + s_red[5] + s_red[7]);
+  }
+  if (dBprev) dBprev[(size_t)bg * 128 + j] = from_f32<TIn>(acc_db);
 }

@@ -281,7 +281,19 @@ def measure_scan(iters, dev):
                               y_dtype=torch.bfloat16, want_final=False, save_states=True)
     _, fin, st = fwd()
     bht = 8 * 16 * 4096
-    return [report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name),
+    # the same size with grouped B/C (4 heads per group) and with carried taps + carried state:
+    # what segmented (streaming-state) training and bc_groups < heads models run
+    g = make_scan_case(8, 16, 4096, 64, 64, groups=4, dtype=torch.bfloat16, seed=1, streaming=True,
+                       with_init=True).to(dev)
+    _, gfin, gst = _C.scan_fwd(g.U, g.M, g.K, g.B, g.C, g.initial_states, g.B_prev, g.U_prev, chunk_size=64,
+                               y_dtype=torch.bfloat16, want_final=True, save_states=True)
+    gname = name + ", 4 groups of B/C, carried state and taps"
+    gbytes = bht * (1456 - 2 * 256 + 2 * 64) + 2 * 8 * 16 * 64 * 128 * 4   # B, C, dB, dC shrink 4x; + z0, d_initial
+    grouped = [report("sl_v2x2ssd_bwd (grouped B/C, carried state and taps; saved chunk states)",
+                      time_ms(lambda: _C.scan_bwd(g.U, g.M, g.K, g.B, g.C, g.initial_states, g.B_prev, g.U_prev,
+                                                  g.dY, None, chunk_size=64, saved=(gst, gfin)), iters),
+                      gbytes, gname)]
+    return grouped + [report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name),
             report("sl_v2x2ssd_bwd (saved chunk states)",
                    time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
                                                chunk_size=64, saved=(st, fin)), iters), bht * 1456, name),

@@ -272,18 +272,22 @@ def test_auto_path_prefers_tensor_cores_and_falls_back_for_float32():
     assert rel(Y, _oracle_fwd(case)[0]) <= 1e-5
 
 
-# (batch, heads, T, initial state, gradient of the final state, groups of B/C)
+# (batch, heads, T, initial state, gradient of the final state, groups of B/C, carried B_prev / U_prev)
 TC_BWD_SHAPES = [
-    (1, 1, 64, False, False, 1),
-    (1, 2, 1, True, True, 2),
-    (2, 2, 63, False, True, 2),
-    (1, 3, 65, True, True, 3),
-    (2, 4, 200, True, False, 4),
-    (1, 2, 333, False, False, 2),
-    (1, 2, 1024, True, True, 2),
-    (2, 4, 200, True, True, 2),      # grouped B/C: two heads share a row of B and C
-    (1, 4, 333, False, False, 1),    # one group for all heads
-    (1, 6, 130, True, True, 3),
+    (1, 1, 64, False, False, 1, False),
+    (1, 2, 1, True, True, 2, False),
+    (2, 2, 63, False, True, 2, False),
+    (1, 3, 65, True, True, 3, False),
+    (2, 4, 200, True, False, 4, False),
+    (1, 2, 333, False, False, 2, False),
+    (1, 2, 1024, True, True, 2, False),
+    (2, 4, 200, True, True, 2, False),      # grouped B/C: two heads share a row of B and C
+    (1, 4, 333, False, False, 1, False),    # one group for all heads
+    (1, 6, 130, True, True, 3, False),
+    (1, 2, 1, True, True, 2, True),         # carried taps: the token before the sequence
+    (2, 2, 65, False, False, 2, True),
+    (2, 4, 200, True, True, 2, True),       # ... grouped as well
+    (1, 3, 333, True, False, 1, True),
 ]
 
 
@@ -291,13 +295,16 @@ TC_BWD_SHAPES = [
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_backward_tensor_core_path(shape, dtype):
     from slinoss_b200 import _C
-    b, h, T, init, with_dfinal, g = shape
-    case = make_scan_case(b, h, T, 64, 64, groups=g, dtype=dtype, seed=11 * T + h, with_init=init)
+    b, h, T, init, with_dfinal, g, streaming = shape
+    case = make_scan_case(b, h, T, 64, 64, groups=g, dtype=dtype, seed=11 * T + h, with_init=init,
+                          streaming=streaming)
     c = case.to(DEV)
-    names = ["U", "M", "K", "B", "C"] + (["initial_states"] if init else [])
+    names = ["U", "M", "K", "B", "C"] + (["initial_states"] if init else []) \
+        + (["B_prev", "U_prev"] if streaming else [])
     leaves = {k: getattr(c, k).clone().requires_grad_(True) for k in names}
     out = v2x2ssd(leaves["U"], leaves["M"], leaves["K"], leaves["B"], leaves["C"], chunk_size=64,
-                  initial_states=leaves.get("initial_states"), path="tc")
+                  initial_states=leaves.get("initial_states"), B_prev=leaves.get("B_prev"),
+                  U_prev=leaves.get("U_prev"), path="tc")
     gen = torch.Generator().manual_seed(5)
     d_final = torch.randn(out[1].shape, generator=gen).to(dtype) if with_dfinal else None
     outs, cots = [out[0]], [c.dY]
@@ -306,10 +313,42 @@ def test_backward_tensor_core_path(shape, dtype):
     grads = torch.autograd.grad(outs, list(leaves.values()), cots)
     assert _C.device_status() == 0
     want = scan_np.v2x2ssd_bwd(*[n64(t) for t in case.tensors()], n64(case.dY),
-                               d_final_state=n64(d_final), initial_states=n64(case.initial_states))
+                               d_final_state=n64(d_final), initial_states=n64(case.initial_states),
+                               B_prev=n64(case.B_prev), U_prev=n64(case.U_prev))
     for name, gr in zip(names, grads):
         assert torch.isfinite(gr).all(), name
         assert rel(gr, want[name]) <= 2e-2, (name, rel(gr, want[name]))
+
+
+def test_segmented_training_on_the_tensor_core_path_matches_the_single_pass():
+    """Two segments chained through (final_state, B_last, U_last): the gradients that flow back through
+    the carried state and the carried taps must add up to those of the single pass."""
+    case = make_scan_case(2, 4, 333, 64, 64, groups=2, dtype=torch.bfloat16, seed=17).to(DEV)
+    cut = 150
+
+    def run(segmented):
+        lv = [t.clone().requires_grad_(True) for t in case.tensors()]
+        if not segmented:
+            Y = v2x2ssd_cute(*lv, chunk_size=64, path="tc")
+        else:
+            a = [t[:, :, :cut].contiguous() for t in lv]
+            b = [t[:, :, cut:].contiguous() for t in lv]
+            Ya, fa, ba, ua = v2x2ssd_cute(*a, chunk_size=64, path="tc", return_state=True,
+                                          output_dtype=torch.float32)
+            Yb = v2x2ssd_cute(*b, chunk_size=64, path="tc", initial_states=fa,
+                              B_prev=ba.to(torch.bfloat16), U_prev=ua.to(torch.bfloat16),
+                              output_dtype=torch.float32)
+            Y = torch.cat([Ya, Yb], 2)
+        return Y, torch.autograd.grad(Y, lv, case.dY.to(Y.dtype))
+
+    Yf, gf = run(False)
+    Ys, gs = run(True)
+    assert rel(Ys, Yf) <= 2e-2
+    for name, a, b in zip("UMKBC", gs, gf):
+        assert rel(a, b) <= 2e-2, (name, rel(a, b))
+    want = scan_np.v2x2ssd_bwd(*[n64(t) for t in case.tensors()], n64(case.dY))
+    for name, a in zip("UMKBC", gs):
+        assert rel(a, want[name]) <= 2e-2, (name, rel(a, want[name]))
 
 
 def test_backward_tensor_core_agrees_with_exact_path_at_strong_decay():
