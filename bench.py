@@ -400,7 +400,8 @@ def main():
         measure.PRINT_LINES = False
         bshare = max(1, 8 // world)
         others = {
-            "config3_decode": measure.measure_decode_sequence(0, dev, steps=1024, batch=256),
+            "config3_decode": measure.measure_decode_sequence(0, dev, steps=1024, batch=256)
+                              + measure.measure_mixer_step(20, dev, batch=256),
             "config2_mixer": measure.measure_mixer(12, dev, batch=bshare)
                              + measure.measure_scanprep(10, dev, batch=bshare)
                              + measure.measure_tail(10, dev, batch=bshare),

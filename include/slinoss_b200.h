@@ -273,6 +273,39 @@ SL_API int sl_mixer_tail_bwd(const void* Y, const void* gate, int64_t gate_row_s
                       void* d_skip_input, float* d_d_skip, float* d_norm_weight, int batch,
                       int heads, int T, int P, int io_dtype, void* stream);
 
+/*
+ * One decode token of the whole mixer between in_proj and out_proj, in one launch: causal conv
+ * update + bias + SiLU, scan preparation of the token, state update and read-out, skip, gate and
+ * RMSNorm.  Replaces the per-token path of SLinOSSMixer.step: run_reference_decode_step
+ * (slinoss/ops/mixer/step.py:201-258, 323-429; a chain of torch ops) and mixer_decode_step_cute
+ * (slinoss/ops/v2x2ssd/cute/step.py:224-627; fused, but unreachable for mixers with d_skip).
+ *   gate, value (batch, heads*P) : io_dtype, row strides in elements (column slices of the in_proj
+ *          output are passed where they lie)
+ *   params (batch, 3*heads), bc (batch, groups, 4, N) : io_dtype, dense
+ *   conv_weight (heads*P, d_conv), conv_bias (heads*P) : io_dtype; conv_weight == NULL skips the conv
+ *   conv_state (batch, heads*P, d_conv-1) : io_dtype, the carried inputs, UPDATED IN PLACE
+ *   dt_bias ... theta_sign, d_skip (heads) float32 (d_skip may be NULL);  norm_weight (heads*P) io_dtype
+ *   state (batch, heads, P, 2N) float32, UPDATED IN PLACE
+ *   b_prev_in (batch, groups, 2N) io_dtype or NULL (zeros): the previous token's b
+ *   b_prev_out (batch, groups, 2N): this token's b; must not alias b_prev_in (the heads of a group
+ *          read one while one of them writes the other)
+ *   u_prev (batch, heads, P) : io_dtype, the previous token's u, UPDATED IN PLACE
+ *   normed (batch, heads*P) : io_dtype, dense - the input of out_proj
+ *   workspace: sl_mixer_decode_step_workspace_bytes(batch, heads, P) bytes that are ZERO before the
+ *          first call; every call leaves them zero again (calls on one workspace must not overlap).
+ */
+SL_API size_t sl_mixer_decode_step_workspace_bytes(int batch, int heads, int P);
+SL_API int sl_mixer_decode_step(const void* gate, int64_t gate_row_stride, const void* value,
+                                int64_t value_row_stride, const void* params, const void* bc,
+                                const void* conv_weight, const void* conv_bias, void* conv_state,
+                                int d_conv, const float* dt_bias, const float* alpha_bias,
+                                const float* theta_mod_bias, const float* theta_bias,
+                                const float* theta_sign, const sl_scanprep_config* cfg,
+                                const float* d_skip, const void* norm_weight, float norm_eps,
+                                float* state, const void* b_prev_in, void* b_prev_out, void* u_prev,
+                                void* normed, void* workspace, size_t workspace_bytes, int batch,
+                                int heads, int groups, int P, int N, int io_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

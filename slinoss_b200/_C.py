@@ -58,6 +58,10 @@ _PROTOTYPES = {
                                      ctypes.POINTER(ScanPrepConfig), _P, c_int64, c_int64, c_int64,
                                      _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]
                              + [c_int] * 7 + [_P]),
+    "sl_mixer_decode_step_workspace_bytes": (c_size_t, [c_int] * 3),
+    "sl_mixer_decode_step": (c_int, [_P, c_int64, _P, c_int64, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P,
+                                     ctypes.POINTER(ScanPrepConfig), _P, _P, c_float, _P, _P, _P, _P, _P, _P,
+                                     c_size_t] + [c_int] * 6 + [_P]),
     "sl_mixer_tail_fwd": (c_int, [_P, _P, c_int64, _P, _P, _P, c_float, _P] + [c_int] * 5 + [_P]),
     "sl_mixer_tail_bwd": (c_int, [_P, _P, c_int64, _P, _P, _P, c_float, _P, _P, _P, _P, _P, _P]
                           + [c_int] * 5 + [_P]),
@@ -415,3 +419,37 @@ def mixer_tail_bwd(Y, gate, skip, d_skip, norm_weight, eps, d_normed):
             float(eps), _ptr(d_normed), _ptr(dY), _ptr(d_gate), _ptr(d_skip_in), _ptr(d_d_skip),
             _ptr(d_w), batch, heads, T, P, dtype_code(Y.dtype), _stream(dev)), "sl_mixer_tail_bwd")
     return dY, d_gate, d_skip_in, d_d_skip, d_w
+
+
+# ---------------------------------------------------------------------------------
+# fused decode step of the mixer
+# ---------------------------------------------------------------------------------
+def mixer_decode_workspace(batch, heads, P, dev) -> torch.Tensor:
+    """The zero-initialised scratch ``mixer_decode_step`` needs (allocate once, reuse every token)."""
+    n = lib().sl_mixer_decode_step_workspace_bytes(batch, heads, P)
+    return torch.zeros(n, dtype=torch.uint8, device=dev)
+
+
+def mixer_decode_step(gate, value, params, bc, conv_weight, conv_bias, conv_state, biases, cfg, d_skip,
+                      norm_weight, eps, state, b_prev_in, b_prev_out, u_prev, workspace, *, heads, P,
+                      normed=None):
+    """Launch ``sl_mixer_decode_step``.  ``gate`` and ``value`` are (batch, heads*P) views with a row
+    stride; ``conv_state``, ``state`` and ``u_prev`` are updated in place; ``b_prev_out`` receives this
+    token's b.  Returns ``normed`` (batch, heads*P)."""
+    dev = require_cuda(gate, value, params, bc, conv_weight, conv_bias, conv_state, d_skip, norm_weight, state,
+                       b_prev_in, b_prev_out, u_prev, workspace)
+    batch = int(gate.shape[0])
+    groups, N = int(bc.shape[-3]), int(bc.shape[-1])
+    if gate.stride(-1) != 1 or value.stride(-1) != 1:
+        raise ValueError("gate and value must have dense channels (row-strided views are fine).")
+    if normed is None:
+        normed = torch.empty((batch, heads * P), dtype=gate.dtype, device=dev)
+    d_conv = 1 if conv_weight is None else int(conv_weight.shape[1])
+    with torch.cuda.device(dev):
+        check(lib().sl_mixer_decode_step(
+            _ptr(gate), int(gate.stride(0)), _ptr(value), int(value.stride(0)), _ptr(params), _ptr(bc),
+            _ptr(conv_weight), _ptr(conv_bias), _ptr(conv_state), d_conv, *[_ptr(b) for b in biases],
+            ctypes.byref(cfg), _ptr(d_skip), _ptr(norm_weight), float(eps), _ptr(state), _ptr(b_prev_in),
+            _ptr(b_prev_out), _ptr(u_prev), _ptr(normed), _ptr(workspace), workspace.numel(), batch, heads,
+            groups, P, N, dtype_code(gate.dtype), _stream(dev)), "sl_mixer_decode_step")
+    return normed

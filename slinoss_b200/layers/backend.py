@@ -120,12 +120,44 @@ class B200ScanBackend:
 
 
 class B200MixerDecodeBackend:
-    """Per-token decode: scan preparation of one token + the decode kernel + the gated
-    RMSNorm, all on CUDA kernels (d_skip is supported, unlike the reference's fast path,
-    slinoss/ops/mixer/step.py:107-122)."""
+    """Per-token decode on CUDA kernels (d_skip is supported, unlike the reference's fast path,
+    slinoss/ops/mixer/step.py:107-122).
+
+    ``fused_step`` is the one-launch path ``SLinOSSMixer.step`` takes outside autograd: conv update,
+    scan preparation of the token, state update, skip, gate and RMSNorm in ``sl_mixer_decode_step``,
+    with the mixer state updated in place.  ``__call__`` is the Protocol entry
+    (slinoss/layers/backend.py:220-237): it takes the already convolved value and runs scan
+    preparation, the decode kernel and the gated RMSNorm as separate launches."""
+
+    fused = True
 
     def supports(self, owner, *, batch_size, device, dtype) -> bool:
         return device.type == "cuda" and dtype in (torch.float32, torch.bfloat16, torch.float16)
+
+    def fused_step(self, owner, gate, value_raw, params, bc, state, *, normed=None, workspace=None):
+        """``gate, value_raw (batch, d_inner)`` (row-strided views are fine), ``params (batch, 3H)``,
+        ``bc (batch, G*4*N)``; ``state`` is the mixer's decode state (conv window, float32 scan
+        state, previous b and u), all of it updated in place.  Returns ``normed (batch, d_inner)``."""
+        from .. import _C
+        batch = int(gate.shape[0])
+        sp, scan = owner.scanprep, state.scan
+        dev, dt = gate.device, gate.dtype
+        if workspace is None:
+            workspace = getattr(state, "_step_workspace", None)
+            if workspace is None or workspace.device != dev:
+                workspace = _C.mixer_decode_workspace(batch, owner.n_heads, owner.d_head, dev)
+                state._step_workspace = workspace
+        biases = tuple(getattr(sp, k).detach().float().contiguous()
+                       for k in ("dt_bias", "alpha_bias", "theta_mod_bias", "theta_bias", "theta_sign"))
+        b_out = torch.empty_like(scan.b_prev)
+        normed = _C.mixer_decode_step(
+            gate, value_raw, params.contiguous(), bc.contiguous().view(batch, owner.bc_groups, 4, owner.d_state),
+            owner.dw_weight.detach().to(dt).contiguous(), owner.dw_bias.detach().to(dt).contiguous(),
+            state.conv, biases, _C.make_config(sp), owner.d_skip.detach().float().contiguous(),
+            owner.out_norm.weight.detach().to(dt).contiguous(), owner.out_norm.eps, scan.state, scan.b_prev,
+            b_out, scan.u_prev, workspace, heads=owner.n_heads, P=owner.d_head, normed=normed)
+        scan.b_prev = b_out
+        return normed
 
     def __call__(self, owner, inputs: MixerDecodeInputs, state: ScanState):
         from ..ops.mixer import mixer_gated_norm

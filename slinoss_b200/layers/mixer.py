@@ -170,10 +170,25 @@ class SLinOSSMixer(nn.Module):
             y = self._decode_token(token, nxt).unsqueeze(1)
         return (y[:, 0, :], nxt) if squeeze else (y, nxt)
 
+    def _fused_decode_ready(self, state: SLinOSSMixerState, token: torch.Tensor) -> bool:
+        """The one-launch decode step needs a complete in-place state in the kernel's layouts."""
+        sc = state.scan
+        return (getattr(self.decode_backend, "fused", False)
+                and self.decode_backend.supports(self, batch_size=int(token.shape[0]), device=token.device,
+                                                 dtype=token.dtype)
+                and self.d_conv <= 4 and state.conv is not None and state.conv.dtype == token.dtype
+                and state.conv.is_contiguous() and sc.state is not None and sc.state.dtype == torch.float32
+                and sc.state.is_contiguous() and sc.b_prev is not None and sc.u_prev is not None
+                and sc.b_prev.dtype == token.dtype and sc.u_prev.dtype == token.dtype
+                and sc.b_prev.is_contiguous() and sc.u_prev.is_contiguous())
+
     def _decode_token(self, token: torch.Tensor, state: SLinOSSMixerState) -> torch.Tensor:
         batch = int(token.shape[0])
         gate, value_proj, params, bc = split_mixer_projection(
             token, self.in_proj.weight, d_inner=self.d_inner, param_proj_dim=self.param_proj_dim)
+        if self._fused_decode_ready(state, token):
+            normed = self.decode_backend.fused_step(self, gate, value_proj, params, bc, state)
+            return self.out_proj(normed)
         value, conv_state = self.cconv_backend(self, value_proj.unsqueeze(1), state.conv)
         state.conv = conv_state if state.conv is None or state.conv.shape != conv_state.shape \
             else state.conv.copy_(conv_state)

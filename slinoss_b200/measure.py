@@ -1,6 +1,6 @@
 """Device timing of every C-ABI entry point at the sizes of the reference's configs.
 
-    python -m slinoss_b200.measure [--what decode,decode_sequence,scanprep,tail,mixer,scan] [--iters 20]
+    python -m slinoss_b200.measure [--what decode,decode_sequence,mixer_step,scanprep,tail,mixer,scan] [--iters 20]
 
 Prints one JSON line per measured call: CUDA-event time (mean of ``iters`` back-to-back
 launches after warm-up, on the launching stream), the call's algorithmic bytes (every
@@ -271,6 +271,40 @@ def measure_mixer(iters, dev, batch=8):
                   "config": f"x ({batch}, 2048, 1024) bf16, d_inner 2048, 32 heads x 64, N 64, d_conv 4"})]
 
 
+def measure_mixer_step(iters, dev, batch=256):
+    """One decode token of the whole mixer (d_model 1024, 32 heads x 64, N 64, conv width 4, bf16) at
+    the decode configuration's batch: in_proj, the one-launch fused step, out_proj.  Eager through
+    ``SLinOSSMixer.step`` and replayed from the CUDA-graph engine; the traffic that bounds it is the
+    float32 state read and written once (2 x 268 MB at batch 256)."""
+    import slinoss_b200 as sb
+    from .engine import MixerDecodeEngine
+    torch.manual_seed(0)
+    m = sb.SLinOSSMixer(1024, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(dev).to(torch.bfloat16)
+    x = torch.randn(batch, 1024, device=dev, dtype=torch.bfloat16)
+    algo = 2 * batch * 32 * 64 * 128 * 4
+    cfg = f"SLinOSSMixer.step: batch {batch}, d_model 1024, 32 heads x 64, N 64, d_conv 4, bf16"
+    lines = []
+    with torch.no_grad():
+        _, state = m.step(x, None)
+
+        def eager():
+            m.step(x, state, inplace=True)
+
+        ms = time_ms(eager, max(iters, 20))
+        lines.append(report("SLinOSSMixer.step, eager (in_proj + fused step + out_proj, per token)", ms, algo, cfg,
+                            {"us_per_step": ms * 1e3, "tokens_per_s": batch / (ms * 1e-3)}))
+        eng = MixerDecodeEngine(m, batch)
+        ms = time_ms(lambda: eng.step(x), max(iters, 20))
+        lines.append(report("MixerDecodeEngine.step, CUDA-graph replay (per token)", ms, algo, cfg,
+                            {"us_per_step": ms * 1e3, "tokens_per_s": batch / (ms * 1e-3)}))
+        m.decode_backend.fused = False
+        _, state2 = m.step(x, None)
+        ms = time_ms(lambda: m.step(x, state2, inplace=True), max(iters, 20))
+        lines.append(report("SLinOSSMixer.step with separate launches (conv, scan preparation, decode, tail)", ms, algo,
+                            cfg, {"us_per_step": ms * 1e3, "tokens_per_s": batch / (ms * 1e-3)}))
+    return lines
+
+
 def measure_scan(iters, dev):
     """Config 1 scan forward / backward through the C ABI (the figures bench.py headlines)."""
     from . import _C
@@ -302,13 +336,13 @@ def measure_scan(iters, dev):
                                                chunk_size=64), iters), bht * 1456, name)]
 
 
-WHAT = {"decode": measure_decode, "decode_sequence": measure_decode_sequence,
+WHAT = {"decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
         "scanprep": measure_scanprep, "tail": measure_tail, "mixer": measure_mixer, "scan": measure_scan}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="decode,decode_sequence,scanprep,tail,mixer,scan")
+    ap.add_argument("--what", default="decode,decode_sequence,mixer_step,scanprep,tail,mixer,scan")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():

@@ -1,6 +1,8 @@
 """Parity of the CUDA scan-preparation / conv / tail kernels and of the whole mixer
 with the oracle and with golden vectors of the reference (through the C ABI)."""
 
+from pathlib import Path
+
 import numpy as np
 import pytest
 import torch
@@ -259,6 +261,56 @@ def test_stack_against_reference_golden(golden):
             y, state = stack.step(x[:, t], state)
             ys.append(y)
         assert rel(torch.stack(ys, 1), g["out_steps"]) <= 5e-5
+
+
+def test_fused_decode_step_and_graph_engine_follow_the_forward_pass():
+    """``SLinOSSMixer.step`` (one launch per token between the two GEMMs) and the CUDA-graph engine
+    against the reference's own step outputs and against a forward pass over the same tokens."""
+    from slinoss_b200.engine import MixerDecodeEngine
+    g = dict(np.load(Path(__file__).resolve().parent / "golden" / "mixer.npz"))
+    m = _load_mixer(g)
+    x = torch.from_numpy(g["x"]).to(DEV)
+    with torch.no_grad():
+        full = m(x)
+        state, ys = None, []
+        for t in range(x.shape[1]):
+            y, state = m.step(x[:, t], state)
+            ys.append(y)
+        ys = torch.stack(ys, 1)
+        assert rel(ys[:, :3], g["out_steps"]) <= 5e-5          # the reference's decode steps
+        assert rel(ys, full) <= 5e-5                            # token by token == forward pass
+        for use_graph in (False, True):
+            eng = MixerDecodeEngine(m, x.shape[0], use_graph=use_graph)
+            for rep in range(2):                                # reset() brings the engine back to token 0
+                eng.reset()
+                es = torch.stack([eng.step(x[:, t]).clone() for t in range(x.shape[1])], 1)
+                assert rel(es, full) <= 5e-5, (use_graph, rep, rel(es, full))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_decode_step_at_the_benchmark_shape(dtype):
+    """d_model 1024, 32 heads x 64, N 64 (the N = 64 fast path of the state update), bf16 and float32:
+    the one-launch step against the separate-kernel backend call on the same state."""
+    torch.manual_seed(3)
+    m = sb.SLinOSSMixer(1024, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(DEV).to(dtype)
+    x = torch.randn(3, 7, 1024, device=DEV, dtype=dtype)
+    with torch.no_grad():
+        full = m(x)
+        state, ys = None, []
+        for t in range(7):
+            y, state = m.step(x[:, t], state)
+            ys.append(y)
+        assert rel(torch.stack(ys, 1), full) <= (5e-5 if dtype == torch.float32 else 2e-2)
+        # the Protocol path (separate launches) from the same starting state gives the same token
+        m2 = sb.SLinOSSMixer(1024, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(DEV).to(dtype)
+        m2.load_state_dict(m.state_dict())
+        m2.decode_backend.fused = False
+        state2, ys2 = None, []
+        for t in range(7):
+            y, state2 = m2.step(x[:, t], state2)
+            ys2.append(y)
+        assert rel(torch.stack(ys2, 1), torch.stack(ys, 1)) <= (1e-5 if dtype == torch.float32 else 2e-2)
+        assert rel(state2.scan.state, state.scan.state) <= (1e-5 if dtype == torch.float32 else 2e-2)
 
 
 def test_mixer_bf16_close_to_float32():
