@@ -49,7 +49,7 @@ struct StepParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256) mixer_step_kernel(StepParams p) {
+__global__ void __launch_bounds__(256, 4) mixer_step_kernel(StepParams p) {
   extern __shared__ __align__(16) float smem[];
   const int D = 2 * p.N, C = p.H * p.P;
   float* s_bp = smem;            // kp * b_prev
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) mixer_step_kernel(StepParams p) {
   // ---- B. transition and taps of this head (one thread; float64 inside) ------------------------
   if (tid == blockDim.x - 1) {
     const T* pr = reinterpret_cast<const T*>(p.params) + (size_t)b * 3 * p.H + 3 * h;
-    const CoeffOut o = coeff_eval(to_f32(pr[0]) + p.dt_bias[h], to_f32(pr[1]) + p.alpha_bias[h],
+    const CoeffOut o = coeff_eval<false>(to_f32(pr[0]) + p.dt_bias[h], to_f32(pr[1]) + p.alpha_bias[h],
                                   to_f32(pr[2]) + p.theta_mod_bias[h], p.theta_bias[h], p.theta_sign[h], p.cfg);
     const zc kp = {o.dt * o.k2.re, o.dt * o.k2.im};
     s_coef[0] = (float)o.rho.re; s_coef[1] = (float)o.rho.im;

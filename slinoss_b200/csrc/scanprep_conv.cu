@@ -753,7 +753,7 @@ __global__ void __launch_bounds__(128) coeff_fwd_kernel(CoeffParams p) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y, b = blockIdx.z;
   if (t >= p.T) return;
   const T* pr = reinterpret_cast<const T*>(p.params) + ((size_t)b * p.T + t) * 3 * p.H + 3 * h;
-  const CoeffOut o = coeff_eval(to_f32(pr[0]) + p.dt_bias[h], to_f32(pr[1]) + p.alpha_bias[h],
+  const CoeffOut o = coeff_eval<false>(to_f32(pr[0]) + p.dt_bias[h], to_f32(pr[1]) + p.alpha_bias[h],
                                 to_f32(pr[2]) + p.theta_mod_bias[h], p.theta_bias[h],
                                 p.theta_sign[h], p.cfg);
   const size_t i = ((size_t)b * p.H + h) * p.T + t;

@@ -33,6 +33,9 @@ __device__ __forceinline__ float wrap_angle_f(float theta) {
   return r - pi;
 }
 
+// WITH_DERIVS = false leaves the derivative fields (dsg_*, tanh2, dk1, dk2) unset: the forward kernels
+// do not pay for the backward's float64 exponentials and quotients.
+template <bool WITH_DERIVS = true>
 __device__ __forceinline__ CoeffOut coeff_eval(float p0, float p1, float p2, float th_bias,
                                                float th_sign, const sl_scanprep_config& c) {
   CoeffOut o;
@@ -50,10 +53,12 @@ __device__ __forceinline__ CoeffOut coeff_eval(float p0, float p1, float p2, flo
   o.dt = dt; o.r = r; o.theta = theta; o.ea = ea;
   // sigma'(x) = sigma(x) sigma(-x) = e / (1 + e)^2 with e = exp(-|x|): exact even where
   // the sigmoid saturates (1 - sigma(x) would cancel in float32)
-  auto dsig = [](double x) { const double e = exp(-fabs(x)); return e / ((1.0 + e) * (1.0 + e)); };
-  o.dsg_dt = dsig((double)p0); o.dsg_al = dsig((double)p1);
-  o.dsg_thu = dsig((double)th_bias + (double)c.theta_mod_scale * (double)th);
-  o.tanh2 = (double)th * th;
+  if constexpr (WITH_DERIVS) {
+    auto dsig = [](double x) { const double e = exp(-fabs(x)); return e / ((1.0 + e) * (1.0 + e)); };
+    o.dsg_dt = dsig((double)p0); o.dsg_al = dsig((double)p1);
+    o.dsg_thu = dsig((double)th_bias + (double)c.theta_mod_scale * (double)th);
+    o.tanh2 = (double)th * th;
+  }
   const double a = log((double)r);
   double sn, cs;
   sincos((double)theta, &sn, &cs);
@@ -66,8 +71,10 @@ __device__ __forceinline__ CoeffOut coeff_eval(float p0, float p1, float p2, flo
     const zc z2 = zmul(z, z), z3 = zmul(z2, z);
     o.k1 = {1.0 + 0.5 * z.re + z2.re / 6.0 + z3.re / 24.0, 0.5 * z.im + z2.im / 6.0 + z3.im / 24.0};
     o.k2 = {0.5 + z.re / 3.0 + z2.re / 8.0 + z3.re / 30.0, z.im / 3.0 + z2.im / 8.0 + z3.im / 30.0};
-    o.dk1 = {0.5 + z.re / 3.0 + z2.re / 8.0, z.im / 3.0 + z2.im / 8.0};
-    o.dk2 = {1.0 / 3.0 + z.re / 4.0 + z2.re / 10.0, z.im / 4.0 + z2.im / 10.0};
+    if constexpr (WITH_DERIVS) {
+      o.dk1 = {0.5 + z.re / 3.0 + z2.re / 8.0, z.im / 3.0 + z2.im / 8.0};
+      o.dk2 = {1.0 / 3.0 + z.re / 4.0 + z2.re / 10.0, z.im / 4.0 + z2.im / 10.0};
+    }
   } else {
     const zc rm1 = {o.rho.re - 1.0, o.rho.im};
     o.k1 = zdiv(rm1, z);
@@ -75,9 +82,11 @@ __device__ __forceinline__ CoeffOut coeff_eval(float p0, float p1, float p2, flo
     zc num = zmul(o.rho, zm1);
     num.re += 1.0;
     o.k2 = zdiv(num, zmul(z, z));
-    // kappa1' = (rho - kappa1)/z ; kappa2' = (rho - 2 kappa2)/z
-    o.dk1 = zdiv({o.rho.re - o.k1.re, o.rho.im - o.k1.im}, z);
-    o.dk2 = zdiv({o.rho.re - 2.0 * o.k2.re, o.rho.im - 2.0 * o.k2.im}, z);
+    if constexpr (WITH_DERIVS) {
+      // kappa1' = (rho - kappa1)/z ; kappa2' = (rho - 2 kappa2)/z
+      o.dk1 = zdiv({o.rho.re - o.k1.re, o.rho.im - o.k1.im}, z);
+      o.dk2 = zdiv({o.rho.re - 2.0 * o.k2.re, o.rho.im - 2.0 * o.k2.im}, z);
+    }
   }
   return o;
 }
