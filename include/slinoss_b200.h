@@ -306,6 +306,27 @@ SL_API int sl_mixer_decode_step(const void* gate, int64_t gate_row_stride, const
                                 void* normed, void* workspace, size_t workspace_bytes, int batch,
                                 int heads, int groups, int P, int N, int io_dtype, void* stream);
 
+/*
+ * Row-wise kernels of the block's FFN branch (the two GEMMs stay library calls): RMSNorm and the
+ * activation, forward and backward.  With them the branch is rematerialised in the backward pass
+ * from its input alone.  They replace FFNRmsNormFwdFused / FFNRmsNormBwdFused
+ * (slinoss/ops/block/cute/norm.py:85,173) and FFNActivationFwdFused / FFNActivationBwdFused
+ * (slinoss/ops/block/cute/activation.py:78,153) as block_ffn_residual calls them
+ * (slinoss/ops/block/training.py:193-354).
+ *   x, out, d_out, d_x (rows, C) dense : io_dtype;  weight (C) : io_dtype;  d_weight (C) float32,
+ *   ACCUMULATED into (caller zeroes it).  C a multiple of 8 (4 for float32), at most 2048 (1024).
+ *   kind 0 = GELU (tanh form): projected, hidden, d_* (rows, hidden_dim);
+ *   kind 1 = SwiGLU: projected, d_projected (rows, 2*hidden_dim) = [value | gate], hidden = value*silu(gate).
+ */
+SL_API int sl_rmsnorm_fwd(const void* x, const void* weight, float eps, void* out, long long rows, int C,
+                          int io_dtype, void* stream);
+SL_API int sl_rmsnorm_bwd(const void* x, const void* weight, float eps, const void* d_out, void* d_x,
+                          float* d_weight, long long rows, int C, int io_dtype, void* stream);
+SL_API int sl_ffn_activation_fwd(const void* projected, void* hidden, long long rows, int hidden_dim,
+                                 int kind, int io_dtype, void* stream);
+SL_API int sl_ffn_activation_bwd(const void* projected, const void* d_hidden, void* d_projected,
+                                 long long rows, int hidden_dim, int kind, int io_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

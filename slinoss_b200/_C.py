@@ -62,6 +62,10 @@ _PROTOTYPES = {
     "sl_mixer_decode_step": (c_int, [_P, c_int64, _P, c_int64, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P,
                                      ctypes.POINTER(ScanPrepConfig), _P, _P, c_float, _P, _P, _P, _P, _P, _P,
                                      c_size_t] + [c_int] * 6 + [_P]),
+    "sl_rmsnorm_fwd": (c_int, [_P, _P, c_float, _P, ctypes.c_longlong, c_int, c_int, _P]),
+    "sl_rmsnorm_bwd": (c_int, [_P, _P, c_float, _P, _P, _P, ctypes.c_longlong, c_int, c_int, _P]),
+    "sl_ffn_activation_fwd": (c_int, [_P, _P, ctypes.c_longlong, c_int, c_int, c_int, _P]),
+    "sl_ffn_activation_bwd": (c_int, [_P, _P, _P, ctypes.c_longlong, c_int, c_int, c_int, _P]),
     "sl_mixer_tail_fwd": (c_int, [_P, _P, c_int64, _P, _P, _P, c_float, _P] + [c_int] * 5 + [_P]),
     "sl_mixer_tail_bwd": (c_int, [_P, _P, c_int64, _P, _P, _P, c_float, _P, _P, _P, _P, _P, _P]
                           + [c_int] * 5 + [_P]),
@@ -453,3 +457,62 @@ def mixer_decode_step(gate, value, params, bc, conv_weight, conv_bias, conv_stat
             _ptr(b_prev_out), _ptr(u_prev), _ptr(normed), _ptr(workspace), workspace.numel(), batch, heads,
             groups, P, N, dtype_code(gate.dtype), _stream(dev)), "sl_mixer_decode_step")
     return normed
+
+
+# ---------------------------------------------------------------------------------
+# FFN branch: row-wise kernels
+# ---------------------------------------------------------------------------------
+FFN_KINDS = {"gelu": 0, "swiglu": 1}
+
+
+def rmsnorm_supported(C: int, dtype: torch.dtype) -> bool:
+    v = 4 if dtype == torch.float32 else 8
+    return dtype in _DTYPE_CODE and C % v == 0 and C // v <= 256
+
+
+def rmsnorm_fwd(x, weight, eps):
+    """``x (..., C)`` dense -> same shape; launches ``sl_rmsnorm_fwd``."""
+    dev = require_cuda(x, weight)
+    C = int(x.shape[-1])
+    out = torch.empty_like(x)
+    with torch.cuda.device(dev):
+        check(lib().sl_rmsnorm_fwd(_ptr(x), _ptr(weight), float(eps), _ptr(out), x.numel() // C, C,
+                                   dtype_code(x.dtype), _stream(dev)), "sl_rmsnorm_fwd")
+    return out
+
+
+def rmsnorm_bwd(x, weight, eps, d_out):
+    """Returns ``(d_x, d_weight float32)``."""
+    dev = require_cuda(x, weight, d_out)
+    C = int(x.shape[-1])
+    d_x = torch.empty_like(x)
+    d_w = torch.zeros(C, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().sl_rmsnorm_bwd(_ptr(x), _ptr(weight), float(eps), _ptr(d_out), _ptr(d_x), _ptr(d_w),
+                                   x.numel() // C, C, dtype_code(x.dtype), _stream(dev)), "sl_rmsnorm_bwd")
+    return d_x, d_w
+
+
+def ffn_activation_fwd(projected, kind: str):
+    """``projected (..., W)`` dense, W = hidden (gelu) or 2*hidden (swiglu) -> ``hidden (..., hidden)``."""
+    dev = require_cuda(projected)
+    W = int(projected.shape[-1])
+    H = W // 2 if kind == "swiglu" else W
+    hidden = torch.empty(projected.shape[:-1] + (H,), dtype=projected.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().sl_ffn_activation_fwd(_ptr(projected), _ptr(hidden), projected.numel() // W, H,
+                                          FFN_KINDS[kind], dtype_code(projected.dtype), _stream(dev)),
+              "sl_ffn_activation_fwd")
+    return hidden
+
+
+def ffn_activation_bwd(projected, d_hidden, kind: str):
+    dev = require_cuda(projected, d_hidden)
+    W = int(projected.shape[-1])
+    H = W // 2 if kind == "swiglu" else W
+    d_proj = torch.empty_like(projected)
+    with torch.cuda.device(dev):
+        check(lib().sl_ffn_activation_bwd(_ptr(projected), _ptr(d_hidden), _ptr(d_proj), projected.numel() // W, H,
+                                          FFN_KINDS[kind], dtype_code(projected.dtype), _stream(dev)),
+              "sl_ffn_activation_bwd")
+    return d_proj

@@ -1,8 +1,9 @@
 """Pre-norm residual block: ``x + mixer(norm(x))`` then ``x + ffn(norm(x))``.
 
 Composition, parameter names and residual arithmetic (float32 add, cast back)
-follow the reference block (slinoss/blocks/block.py:41-303).  The FFN branch is
-plain torch; only the mixer branch runs on the custom kernels.
+follow the reference block (slinoss/blocks/block.py:41-303).  On CUDA the FFN
+branch runs as one rematerialising op (``ops.block.ffn_residual``) when its
+conditions hold, else as plain torch.
 """
 
 from __future__ import annotations
@@ -13,6 +14,7 @@ from torch import nn
 
 from ..layers import RMSNorm, SLinOSSMixer
 from ..layers.mlp import SLinOSSMLP
+from ..ops.block import ffn_residual, ffn_residual_supported, residual_add
 from .config import SLinOSSBlockConfig
 from .state import SLinOSSBlockState
 
@@ -34,6 +36,10 @@ class SLinOSSBlock(nn.Module):
         self.config, self.d_model = config, config.d_model
         self.residual_in_fp32 = bool(config.residual_in_fp32)
         self.residual_dropout = float(config.residual_dropout)
+        # What the FFN branch rebuilds in the backward pass on CUDA: "full" (keeps only the branch input,
+        # the reference's schedule), "rows" (keeps the projection too: no GEMM is repeated) or "none"
+        # (plain autograd, the default: fastest while the activations fit in memory).
+        self.ffn_remat = "none"
         kw = {"device": device, "dtype": dtype}
         self.mixer_norm = make_norm(config.norm_kind, config.d_model, eps=config.norm_eps, **kw)
         self.mixer = SLinOSSMixer(config.d_model, **config.mixer.build_kwargs(), **kw)
@@ -54,10 +60,13 @@ class SLinOSSBlock(nn.Module):
         return x if self.residual_dropout <= 0.0 else F.dropout(x, self.residual_dropout, self.training)
 
     def _add(self, residual, branch):
-        dt = torch.float32 if self.residual_in_fp32 else residual.dtype
-        return residual.to(dt).add(branch.to(dt)).to(dtype=residual.dtype)
+        return residual_add(residual, branch, self.residual_in_fp32)
 
     def _ffn_residual(self, x):
+        no_drop = self.residual_dropout <= 0.0 or not self.training
+        if no_drop and self.ffn_remat != "none" and ffn_residual_supported(x, self.ffn_norm, self.ffn):
+            return ffn_residual(x, self.ffn_norm, self.ffn, residual_in_fp32=self.residual_in_fp32,
+                                remat=self.ffn_remat)
         return self._add(x, self._drop(self.ffn(apply_norm(self.ffn_norm, x))))
 
     def forward(self, x, *, state: SLinOSSBlockState | None = None, return_state: bool = False,

@@ -20,7 +20,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "_lib"
 LIB_PATH = LIB_DIR / "libslinoss_b200.so"
 SOURCES = ["abi.cu", "scan_simt.cu", "scan_tc.cu", "decode.cu", "scanprep_conv.cu", "mixer_tail.cu",
-           "scan_bwd_static.cu", "mixer_step.cu"]
+           "scan_bwd_static.cu", "mixer_step.cu", "ffn_rowwise.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xptxas=-v", "-Xcompiler", "-fPIC", "-Xcompiler",

@@ -51,6 +51,8 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--batch-per-gpu", type=int, default=4)
     ap.add_argument("--bucket-mb", type=int, default=32)
+    ap.add_argument("--ffn-remat", choices=["full", "rows", "none"], default=None,
+                    help="what the FFN branch rebuilds in the backward pass (default: the block's own)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -73,6 +75,10 @@ def main():
     torch.manual_seed(0)                         # identical replicas on every rank
     cfg = lm_stack_config(args.d_model, args.layers)
     model = SLinOSSLM(args.vocab, cfg, device=dev, dtype=torch.bfloat16)
+    if args.ffn_remat is not None:
+        for blk in model.backbone.blocks:
+            blk.ffn_remat = args.ffn_remat
+    ffn_remat = model.backbone.blocks[0].ffn_remat
     n_params = sum(p.numel() for p in model.parameters())
     g = torch.Generator(device=dev).manual_seed(shard.rank_seed(1, rank))
     ids = torch.randint(0, args.vocab, (args.batch_per_gpu, args.seq), generator=g, device=dev)
@@ -97,7 +103,7 @@ def main():
             "config": {"layers": args.layers, "d_model": args.d_model, "heads": args.d_model // 64,
                        "d_state": 64, "vocab": args.vocab, "seq": args.seq,
                        "batch_per_gpu": args.batch_per_gpu, "global_batch": world * args.batch_per_gpu,
-                       "dtype": "bf16", "parameters": n_params, "data": "synthetic uniform ids"},
+                       "dtype": "bf16", "parameters": n_params, "ffn_remat": ffn_remat, "data": "synthetic uniform ids"},
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
             "ms_per_step_without_allreduce": ms_plain,
