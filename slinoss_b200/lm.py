@@ -54,14 +54,17 @@ class SLinOSSLM(nn.Module):
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         if ids.ndim != 2:
             raise ValueError(f"Expected ids shape (batch, T), got {tuple(ids.shape)}.")
-        hidden = self.backbone(self.token_embed(ids))
-        return F.linear(hidden, self.token_embed.weight)
+        return F.linear(self.hidden(ids), self.token_embed.weight)
+
+    def hidden(self, ids: torch.Tensor) -> torch.Tensor:
+        return self.backbone(self.token_embed(ids))
 
     def loss(self, ids: torch.Tensor) -> torch.Tensor:
-        """Mean next-token cross-entropy of ``ids`` (float32)."""
-        logits = self(ids)
-        return F.cross_entropy(logits[:, :-1].reshape(-1, self.vocab_size).float(),
-                               ids[:, 1:].reshape(-1))
+        """Mean next-token cross-entropy of ``ids`` (float32).  The last position has no target, so
+        its row is dropped before the head GEMM rather than from the logits."""
+        rows = self.hidden(ids)[:, :-1].reshape(-1, self.d_model)
+        logits = F.linear(rows, self.token_embed.weight)
+        return F.cross_entropy(logits.float(), ids[:, 1:].reshape(-1))
 
 
 def decay_groups(model: nn.Module, weight_decay: float):
@@ -82,22 +85,37 @@ class DataParallelTrainer:
     def __init__(self, model: SLinOSSLM, *, lr: float = 3e-4, weight_decay: float = 0.05,
                  grad_clip: float = 1.0, bucket_bytes: int = 32 << 20, reduce: bool = True) -> None:
         self.model, self.grad_clip = model, grad_clip
-        fused = next(model.parameters()).is_cuda
+        fused = self.fused = next(model.parameters()).is_cuda
         self.opt = torch.optim.AdamW(decay_groups(model, weight_decay), lr=lr, betas=(0.9, 0.95),
                                      fused=fused)
         self.reducer = shard.GradBucketReducer(model.parameters(), bucket_bytes=bucket_bytes) \
             if reduce else None
 
     def step(self, ids: torch.Tensor) -> torch.Tensor:
-        self.opt.zero_grad(set_to_none=False)
+        self.opt.zero_grad(set_to_none=True)
         loss = self.model.loss(ids)
         loss.backward()
         if self.reducer is not None:
             self.reducer.finish()
         if self.grad_clip and self.grad_clip > 0:
-            torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
+            self._clip()
         self.opt.step()
         return loss.detach()
+
+    def _clip(self) -> None:
+        """Global-norm clipping.  With the fused optimizer the coefficient is not applied as a pass over
+        the gradients: the optimizer kernel divides every gradient by ``grad_scale`` as it reads it
+        (the hook loss scaling uses), so ``grad_scale = 1 / coefficient`` clips with no extra traffic
+        and no host synchronisation."""
+        grads = [p.grad for p in self.model.parameters() if p.grad is not None]
+        if not self.fused:
+            torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
+            return
+        norms = torch._foreach_norm(grads, 2.0)
+        total = torch.linalg.vector_norm(torch.stack([n.float() for n in norms]), 2.0)
+        # clip_grad_norm_'s coefficient is min(1, clip / (total + 1e-6)); grad_scale is its reciprocal
+        self.opt.grad_scale = torch.clamp((total + 1e-6) / self.grad_clip, min=1.0).reshape(())
+        self.last_grad_norm = total
 
 
 __all__ = ["DataParallelTrainer", "SLinOSSLM", "decay_groups", "lm_stack_config"]

@@ -102,7 +102,7 @@ def test_ffn_branch_of_the_block_rematerialised_against_plain_autograd(dtype, ki
     out_f, dx_f, g_f = run(True)
     assert _C.kernel_launches() - launches == 6      # norm, act; norm, act, act', norm'
     out_p, dx_p, g_p = run(False)
-    assert _C.kernel_launches() - launches == 6
+    assert _C.kernel_launches() - launches == 6 + 2  # the plain path: the norm's forward and backward only
 
     # float64 evaluation of the same expression
     blk64 = _block(kind, bias, dtype, remat="none").double()
@@ -138,7 +138,7 @@ def test_plain_path_is_kept_for_layernorm_dropout_and_autocast():
     n0 = _C.kernel_launches()
     blk.ffn_remat = "none"
     blk._ffn_residual(x)
-    assert _C.kernel_launches() == n0
+    assert _C.kernel_launches() == n0 + 1        # the norm alone
     blk.ffn_remat = "full"
     assert block_mod.ffn_residual_supported(x, blk.ffn_norm, blk.ffn)
     assert not block_mod.ffn_residual_supported(x.bfloat16(), blk.ffn_norm, blk.ffn)
@@ -149,4 +149,26 @@ def test_plain_path_is_kept_for_layernorm_dropout_and_autocast():
     blk.train()
     n0 = _C.kernel_launches()
     blk._ffn_residual(x)
-    assert _C.kernel_launches() == n0
+    assert _C.kernel_launches() == n0 + 1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_module_runs_on_the_row_kernels_and_matches_torch(dtype):
+    torch.manual_seed(5)
+    norm = sb.RMSNorm(512, eps=1e-5, device=DEV, dtype=dtype)
+    with torch.no_grad():
+        norm.weight.add_(0.3 * torch.randn_like(norm.weight))
+    x = torch.randn(4, 33, 512, device=DEV).to(dtype).requires_grad_()
+    dy = torch.randn_like(x)
+    n0 = _C.kernel_launches()
+    out = norm(x)
+    out.backward(dy)
+    assert _C.kernel_launches() - n0 == 2
+    x64 = x.detach().double().requires_grad_()
+    w64 = norm.weight.detach().double().requires_grad_()
+    want = F.rms_norm(x64, (512,), w64, 1e-5)
+    want.backward(dy.double())
+    assert rel(out, want) <= TOL[dtype] and rel(x.grad, x64.grad) <= TOL[dtype]
+    assert rel(norm.weight.grad, w64.grad) <= TOL[dtype]
+    # rows in another type than the weight: computed in the weight's type, returned in the rows'
+    assert norm(x.detach().double()).dtype == torch.float64
