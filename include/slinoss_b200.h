@@ -56,7 +56,9 @@ enum { SL_F32 = 0, SL_BF16 = 1, SL_F16 = 2 };
 enum {
   SL_PATH_AUTO = 0, /* tensor-core path when the shape allows, else SIMT */
   SL_PATH_SIMT = 1, /* exact float32 sequential recurrence (any dtype in)     */
-  SL_PATH_TC = 2    /* tcgen05/TMEM chunked path (bf16 / fp16 operands)       */
+  SL_PATH_TC = 2    /* tcgen05/TMEM chunked path: bf16 / fp16 operands, P = 64, N = 64 or 128
+                       (N = 128 runs as two passes over the column blocks of B and C and needs the
+                       SL_WS_SCAN_FWD workspace in the forward pass too)       */
 };
 
 /* workspace kinds for sl_workspace_bytes */

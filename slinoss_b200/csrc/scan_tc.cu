@@ -63,6 +63,7 @@ struct alignas(64) TcFwdParams {
   const void* Bprev;
   const void* Uprev;
   void* Y;
+  const float* Yadd;    // optional float32 (batch*heads, T, 64): added to the output before it is rounded
   float* zfinal;
   void* states16;       // optional (batch*heads, nchunks, 64, 128) 16-bit: conjugated start state of every chunk
   int heads, groups, T, nchunks;
@@ -184,11 +185,33 @@ __device__ void chunk_scalars(float* sc, const float* __restrict__ Mb, const flo
 
 }  // namespace
 
+// The kernels hold 64 complex state columns per (batch, head).  The recurrence does not couple state
+// columns (z[:, n] sees b[n] only, and y sums c[n] z[:, n] over n), so N = 128 runs as two passes over the
+// column blocks 0..63 and 64..127 of B and C, addressed in place through tensor maps with the full row
+// pitch; the passes' Y, dU, dM, dK and dU_prev add, everything else is per column block.
 bool scan_tc_supported(const ScanDims& d, int io_dtype) {
-  return d.P == 64 && d.N == 64 && (io_dtype == SL_BF16 || io_dtype == SL_F16) && d.T >= 1 &&
+  return d.P == 64 && (d.N == 64 || d.N == 128) && (io_dtype == SL_BF16 || io_dtype == SL_F16) && d.T >= 1 &&
          tc::encode_tiled_fn() != nullptr;
 }
-size_t scan_tc_fwd_workspace(const ScanDims&) { return 0; }
+namespace {
+inline ScanDims one_block(const ScanDims& d) { ScanDims o = d; o.N = 64; return o; }
+// forward workspace of the two-pass form: start state, final state and B_prev of one column block (dense),
+// and the float32 output of the first pass
+struct TcFwdSplitLayout { size_t z0, zf, bprev, ypart, total; };
+TcFwdSplitLayout tc_fwd_split_layout(const ScanDims& d) {
+  const size_t BH = (size_t)d.batch * d.heads, BG = (size_t)d.batch * d.groups;
+  TcFwdSplitLayout o{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t r = off; off += round_up(bytes, 256); return r; };
+  o.z0 = take(BH * 64 * 128 * 4);
+  o.zf = take(BH * 64 * 128 * 4);
+  o.bprev = take(BG * 128 * 2);
+  o.ypart = take(BH * (size_t)d.T * 64 * 4);
+  o.total = off;
+  return o;
+}
+}  // namespace
+size_t scan_tc_fwd_workspace(const ScanDims& d) { return d.N == 128 ? tc_fwd_split_layout(d).total : 0; }
 namespace {
 struct TcBwdLayout {
   size_t states, zfinal, dg, sterm, dkcd, anchor, dbh, dch, dstart, dgb, total;
@@ -217,8 +240,34 @@ TcBwdLayout tc_bwd_layout(const ScanDims& d) {
 }
 }  // namespace
 
+// backward workspace of the two-pass form: the one-block workspace (reused by both passes), dense copies
+// of the per-block inputs, dense per-block outputs, and the second pass' summands
+struct TcBwdSplitLayout {
+  size_t inner, z0, zf, dfin, dinit, bprev, dbprev, du, dm, dk, duprev, total;
+};
+TcBwdSplitLayout tc_bwd_split_layout(const ScanDims& d) {
+  const size_t BH = (size_t)d.batch * d.heads, BG = (size_t)d.batch * d.groups;
+  TcBwdSplitLayout o{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t r = off; off += round_up(bytes, 256); return r; };
+  o.inner = take(tc_bwd_layout(one_block(d)).total);
+  o.z0 = take(BH * 64 * 128 * 4);
+  o.zf = take(BH * 64 * 128 * 4);
+  o.dfin = take(BH * 64 * 128 * 4);
+  o.dinit = take(BH * 64 * 128 * 4);
+  o.bprev = take(BG * 128 * 2);
+  o.dbprev = take(BG * 128 * 2);
+  o.du = take(BH * (size_t)d.T * 64 * 2);
+  o.dm = take(BH * (size_t)d.T * 2 * 4);
+  o.dk = take(BH * (size_t)d.T * 4 * 4);
+  o.duprev = take(BH * 64 * 2);
+  o.total = off;
+  return o;
+}
+
 size_t scan_tc_bwd_workspace(const ScanDims& d) {
-  return std::max(scan_simt_bwd_workspace(d), tc_bwd_layout(d).total);
+  const size_t tcw = d.N == 128 ? tc_bwd_split_layout(d).total : tc_bwd_layout(d).total;
+  return std::max(scan_simt_bwd_workspace(d), tcw);
 }
 
 constexpr int NW = 4;   // worker warps per TMEM lane quadrant
@@ -234,17 +283,21 @@ static int launch_tc_fwd(const TcFwdParams& p, int grid, cudaStream_t st) {
 }
 
 // Y == nullptr runs the state pre-sweep only (chunk-start states + final state).
+// ``bc_pitch`` = elements per row of B and C (128, or 256 when B / C point at one column block of
+// N = 128 rows); everything else is dense with 64 state columns.  ``Yadd`` (float32, or null) is added to
+// the output before it is rounded: the first pass' output in the two-pass form.
 int scan_tc_fwd_impl(const void* U, const float* M, const float* K, const void* B, const void* C,
                      const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
                      void* states16, const ScanDims& d, int io_dtype, int y_dtype,
-                     cudaStream_t st) {
+                     cudaStream_t st, int bc_pitch = 128, const float* Yadd = nullptr) {
   TcFwdParams p{};
   const bool bf = io_dtype == SL_BF16;
   const uint64_t BH = (uint64_t)d.batch * d.heads, BG = (uint64_t)d.batch * d.groups;
-  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BG, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmC, C ? C : B, 128, d.T, BG, 64, bf))
+  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BG, 64, bf, bc_pitch) ||
+      !tc::make_tmap_3d(&p.tmC, C ? C : B, 128, d.T, BG, 64, bf, bc_pitch))
     return SL_ERR_LAUNCH_FAILED;
-  p.M = M; p.K = K; p.z0 = z0; p.Bprev = Bprev; p.Uprev = Uprev; p.Y = Y; p.zfinal = zfinal;
+  p.M = M; p.K = K; p.z0 = z0; p.Bprev = Bprev; p.Uprev = Uprev; p.Y = Y; p.zfinal = zfinal; p.Yadd = Yadd;
   p.states16 = states16;
   p.heads = d.heads; p.groups = d.groups; p.T = d.T; p.nchunks = (d.T + L - 1) / L;
   p.wait_limit = wait_limit_clocks();
@@ -265,15 +318,79 @@ int scan_tc_fwd_impl(const void* U, const float* M, const float* K, const void* 
   return rc;
 }
 
-size_t scan_tc_states_bytes(const ScanDims& d) {
-  return (size_t)d.batch * d.heads * ((d.T + L - 1) / L) * 64 * 128 * 2;
+size_t scan_tc_states_bytes(const ScanDims& d) {   // N = 128: the two column blocks one after the other
+  return (size_t)d.batch * d.heads * ((d.T + L - 1) / L) * 64 * 128 * 2 * (d.N / 64);
 }
+
+namespace {
+// column block ``blk`` (128 values of 256) of a (rows, 256) tensor <-> a dense (rows, 128) one
+inline bool copy_block_in(void* dense, const void* wide, int blk, size_t rows, size_t esize, cudaStream_t st) {
+  return cudaMemcpy2DAsync(dense, 128 * esize, reinterpret_cast<const uint8_t*>(wide) + blk * 128 * esize,
+                           256 * esize, 128 * esize, rows, cudaMemcpyDeviceToDevice, st) == cudaSuccess;
+}
+inline bool copy_block_out(void* wide, const void* dense, int blk, size_t rows, size_t esize, cudaStream_t st) {
+  return cudaMemcpy2DAsync(reinterpret_cast<uint8_t*>(wide) + blk * 128 * esize, 256 * esize, dense,
+                           128 * esize, 128 * esize, rows, cudaMemcpyDeviceToDevice, st) == cudaSuccess;
+}
+inline const void* block_of(const void* wide, int blk) {   // 16-bit rows of 256: start of a column block
+  return wide ? reinterpret_cast<const uint8_t*>(wide) + blk * 256 : nullptr;
+}
+
+// a += b over n 16-bit values (summed in float32) or float32 values; 16 bytes per thread, the last
+// thread takes what is left of a length that is no multiple of that
+template <typename T>
+__global__ void __launch_bounds__(256) add_into_kernel(T* __restrict__ a, const T* __restrict__ b, size_t n) {
+  constexpr int V = Vec16<T>::N;
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
+  if (i >= n) return;
+  if (i + V <= n) {
+    float x[V], y[V];
+    load16<T>(a + i, x);
+    load16<T>(b + i, y);
+#pragma unroll
+    for (int k = 0; k < V; ++k) x[k] += y[k];
+    store16<T>(a + i, x);
+  } else {
+    for (size_t j = i; j < n; ++j) a[j] = from_f32<T>(to_f32(a[j]) + to_f32(b[j]));
+  }
+}
+template <typename T>
+void add_into(void* a, const void* b, size_t n, cudaStream_t st) {
+  const size_t pieces = (n + Vec16<T>::N - 1) / Vec16<T>::N;
+  add_into_kernel<T><<<(unsigned)((pieces + 255) / 256), 256, 0, st>>>(reinterpret_cast<T*>(a),
+                                                                      reinterpret_cast<const T*>(b), n);
+  note_launches(1);
+}
+}  // namespace
 
 int scan_tc_fwd(const void* U, const float* M, const float* K, const void* B, const void* C,
                 const float* z0, const void* Bprev, const void* Uprev, void* Y, float* zfinal,
-                void* states_out, const ScanDims& d, int io_dtype, int y_dtype, void*, size_t,
+                void* states_out, const ScanDims& d, int io_dtype, int y_dtype, void* ws, size_t ws_bytes,
                 cudaStream_t st) {
-  return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, states_out, d, io_dtype, y_dtype, st);
+  if (d.N == 64)
+    return scan_tc_fwd_impl(U, M, K, B, C, z0, Bprev, Uprev, Y, zfinal, states_out, d, io_dtype, y_dtype, st);
+  // N = 128: two passes over the column blocks; the second adds the first's float32 output
+  const TcFwdSplitLayout lay = tc_fwd_split_layout(d);
+  if (!ws || ws_bytes < lay.total) return SL_ERR_WORKSPACE_TOO_SMALL;
+  uint8_t* w = reinterpret_cast<uint8_t*>(ws);
+  const ScanDims d1 = one_block(d);
+  const size_t BH = (size_t)d.batch * d.heads, BG = (size_t)d.batch * d.groups;
+  const size_t st_bytes = scan_tc_states_bytes(d1);
+  float* ypart = reinterpret_cast<float*>(w + lay.ypart);
+  for (int blk = 0; blk < 2; ++blk) {
+    float* z0b = z0 ? reinterpret_cast<float*>(w + lay.z0) : nullptr;
+    float* zfb = zfinal ? reinterpret_cast<float*>(w + lay.zf) : nullptr;
+    void* bpb = Bprev ? (void*)(w + lay.bprev) : nullptr;
+    if (z0 && !copy_block_in(z0b, z0, blk, BH * 64, 4, st)) return SL_ERR_LAUNCH_FAILED;
+    if (Bprev && !copy_block_in(bpb, Bprev, blk, BG, 2, st)) return SL_ERR_LAUNCH_FAILED;
+    void* st_out = states_out ? reinterpret_cast<uint8_t*>(states_out) + blk * st_bytes : nullptr;
+    const int rc = scan_tc_fwd_impl(U, M, K, block_of(B, blk), block_of(C, blk), z0b, bpb, Uprev,
+                                    blk == 0 ? (void*)ypart : Y, zfb, st_out, d1, io_dtype,
+                                    blk == 0 ? (int)SL_F32 : y_dtype, st, 256, blk == 0 ? nullptr : ypart);
+    if (rc != SL_OK) return rc;
+    if (zfinal && !copy_block_out(zfinal, zfb, blk, BH * 64, 4, st)) return SL_ERR_LAUNCH_FAILED;
+  }
+  return launch_status();
 }
 
 template <typename TIn>
@@ -288,15 +405,15 @@ static int launch_tc_bwd(const TcBwdParams& p, int grid, cudaStream_t st) {
 // Tensor-core backward: state pre-sweep (unless the forward saved its chunk states), reverse sweep,
 // the boundary terms of carried B_prev / U_prev, scalar finish and, for grouped B/C, the reduction of
 // dB / dC over the heads of a group.  A dY of another dtype (or none) takes the exact float32 sweeps.
-int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
-                const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
-                const float* zfinal_in, const void* dY,
-                const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC, float* dinit,
-                void* dBprev, void* dUprev, const ScanDims& d, int io_dtype, int dy_dtype, void* ws,
-                size_t ws_bytes, cudaStream_t st) {
-  if (!dY || dy_dtype != io_dtype)
-    return scan_simt_bwd(U, M, K, B, C, z0, Bprev, Uprev, dY, dfinal, dU, dM, dK, dB, dC, dinit, dBprev,
-                         dUprev, d, io_dtype, dy_dtype, ws, ws_bytes, st);
+//
+// One block of 64 state columns: ``d.N`` is 64; B, C, dB, dC have ``bc_pitch`` elements per row (128, or 256
+// when they point at one column block of N = 128 rows); every other tensor is dense.
+static int scan_tc_bwd_block(const void* U, const float* M, const float* K, const void* B, const void* C,
+                             const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
+                             const float* zfinal_in, const void* dY, const float* dfinal, void* dU, float* dM,
+                             float* dK, void* dB, void* dC, float* dinit, void* dBprev, void* dUprev,
+                             const ScanDims& d, int io_dtype, void* ws, size_t ws_bytes, cudaStream_t st,
+                             int bc_pitch) {
   const TcBwdLayout lay = tc_bwd_layout(d);
   if (!ws || ws_bytes < lay.total) return SL_ERR_WORKSPACE_TOO_SMALL;
   uint8_t* w = reinterpret_cast<uint8_t*>(ws);
@@ -311,17 +428,21 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
   if (!states || !zfinal) {   // nothing saved by the forward: recompute with the state pre-sweep
     float* zf = reinterpret_cast<float*>(w + lay.zfinal);
     if (int e = scan_tc_fwd_impl(U, M, K, B, nullptr, z0, Bprev, Uprev, nullptr, zf, w + lay.states, d,
-                                 io_dtype, SL_F32, st))
+                                 io_dtype, SL_F32, st, bc_pitch))
       return e;
     zfinal = zf;
     states = w + lay.states;
   }
   TcBwdParams p{};
-  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BG, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BG, 64, bf) || !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
+  const uint64_t out_pitch = grouped ? 128 : bc_pitch;   // the per-head workspace is dense
+  if (!tc::make_tmap_3d(&p.tmU, U, 64, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmB, B, 128, d.T, BG, 64, bf, bc_pitch) ||
+      !tc::make_tmap_3d(&p.tmC, C, 128, d.T, BG, 64, bf, bc_pitch) ||
+      !tc::make_tmap_3d(&p.tmdY, dY, 64, d.T, BH, 64, bf) ||
       !tc::make_tmap_3d(&p.tmZ, states, 128, (uint64_t)nC * 64, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmdU, dU, 64, d.T, BH, 64, bf) || !tc::make_tmap_3d(&p.tmdB, dBh, 128, d.T, BH, 64, bf) ||
-      !tc::make_tmap_3d(&p.tmdC, dCh, 128, d.T, BH, 64, bf))
+      !tc::make_tmap_3d(&p.tmdU, dU, 64, d.T, BH, 64, bf) ||
+      !tc::make_tmap_3d(&p.tmdB, dBh, 128, d.T, BH, 64, bf, out_pitch) ||
+      !tc::make_tmap_3d(&p.tmdC, dCh, 128, d.T, BH, 64, bf, out_pitch))
     return SL_ERR_LAUNCH_FAILED;
   p.M = M; p.K = K; p.dfinal = dfinal; p.zfinal = zfinal;
   p.dg = reinterpret_cast<float2*>(w + lay.dg); p.sterm = reinterpret_cast<float2*>(w + lay.sterm);
@@ -353,15 +474,73 @@ int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, co
     if (bf)
       scan_tc_group_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
           (const __nv_bfloat16*)dBh, (const __nv_bfloat16*)dCh, (__nv_bfloat16*)dB, (__nv_bfloat16*)dC, d.heads,
-          d.groups, d.T, pieces);
+          d.groups, d.T, pieces, bc_pitch);
     else
       scan_tc_group_reduce_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)dBh, (const __half*)dCh, (__half*)dB,
-                                                                 (__half*)dC, d.heads, d.groups, d.T, pieces);
+                                                                 (__half*)dC, d.heads, d.groups, d.T, pieces,
+                                                                 bc_pitch);
     note_launches(1);
   }
   return launch_status();
 }
 
+
+int scan_tc_bwd(const void* U, const float* M, const float* K, const void* B, const void* C,
+                const float* z0, const void* Bprev, const void* Uprev, const void* states_in,
+                const float* zfinal_in, const void* dY,
+                const float* dfinal, void* dU, float* dM, float* dK, void* dB, void* dC, float* dinit,
+                void* dBprev, void* dUprev, const ScanDims& d, int io_dtype, int dy_dtype, void* ws,
+                size_t ws_bytes, cudaStream_t st) {
+  if (!dY || dy_dtype != io_dtype)
+    return scan_simt_bwd(U, M, K, B, C, z0, Bprev, Uprev, dY, dfinal, dU, dM, dK, dB, dC, dinit, dBprev,
+                         dUprev, d, io_dtype, dy_dtype, ws, ws_bytes, st);
+  if (d.N == 64)
+    return scan_tc_bwd_block(U, M, K, B, C, z0, Bprev, Uprev, states_in, zfinal_in, dY, dfinal, dU, dM, dK, dB,
+                             dC, dinit, dBprev, dUprev, d, io_dtype, ws, ws_bytes, st, 128);
+  // N = 128: one pass per column block.  dB, dC, d_initial and dB_prev are per block; dU, dM, dK and
+  // dU_prev are the sums of the passes (the second pass writes into the workspace and is added).
+  const TcBwdSplitLayout lay = tc_bwd_split_layout(d);
+  if (!ws || ws_bytes < lay.total) return SL_ERR_WORKSPACE_TOO_SMALL;
+  uint8_t* w = reinterpret_cast<uint8_t*>(ws);
+  const ScanDims d1 = one_block(d);
+  const size_t BH = (size_t)d.batch * d.heads, BG = (size_t)d.batch * d.groups;
+  const size_t st_bytes = scan_tc_states_bytes(d1), inner_bytes = tc_bwd_layout(d1).total;
+  const bool saved = states_in && zfinal_in;
+  for (int blk = 0; blk < 2; ++blk) {
+    float* z0b = z0 ? reinterpret_cast<float*>(w + lay.z0) : nullptr;
+    float* zfb = saved ? reinterpret_cast<float*>(w + lay.zf) : nullptr;
+    float* dfb = dfinal ? reinterpret_cast<float*>(w + lay.dfin) : nullptr;
+    float* dib = dinit ? reinterpret_cast<float*>(w + lay.dinit) : nullptr;
+    void* bpb = Bprev ? (void*)(w + lay.bprev) : nullptr;
+    void* dbpb = Bprev ? (void*)(w + lay.dbprev) : nullptr;
+    if (z0 && !copy_block_in(z0b, z0, blk, BH * 64, 4, st)) return SL_ERR_LAUNCH_FAILED;
+    if (saved && !copy_block_in(zfb, zfinal_in, blk, BH * 64, 4, st)) return SL_ERR_LAUNCH_FAILED;
+    if (dfinal && !copy_block_in(dfb, dfinal, blk, BH * 64, 4, st)) return SL_ERR_LAUNCH_FAILED;
+    if (Bprev && !copy_block_in(bpb, Bprev, blk, BG, 2, st)) return SL_ERR_LAUNCH_FAILED;
+    const void* stb = saved ? reinterpret_cast<const uint8_t*>(states_in) + blk * st_bytes : nullptr;
+    void* dUb = blk == 0 ? dU : (void*)(w + lay.du);
+    float* dMb = blk == 0 ? dM : reinterpret_cast<float*>(w + lay.dm);
+    float* dKb = blk == 0 ? dK : reinterpret_cast<float*>(w + lay.dk);
+    void* dUpb = !Uprev ? nullptr : (blk == 0 ? dUprev : (void*)(w + lay.duprev));
+    const int rc = scan_tc_bwd_block(U, M, K, block_of(B, blk), block_of(C, blk), z0b, bpb, Uprev, stb, zfb, dY, dfb,
+                                     dUb, dMb, dKb, const_cast<void*>(block_of(dB, blk)),
+                                     const_cast<void*>(block_of(dC, blk)), dib, dbpb, dUpb, d1, io_dtype,
+                                     w + lay.inner, inner_bytes, st, 256);
+    if (rc != SL_OK) return rc;
+    if (dinit && !copy_block_out(dinit, dib, blk, BH * 64, 4, st)) return SL_ERR_LAUNCH_FAILED;
+    if (Bprev && dBprev && !copy_block_out(dBprev, dbpb, blk, BG, 2, st)) return SL_ERR_LAUNCH_FAILED;
+  }
+  const bool bf = io_dtype == SL_BF16;
+  if (bf) add_into<__nv_bfloat16>(dU, w + lay.du, BH * (size_t)d.T * 64, st);
+  else add_into<__half>(dU, w + lay.du, BH * (size_t)d.T * 64, st);
+  add_into<float>(dM, w + lay.dm, BH * (size_t)d.T * 2, st);
+  add_into<float>(dK, w + lay.dk, BH * (size_t)d.T * 4, st);
+  if (Uprev && dUprev) {
+    if (bf) add_into<__nv_bfloat16>(dUprev, w + lay.duprev, BH * 64, st);
+    else add_into<__half>(dUprev, w + lay.duprev, BH * 64, st);
+  }
+  return launch_status();
+}
 
 // The site code of the first expired wait on the current device since the last reset (0 = none).
 int scan_tc_device_status(bool reset) {

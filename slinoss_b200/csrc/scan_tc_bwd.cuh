@@ -793,7 +793,8 @@ template <typename TIn>
 __global__ void __launch_bounds__(256) scan_tc_group_reduce_kernel(const TIn* __restrict__ per_head_b,
                                                                    const TIn* __restrict__ per_head_c,
                                                                    TIn* __restrict__ dB, TIn* __restrict__ dC,
-                                                                   int heads, int groups, int T, size_t pieces) {
+                                                                   int heads, int groups, int T, size_t pieces,
+                                                                   int out_pitch) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // piece index over (batch*groups, T, 16)
   if (i >= pieces) return;
   const int hpg = heads / groups;
@@ -813,7 +814,7 @@ __global__ void __launch_bounds__(256) scan_tc_group_reduce_kernel(const TIn* __
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += v[k];
     }
-    store16<TIn>((which ? dC : dB) + (bgi * T + t) * 128 + piece * 8, acc);
+    store16<TIn>((which ? dC : dB) + (bgi * T + t) * out_pitch + piece * 8, acc);
   }
 }
 

@@ -136,6 +136,22 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
   // while the [S | Yoff] MMAs of the next chunk execute (their accumulators alternate by chunk parity).
   float et_keep[2] = {0.f, 0.f};   // exp(l_t) of this thread's two rows in the chunk whose output is pending
   auto output_epilogue = [&](int cp, bool live) {
+    float yadd[4 * SB];   // the summand of this thread's outputs, requested ahead of the wait
+#pragma unroll
+    for (int j = 0; j < 4 * SB; ++j) yadd[j] = 0.f;
+    if (!STATES_ONLY && p.Yadd != nullptr && live) {
+#pragma unroll
+      for (int i = 0; i < SB; ++i)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int t = cp * L + (hh ? rowB : rowA);
+          if (t < T) {
+            const float2 a = __ldg(reinterpret_cast<const float2*>(
+                p.Yadd + ((size_t)bh * T + t) * 64 + cg * SC + 8 * i + 2 * cq));
+            yadd[4 * i + 2 * hh] = a.x; yadd[4 * i + 2 * hh + 1] = a.y;
+          }
+        }
+    }
     if (live && !mbar_wait(&bar_mma[2], cp & 1, wl)) { report_timeout(4); s_abort = 1; live = false; }
     tc_fence_after_sync();
     if (live) {
@@ -150,8 +166,10 @@ __global__ void __launch_bounds__(128 * NW + 64, 1) scan_tc_fwd_kernel(const __g
         for (int hh = 0; hh < 2; ++hh) {
           const int R = hh ? rowB : rowA;
           const float et = hh ? et_keep[1] : et_keep[0];
-          const float y0 = __uint_as_float(yd[4 * i + 2 * hh]) + et * __uint_as_float(yo[4 * i + 2 * hh]);
-          const float y1 = __uint_as_float(yd[4 * i + 2 * hh + 1]) + et * __uint_as_float(yo[4 * i + 2 * hh + 1]);
+          const float y0 = __uint_as_float(yd[4 * i + 2 * hh]) + et * __uint_as_float(yo[4 * i + 2 * hh]) +
+                           yadd[4 * i + 2 * hh];
+          const float y1 = __uint_as_float(yd[4 * i + 2 * hh + 1]) + et * __uint_as_float(yo[4 * i + 2 * hh + 1]) +
+                           yadd[4 * i + 2 * hh + 1];
           if constexpr (sizeof(TY) == 2) {   // into the staging tile; rows beyond T are clipped by the store
             *reinterpret_cast<uint32_t*>(smem + OFF_Y + sw128(R, cg * SB + i) + 4 * cq) = Pack2<TY>::pack(y0, y1);
           } else if (t0p + R < T) {

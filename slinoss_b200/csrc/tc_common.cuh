@@ -310,12 +310,15 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // 3-D map over a dense (outer, rows, cols) 16-bit tensor with a (1, box_rows, 64) box and
 // the 128-byte swizzle; rows beyond `rows` read as zero.
+// ``pitch`` = elements between consecutive rows (0: the rows are dense, pitch = cols); a wider pitch
+// addresses a column block of a wider tensor.
 inline bool make_tmap_3d(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
-                         uint64_t outer, uint32_t box_rows, bool is_bf16) {
+                         uint64_t outer, uint32_t box_rows, bool is_bf16, uint64_t pitch = 0) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
+  if (pitch == 0) pitch = cols;
   cuuint64_t dims[3] = {cols, rows, outer};
-  cuuint64_t strides[2] = {cols * 2, cols * rows * 2};
+  cuuint64_t strides[2] = {pitch * 2, pitch * rows * 2};
   cuuint32_t box[3] = {64, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r =

@@ -336,13 +336,30 @@ def measure_scan(iters, dev):
                                                chunk_size=64), iters), bht * 1456, name)]
 
 
-WHAT = {"decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
+def measure_scan_n128(iters, dev):
+    """The config-1 streams with 128 state columns (the mixer's default d_state): two passes over the
+    column blocks of B and C."""
+    from . import _C
+    from .synthetic import make_scan_case
+    c = make_scan_case(8, 16, 4096, 64, 128, dtype=torch.bfloat16, seed=0).to(dev)
+    name = "batch 8 x heads 16 x T 4096 x P 64 x N 128, bf16"
+    fwd = lambda: _C.scan_fwd(c.U, c.M, c.K, c.B, c.C, None, None, None, chunk_size=64,
+                              y_dtype=torch.bfloat16, want_final=False, save_states=True)
+    _, fin, st = fwd()
+    bht = 8 * 16 * 4096
+    return [report("sl_v2x2ssd_fwd, N = 128 (saving chunk states)", time_ms(fwd, iters), bht * 1304, name),
+            report("sl_v2x2ssd_bwd, N = 128 (saved chunk states)",
+                   time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
+                                               chunk_size=64, saved=(st, fin)), iters), bht * 2480, name)]
+
+
+WHAT = {"scan_n128": measure_scan_n128, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
         "scanprep": measure_scanprep, "tail": measure_tail, "mixer": measure_mixer, "scan": measure_scan}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="decode,decode_sequence,mixer_step,scanprep,tail,mixer,scan")
+    ap.add_argument("--what", default="decode,decode_sequence,mixer_step,scanprep,tail,mixer,scan,scan_n128")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():

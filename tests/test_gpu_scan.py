@@ -215,7 +215,7 @@ def test_full_size_config1_forward_and_backward_of_whole_streams():
             assert rel(sl(gr), want[name]) <= 2e-2, (b, h, name, rel(sl(gr), want[name]))
 
 
-# ---- tensor-core (tcgen05) path: P = 64, N = 64, 16-bit operands -------------------------------
+# ---- tensor-core (tcgen05) path: P = 64, N = 64 or 128, 16-bit operands -------------------------------
 TC_SHAPES = [
     (1, 1, 1, 64, False, False),
     (2, 4, 2, 1, True, True),
@@ -227,12 +227,13 @@ TC_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("N", [64, 128])           # 128: two passes over the column blocks of B and C
 @pytest.mark.parametrize("shape", TC_SHAPES)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_forward_tensor_core_path(shape, dtype):
+def test_forward_tensor_core_path(shape, dtype, N):
     from slinoss_b200 import _C
     b, h, g, T, streaming, init = shape
-    case = make_scan_case(b, h, T, 64, 64, groups=g, dtype=dtype, seed=3 * T + b, streaming=streaming,
+    case = make_scan_case(b, h, T, 64, N, groups=g, dtype=dtype, seed=3 * T + b, streaming=streaming,
                           with_init=init)
     Y, fin, _, _ = _run(case, 64, "tc", output_dtype=torch.float32)
     wY, wfin, _, _ = _oracle_fwd(case)
@@ -265,6 +266,11 @@ def test_tensor_core_path_agrees_with_exact_path_on_reference_test_distribution(
 def test_auto_path_prefers_tensor_cores_and_falls_back_for_float32():
     from slinoss_b200 import _C
     assert _C.workspace_bytes(_C.WS_SCAN_FWD, 1, 1, 1, 64, 64, 64, 64, torch.bfloat16, "auto") == 0
+    assert _C.workspace_bytes(_C.WS_SCAN_FWD, 1, 1, 1, 64, 64, 128, 64, torch.bfloat16, "auto") > 0
+    odd = make_scan_case(1, 1, 70, 64, 96, dtype=torch.bfloat16)      # neither 64 nor 128 state columns
+    with pytest.raises(RuntimeError, match="unsupported"):
+        _run(odd, 64, "tc")
+    assert rel(_run(odd, 64, "auto", output_dtype=torch.float32)[0], _oracle_fwd(odd)[0]) <= 2e-2
     case = make_scan_case(1, 2, 70, 64, 64, dtype=torch.float32)
     with pytest.raises(RuntimeError, match="unsupported"):
         _run(case, 64, "tc")
@@ -291,12 +297,13 @@ TC_BWD_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("N", [64, 128])
 @pytest.mark.parametrize("shape", TC_BWD_SHAPES)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_backward_tensor_core_path(shape, dtype):
+def test_backward_tensor_core_path(shape, dtype, N):
     from slinoss_b200 import _C
     b, h, T, init, with_dfinal, g, streaming = shape
-    case = make_scan_case(b, h, T, 64, 64, groups=g, dtype=dtype, seed=11 * T + h, with_init=init,
+    case = make_scan_case(b, h, T, 64, N, groups=g, dtype=dtype, seed=11 * T + h, with_init=init,
                           streaming=streaming)
     c = case.to(DEV)
     names = ["U", "M", "K", "B", "C"] + (["initial_states"] if init else []) \
@@ -373,8 +380,9 @@ def test_backward_tensor_core_agrees_with_exact_path_at_strong_decay():
         assert rel(a, want[name]) <= 2e-2, (name, rel(a, want[name]))
 
 
-def test_saved_chunk_states_and_recompute_give_the_same_gradients():
-    case = make_scan_case(2, 2, 300, 64, 64, dtype=torch.bfloat16, seed=2, with_init=True).to(DEV)
+@pytest.mark.parametrize("N", [64, 128])
+def test_saved_chunk_states_and_recompute_give_the_same_gradients(N):
+    case = make_scan_case(2, 2, 300, 64, N, dtype=torch.bfloat16, seed=2, with_init=True).to(DEV)
     res = []
     for keep in (True, False):
         lv = [x.clone().requires_grad_(True) for x in (*case.tensors(), case.initial_states)]
