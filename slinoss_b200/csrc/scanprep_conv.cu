@@ -615,54 +615,53 @@ __device__ __forceinline__ float half_warp_sum(float v) {   // over the 16 lanes
   return v;
 }
 
-constexpr int BC_RPW = 1;   // records per warp (the kernels are bound by the MUFU pipe, not by latency)
+constexpr int BC_GCH = 8;   // groups one warp walks: grid = (tokens / 8, groups / BC_GCH, batch)
 
+// One warp per (batch, token, run of up to BC_GCH groups); the grid carries batch and the run, so no
+// index is divided at run time.  The next record's logits are requested before the current one is
+// evaluated.  (The kernels are bound by instruction issue and the XU pipe - five to six MUFU operations per
+// complex pair - not by DRAM.)
 template <typename T>
 __global__ void __launch_bounds__(256) bc_fwd_vec_kernel(const T* __restrict__ bc, T* __restrict__ Bo,
-                                                         T* __restrict__ Co, int batch, int Tn,
-                                                         int G, int N, float eps) {
+                                                         T* __restrict__ Co, int Tn, int G, int N, float eps) {
   constexpr bool FAST = sizeof(T) == 2;
   const int lane = threadIdx.x & 31, which = lane >> 4, n0 = 4 * (lane & 15);
-  const unsigned rows = (unsigned)batch * (unsigned)Tn * (unsigned)G;   // < 2^31, checked by the launcher
-  const unsigned row0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * BC_RPW;
-  if (row0 >= rows) return;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), b = blockIdx.z;
+  const int g0 = blockIdx.y * BC_GCH, g1 = min(G, g0 + BC_GCH);
+  if (t >= Tn) return;
   const bool act = n0 < N;
-  float amp[BC_RPW][4], ph[BC_RPW][4];
-#pragma unroll
-  for (int r = 0; r < BC_RPW; ++r) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { amp[r][i] = 0.f; ph[r][i] = 0.f; }
-    if (act && row0 + r < rows) {
-      const T* src = bc + (size_t)(row0 + r) * 4 * N + (size_t)(2 * which) * N + n0;
-      load4<T>(src, amp[r]);
-      load4<T>(src + N, ph[r]);
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < BC_RPW; ++r) {
-    const unsigned row = row0 + r;
+  const T* src = bc + (((size_t)b * Tn + t) * G + g0) * 4 * N + (size_t)(2 * which) * N + n0;
+  T* dst = (which ? Co : Bo) + (((size_t)b * G + g0) * Tn + t) * 2 * N + 2 * n0;
+  const size_t dstep = (size_t)Tn * 2 * N;
+  const float inv_n = 1.f / (float)N;
+  float amp[4] = {0.f, 0.f, 0.f, 0.f}, ph[4] = {0.f, 0.f, 0.f, 0.f};
+  if (act) { load4<T>(src, amp); load4<T>(src + N, ph); }
+  for (int g = g0; g < g1; ++g) {
+    float namp[4] = {0.f, 0.f, 0.f, 0.f}, nph[4] = {0.f, 0.f, 0.f, 0.f};
+    src += 4 * N;
+    if (act && g + 1 < g1) { load4<T>(src, namp); load4<T>(src + N, nph); }
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      amp[r][i] = act ? softplus_v<FAST>(amp[r][i]) : 0.f;
-      ss += amp[r][i] * amp[r][i];
+      amp[i] = act ? softplus_v<FAST>(amp[i]) : 0.f;
+      ss += amp[i] * amp[i];
     }
     ss = half_warp_sum(ss);
-    if (!act || row >= rows) continue;
-    const float inv = rsqrtf(fmaxf(ss / (float)N, eps));
-    float o[8];
+    if (act) {
+      const float inv = rsqrtf(fmaxf(ss * inv_n, eps));
+      float o[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float sn, cs;
-      sincos_v<FAST>(3.14159265358979323846f * tanh_v<FAST>(ph[r][i]), &sn, &cs);
-      const float a = amp[r][i] * inv;
-      o[2 * i] = a * cs; o[2 * i + 1] = a * sn;
+      for (int i = 0; i < 4; ++i) {
+        float sn, cs;
+        sincos_v<FAST>(3.14159265358979323846f * tanh_v<FAST>(ph[i]), &sn, &cs);
+        const float a = amp[i] * inv;
+        o[2 * i] = a * cs; o[2 * i + 1] = a * sn;
+      }
+      store8<T>(dst, o);
     }
-    const int g = (int)(row % (unsigned)G);
-    const unsigned bt = row / (unsigned)G;
-    const int t = (int)(bt % (unsigned)Tn), b = (int)(bt / (unsigned)Tn);
-    T* dst = (which ? Co : Bo) + (((size_t)b * G + g) * Tn + t) * 2 * N + 2 * n0;
-    store8<T>(dst, o);
+    dst += dstep;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { amp[i] = namp[i]; ph[i] = nph[i]; }
   }
 }
 
@@ -670,69 +669,67 @@ template <typename T>
 __global__ void __launch_bounds__(256) bc_bwd_vec_kernel(const T* __restrict__ bc,
                                                          const T* __restrict__ dBo,
                                                          const T* __restrict__ dCo,
-                                                         T* __restrict__ dbc, int batch, int Tn,
-                                                         int G, int N, float eps) {
+                                                         T* __restrict__ dbc, int Tn, int G, int N, float eps) {
   constexpr bool FAST = sizeof(T) == 2;
-  constexpr int RPW = BC_RPW;
   const int lane = threadIdx.x & 31, which = lane >> 4, n0 = 4 * (lane & 15);
-  const unsigned rows = (unsigned)batch * (unsigned)Tn * (unsigned)G;   // < 2^31, checked by the launcher
-  const unsigned row0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW;
-  if (row0 >= rows) return;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), b = blockIdx.z;
+  const int g0 = blockIdx.y * BC_GCH, g1 = min(G, g0 + BC_GCH);
+  if (t >= Tn) return;
   const bool act = n0 < N;
-  float xa[RPW][4], xp[RPW][4], gr[RPW][8];
+  const size_t in_off = (((size_t)b * Tn + t) * G + g0) * 4 * N + (size_t)(2 * which) * N + n0;
+  const T* src = bc + in_off;
+  T* dst = dbc + in_off;
+  const T* grad = (which ? dCo : dBo) + (((size_t)b * G + g0) * Tn + t) * 2 * N + 2 * n0;
+  const size_t gstep = (size_t)Tn * 2 * N;
+  const float inv_n = 1.f / (float)N;
+  float xa[4] = {0.f, 0.f, 0.f, 0.f}, xp[4] = {0.f, 0.f, 0.f, 0.f}, gr[8];
 #pragma unroll
-  for (int r = 0; r < RPW; ++r) {
+  for (int i = 0; i < 8; ++i) gr[i] = 0.f;
+  if (act) { load4<T>(src, xa); load4<T>(src + N, xp); load8<T>(grad, gr); }
+  for (int g = g0; g < g1; ++g) {
+    float nxa[4] = {0.f, 0.f, 0.f, 0.f}, nxp[4] = {0.f, 0.f, 0.f, 0.f}, ngr[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { xa[r][i] = 0.f; xp[r][i] = 0.f; }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) gr[r][i] = 0.f;
-    const unsigned row = row0 + r;
-    if (act && row < rows) {
-      const int g = (int)(row % (unsigned)G);
-      const unsigned bt = row / (unsigned)G;
-      const int t = (int)(bt % (unsigned)Tn), b = (int)(bt / (unsigned)Tn);
-      const size_t off = (size_t)row * 4 * N + (size_t)(2 * which) * N + n0;
-      load4<T>(bc + off, xa[r]);
-      load4<T>(bc + off + N, xp[r]);
-      load8<T>((which ? dCo : dBo) + (((size_t)b * G + g) * Tn + t) * 2 * N + 2 * n0, gr[r]);
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    const unsigned row = row0 + r;
+    for (int i = 0; i < 8; ++i) ngr[i] = 0.f;
+    src += 4 * N; grad += gstep;
+    if (act && g + 1 < g1) { load4<T>(src, nxa); load4<T>(src + N, nxp); load8<T>(grad, ngr); }
     float a[4], th[4], sn[4], cs[4];
     float ss = 0.f, gsum = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      a[i] = act ? softplus_v<FAST>(xa[r][i]) : 0.f;
-      th[i] = tanh_v<FAST>(xp[r][i]);
+      a[i] = act ? softplus_v<FAST>(xa[i]) : 0.f;
+      th[i] = tanh_v<FAST>(xp[i]);
       sincos_v<FAST>(3.14159265358979323846f * th[i], &sn[i], &cs[i]);
       ss += a[i] * a[i];
-      gsum += a[i] * (cs[i] * gr[r][2 * i] + sn[i] * gr[r][2 * i + 1]);
+      gsum += a[i] * (cs[i] * gr[2 * i] + sn[i] * gr[2 * i + 1]);
     }
     ss = half_warp_sum(ss); gsum = half_warp_sum(gsum);
-    if (!act || row >= rows) continue;
-    const float ms = ss / (float)N;
-    const float inv = rsqrtf(fmaxf(ms, eps));
-    const float g_ms = ms > eps ? -0.5f * inv * inv * inv * gsum : 0.f;
-    float da[4], dp[4];
+    if (act) {
+      const float ms = ss * inv_n;
+      const float inv = rsqrtf(fmaxf(ms, eps));
+      const float g_ms = ms > eps ? -0.5f * inv * inv * inv * gsum : 0.f;
+      float da[4], dp[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float gre = gr[r][2 * i], gim = gr[r][2 * i + 1];
-      const float g_amp = inv * (cs[i] * gre + sn[i] * gim) + g_ms * 2.f * a[i] / (float)N;
-      const float g_ph = a[i] * inv * (cs[i] * gim - sn[i] * gre);
-      da[i] = g_amp * sigmoid_v<FAST>(xa[r][i]);
-      dp[i] = g_ph * 3.14159265358979323846f * (1.f - th[i] * th[i]);
+      for (int i = 0; i < 4; ++i) {
+        const float gre = gr[2 * i], gim = gr[2 * i + 1];
+        const float g_amp = inv * (cs[i] * gre + sn[i] * gim) + g_ms * 2.f * a[i] * inv_n;
+        const float g_ph = a[i] * inv * (cs[i] * gim - sn[i] * gre);
+        da[i] = g_amp * sigmoid_v<FAST>(xa[i]);
+        dp[i] = g_ph * 3.14159265358979323846f * (1.f - th[i] * th[i]);
+      }
+      store4<T>(dst, da);
+      store4<T>(dst + N, dp);
     }
-    const size_t off = (size_t)row * 4 * N + (size_t)(2 * which) * N + n0;
-    store4<T>(dbc + off, da);
-    store4<T>(dbc + off + N, dp);
+    dst += 4 * N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { xa[i] = nxa[i]; xp[i] = nxp[i]; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gr[i] = ngr[i];
   }
 }
 
-inline bool bc_vec_ok(long long rows, int N, const void* a, const void* b, const void* c, const void* d) {
-  return rows < (1ll << 31) && N % 4 == 0 && N <= 64 && aligned(a, 16) && aligned(b, 16) && aligned(c, 16) &&
-         (d == nullptr || aligned(d, 16));
+inline bool bc_vec_ok(int batch, int groups, int N, const void* a, const void* b, const void* c, const void* d) {
+  return batch <= 65535 && (groups + BC_GCH - 1) / BC_GCH <= 65535 && N % 4 == 0 && N <= 64 && aligned(a, 16) &&
+         aligned(b, 16) && aligned(c, 16) && (d == nullptr || aligned(d, 16));
 }
 
 // (the coefficient arithmetic - zc, CoeffOut, wrap_angle_f, coeff_eval - lives in scanprep_math.cuh)
@@ -854,12 +851,14 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     if (!Bo || !Co || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    const bool vec = bc_vec_ok(rows, N, bc, Bo, Co, nullptr);
-    const unsigned nblk = vec ? (unsigned)((rows + 8 * BC_RPW - 1) / (8 * BC_RPW)) : blocks;
+    const dim3 vgrid((T + 7) / 8, (groups + BC_GCH - 1) / BC_GCH, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
-      auto k = vec ? bc_fwd_vec_kernel<Tt> : bc_fwd_kernel<Tt>;
-      k<<<nblk, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
-                                reinterpret_cast<Tt*>(Co), batch, T, groups, N, cfg->eps);
+      if (bc_vec_ok(batch, groups, N, bc, Bo, Co, nullptr))
+        bc_fwd_vec_kernel<Tt><<<vgrid, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
+                                                     reinterpret_cast<Tt*>(Co), T, groups, N, cfg->eps);
+      else
+        bc_fwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
+                                                  reinterpret_cast<Tt*>(Co), batch, T, groups, N, cfg->eps);
     });
     note_launches(1);
   }
@@ -915,13 +914,17 @@ extern "C" int sl_scanprep_conv_bwd(
     if (!dCo || !bc || !d_bc || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    const bool vec = bc_vec_ok(rows, N, bc, dBo, dCo, d_bc);
-    const unsigned nblk = vec ? (unsigned)((rows + 8 * BC_RPW - 1) / (8 * BC_RPW)) : blocks;
+    const dim3 vgrid((T + 7) / 8, (groups + BC_GCH - 1) / BC_GCH, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
-      auto k = vec ? bc_bwd_vec_kernel<Tt> : bc_bwd_kernel<Tt>;
-      k<<<nblk, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<const Tt*>(dBo),
-                                reinterpret_cast<const Tt*>(dCo), reinterpret_cast<Tt*>(d_bc), batch, T,
-                                groups, N, cfg->eps);
+      if (bc_vec_ok(batch, groups, N, bc, dBo, dCo, d_bc))
+        bc_bwd_vec_kernel<Tt><<<vgrid, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc),
+                                                     reinterpret_cast<const Tt*>(dBo),
+                                                     reinterpret_cast<const Tt*>(dCo), reinterpret_cast<Tt*>(d_bc),
+                                                     T, groups, N, cfg->eps);
+      else
+        bc_bwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<const Tt*>(dBo),
+                                                  reinterpret_cast<const Tt*>(dCo), reinterpret_cast<Tt*>(d_bc),
+                                                  batch, T, groups, N, cfg->eps);
     });
     note_launches(1);
   }
