@@ -373,6 +373,126 @@ __global__ void __launch_bounds__(TAIL_THREADS) tail_bwd_vec_kernel(TailParams p
   }
 }
 
+// The common width (heads * P <= 256 pieces of 16 bytes: one piece per thread) with fewer live registers,
+// so that three CTAs stay resident per SM: the row is kept as its four packed pieces and unpacked again
+// after the reduction (same operations, same roundings), both row sums travel in one reduction, and its
+// shared-memory slots alternate with the row so that one barrier per row is enough.
+template <typename T>
+__global__ void __launch_bounds__(TAIL_THREADS, 3) tail_bwd_row_kernel(TailParams p) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float2 s_red[2][TAIL_THREADS / 32];
+  const int C = p.H * p.P;
+  const T* Y = reinterpret_cast<const T*>(p.Y);
+  const T* S = reinterpret_cast<const T*>(p.skip);
+  const T* gate = reinterpret_cast<const T*>(p.gate);
+  const T* dn = reinterpret_cast<const T*>(p.dn);
+  T* dY = reinterpret_cast<T*>(p.dY);
+  T* dgate = reinterpret_cast<T*>(p.dgate);
+  T* dS = reinterpret_cast<T*>(p.dskip_in);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = threadIdx.x * V;
+  const bool act = c < C;
+  const int hh = act ? c / p.P : 0, pp = c - hh * p.P;
+  const float dsk = (act && S) ? p.d_skip[hh] : 0.f;
+  uint4 wraw = make_uint4(0, 0, 0, 0);
+  if (act) wraw = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.w) + c);
+  float dw_acc[V], dsk_acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < V; ++k) dw_acc[k] = 0.f;
+  const unsigned rows = (unsigned)p.batch * (unsigned)p.T;   // < 2^31, checked by the launcher
+  const size_t head_off = (size_t)hh * p.T * p.P + pp, batch_step = (size_t)p.H * p.T * p.P;
+  uint4 nY = make_uint4(0, 0, 0, 0), nG = nY, nS = nY, nD = nY;
+  auto fetch = [&](unsigned row) {
+    if (!act) return;
+    const unsigned b = row / (unsigned)p.T, t = row - b * (unsigned)p.T;
+    const size_t yi = b * batch_step + head_off + (size_t)t * p.P;
+    nY = *reinterpret_cast<const uint4*>(Y + yi);
+    nG = *reinterpret_cast<const uint4*>(gate + (size_t)row * p.gs + c);
+    nD = *reinterpret_cast<const uint4*>(dn + (size_t)row * C + c);
+    if (S) nS = *reinterpret_cast<const uint4*>(S + yi);
+  };
+  if (blockIdx.x < rows) fetch(blockIdx.x);
+  int par = 0;
+  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+    const uint4 cY = nY, cG = nG, cS = nS, cD = nD;
+    if (row + gridDim.x < rows) fetch(row + gridDim.x);
+    float ss = 0.f, dot = 0.f;
+    if (act) {
+      float pre[V], g[V], dnv[V], wv[V];
+      unpack16<T>(cY, pre); unpack16<T>(cG, g); unpack16<T>(cD, dnv); unpack16<T>(wraw, wv);
+      if (S) {
+        float sv[V];
+        unpack16<T>(cS, sv);
+#pragma unroll
+        for (int k = 0; k < V; k += 2) {
+          pre[k] += sv[k] * dsk; pre[k + 1] += sv[k + 1] * dsk;
+          round_pair<T>(pre[k], pre[k + 1]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < V; k += 2) {
+        float h0 = pre[k] * silu_f(g[k]), h1 = pre[k + 1] * silu_f(g[k + 1]);
+        round_pair<T>(h0, h1);
+        ss += h0 * h0 + h1 * h1;
+        dot += h0 * dnv[k] * wv[k] + h1 * dnv[k + 1] * wv[k + 1];
+      }
+    }
+    ss = warp_sum(ss); dot = warp_sum(dot);
+    if (lane == 0) s_red[par][warp] = make_float2(ss, dot);
+    __syncthreads();
+    ss = 0.f; dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < TAIL_THREADS / 32; ++k) { const float2 v = s_red[par][k]; ss += v.x; dot += v.y; }
+    const float rstd = rsqrtf(ss / (float)C + p.eps);
+    const float coef = dot * rstd * rstd * rstd / (float)C;
+    if (act) {
+      const unsigned b = row / (unsigned)p.T, t = row - b * (unsigned)p.T;
+      const size_t yi = b * batch_step + head_off + (size_t)t * p.P;
+      float pre[V], g[V], dnv[V], wv[V], sv[V];
+      unpack16<T>(cY, pre); unpack16<T>(cG, g); unpack16<T>(cD, dnv); unpack16<T>(wraw, wv);
+      if (S) {
+        unpack16<T>(cS, sv);
+#pragma unroll
+        for (int k = 0; k < V; k += 2) {
+          pre[k] += sv[k] * dsk; pre[k + 1] += sv[k + 1] * dsk;
+          round_pair<T>(pre[k], pre[k + 1]);
+        }
+      }
+      float o_dy[V], o_dg[V], o_ds[V];
+#pragma unroll
+      for (int k2 = 0; k2 < V; k2 += 2) {
+        float sgv[2], hidv[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          sgv[q] = sigmoid_f(g[k2 + q]);
+          hidv[q] = pre[k2 + q] * silu_f(g[k2 + q]);
+        }
+        round_pair<T>(hidv[0], hidv[1]);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int k = k2 + q;
+          const float gg = g[k], sg = sgv[q], hid = hidv[q];
+          dw_acc[k] += dnv[k] * hid * rstd;
+          const float dh = rstd * dnv[k] * wv[k] - hid * coef;
+          const float dpre = dh * gg * sg;
+          o_dg[k] = dh * pre[k] * sg * (1.f + gg * (1.f - sg));
+          o_dy[k] = dpre;
+          o_ds[k] = 0.f;
+          if (S) { o_ds[k] = dpre * dsk; dsk_acc += dpre * sv[k]; }
+        }
+      }
+      store16<T>(dgate + (size_t)row * C + c, o_dg);
+      store16<T>(dY + yi, o_dy);
+      if (S && dS) store16<T>(dS + yi, o_ds);
+    }
+  }
+  if (act) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) atomicAdd(p.d_w + c + k, dw_acc[k]);
+    if (S && p.d_d_skip) atomicAdd(p.d_d_skip + hh, dsk_acc);
+  }
+}
+
 template <typename T>
 bool tail_vec_ok(const TailParams& p) {
   constexpr int V = Vec16<T>::N;
@@ -434,11 +554,12 @@ extern "C" int sl_mixer_tail_bwd(const void* Y, const void* gate, int64_t gate_r
   p.batch = batch; p.H = heads; p.T = T; p.P = P;
   const long long rows = (long long)batch * T;
   const unsigned grid = (unsigned)(rows < 148 * 2 ? rows : 148 * 2);   // two resident CTAs per SM
+  const unsigned grid3 = (unsigned)(rows < 148 * 3 ? rows : 148 * 3);  // three for the one-piece kernel
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)heads * sizeof(float);
   SL_DISPATCH_DTYPE(io_dtype, Tt, {
     if (tail_vec_ok<Tt>(p)) {
-      if ((long long)heads * P <= TAIL_THREADS * Vec16<Tt>::N) tail_bwd_vec_kernel<Tt, 1><<<grid, TAIL_THREADS, 0, st>>>(p);
+      if ((long long)heads * P <= TAIL_THREADS * Vec16<Tt>::N) tail_bwd_row_kernel<Tt><<<grid3, TAIL_THREADS, 0, st>>>(p);
       else tail_bwd_vec_kernel<Tt, 2><<<grid, TAIL_THREADS, 0, st>>>(p);
     } else tail_bwd_kernel<Tt><<<grid, TAIL_THREADS, smem, st>>>(p);
   });
