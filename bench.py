@@ -24,7 +24,8 @@ JSON line:
   others                the other configurations of the hot path, measured on rank 0's GPU after the
                         headline legs: config 3 (decode of 1024 consecutive tokens, eager and as
                         one CUDA graph) and config 2 (the mixer layer forward+backward and its four
-                        row-kernel calls; under --gpus N every rank owns batch 8/N of it)
+                        row-kernel calls; under --gpus N every rank owns batch 8/N of it) and, at
+                        N=1, the config-1 streams with 128 state columns (the mixer's default)
 
 ``--impl reference`` times only that CPU port on WHOLE steps of the same workload with all host
 threads (set explicitly: a launcher may export OMP_NUM_THREADS=1) and prints the same line with
@@ -405,6 +406,7 @@ def main():
             "config2_mixer": measure.measure_mixer(12, dev, batch=bshare)
                              + measure.measure_scanprep(10, dev, batch=bshare)
                              + measure.measure_tail(10, dev, batch=bshare),
+            "scan_d_state_128": measure.measure_scan_n128(10, dev) if world == 1 else None,
             "note": "config 3: 1024 consecutive tokens, fresh inputs per token; config 2: batch "
                     f"{bshare} per GPU (8 sharded over {world} rank(s)); figures of rank 0's GPU",
         }
