@@ -52,27 +52,26 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const T* __restrict__ 
 }
 
 // dx = rstd (g - xhat mean(g xhat)),  g = dy w,  xhat = x rstd;   dw += sum_rows dy xhat.
-// A CTA walks its rows (grid-stride), one warp per row with x and dy packed in registers; each lane keeps
-// its part of dw in float registers across rows, the CTA sums them in shared memory and issues one float
-// atomic per channel at the end.  The weight sits packed in shared memory.
+// A CTA walks its rows (grid-stride), one warp per row with x and dy packed in registers; every warp adds
+// its rows' part of dw into a float row of its own in shared memory (plain 16-byte read-modify-writes: 128
+// wavefronts per row against the ~280 cycles the row's bytes take at the SM's share of the HBM bandwidth),
+// and the CTA sums the warps' rows and issues one global float atomic per channel at the end.  Keeping dw
+// out of the registers leaves room for two CTAs per SM (shared-memory float atomics into one row were
+// slower than this, and dw in registers allowed one CTA per SM).  The weight sits packed in shared memory.
 template <typename T, int MAXP>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
+__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                           const T* __restrict__ dy, T* __restrict__ dx,
                                                           float* __restrict__ dw, long long rows, int C, float eps) {
   constexpr int V = Vec16<T>::N;
   extern __shared__ __align__(16) unsigned char s_raw[];
-  float* s_dw = reinterpret_cast<float*>(s_raw);                        // [C]
-  uint4* s_w = reinterpret_cast<uint4*>(s_raw + (size_t)C * sizeof(float));   // [C / V]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float* s_dw = reinterpret_cast<float*>(s_raw);                        // [nw][C]
+  uint4* s_w = reinterpret_cast<uint4*>(s_raw + (size_t)nw * C * sizeof(float));   // [C / V]
+  float* my_dw = s_dw + (size_t)warp * C;
   const int pieces = C / V;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) s_dw[c] = 0.f;
+  for (int c = threadIdx.x; c < nw * C; c += blockDim.x) s_dw[c] = 0.f;
   for (int c = threadIdx.x; c < pieces; c += blockDim.x) s_w[c] = reinterpret_cast<const uint4*>(w)[c];
   __syncthreads();
-  float dwv[MAXP][V];
-#pragma unroll
-  for (int i = 0; i < MAXP; ++i)
-#pragma unroll
-    for (int k = 0; k < V; ++k) dwv[i][k] = 0.f;
   for (long long row = (long long)blockIdx.x * nw + warp; row < rows; row += (long long)gridDim.x * nw) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + row * C);
@@ -103,32 +102,45 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ 
         float xv[V], gv[V], wv[V], o[V];
         unpack16<T>(xraw[i], xv); unpack16<T>(graw[i], gv); unpack16<T>(s_w[pc], wv);
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          dwv[i][k] += gv[k] * (xv[k] * rstd);
-          o[k] = rstd * (gv[k] * wv[k] - xv[k] * coef);
+        float4* acc = reinterpret_cast<float4*>(my_dw + pc * V);
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q) {
+          float4 a = acc[q];
+          a.x += gv[4 * q] * (xv[4 * q] * rstd); a.y += gv[4 * q + 1] * (xv[4 * q + 1] * rstd);
+          a.z += gv[4 * q + 2] * (xv[4 * q + 2] * rstd); a.w += gv[4 * q + 3] * (xv[4 * q + 3] * rstd);
+          acc[q] = a;
         }
+#pragma unroll
+        for (int k = 0; k < V; ++k) o[k] = rstd * (gv[k] * wv[k] - xv[k] * coef);
         store16<T>(dx + row * C + pc * V, o);
       }
     }
   }
-#pragma unroll
-  for (int i = 0; i < MAXP; ++i) {
-    const int pc = lane + 32 * i;
-    if (pc < pieces)
-#pragma unroll
-      for (int k = 0; k < V; ++k) atomicAdd(&s_dw[pc * V + k], dwv[i][k]);
-  }
   __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) atomicAdd(dw + c, s_dw[c]);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float v = 0.f;
+    for (int q = 0; q < nw; ++q) v += s_dw[(size_t)q * C + c];
+    atomicAdd(dw + c, v);
+  }
 }
 
-__device__ __forceinline__ float gelu_tanh_f(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.f + tanhf(u));
+// 16-bit rows take the one-instruction tanh (relative error 2^-11, below the rounding of the output);
+// float32 rows the precise one.
+template <bool FAST> __device__ __forceinline__ float tanh_io(float x) {
+  if (FAST) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  return tanhf(x);
 }
-__device__ __forceinline__ float dgelu_tanh_f(float x) {
+template <bool FAST> __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = tanhf(u);
+  return 0.5f * x * (1.f + tanh_io<FAST>(u));
+}
+template <bool FAST> __device__ __forceinline__ float dgelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = tanh_io<FAST>(u);
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * x * x);
 }
 
@@ -147,7 +159,7 @@ __global__ void __launch_bounds__(256) ffn_act_fwd_kernel(const T* __restrict__ 
   if (kind == 0) {
     load16<T>(proj + row * H + pc * V, a);
 #pragma unroll
-    for (int k = 0; k < V; ++k) o[k] = gelu_tanh_f(a[k]);
+    for (int k = 0; k < V; ++k) o[k] = gelu_tanh_f<sizeof(T) == 2>(a[k]);
   } else {
     float g[V];
     load16<T>(proj + row * 2 * H + pc * V, a);
@@ -172,7 +184,7 @@ __global__ void __launch_bounds__(256) ffn_act_bwd_kernel(const T* __restrict__ 
   if (kind == 0) {
     load16<T>(proj + row * H + pc * V, a);
 #pragma unroll
-    for (int k = 0; k < V; ++k) o[k] = d[k] * dgelu_tanh_f(a[k]);
+    for (int k = 0; k < V; ++k) o[k] = d[k] * dgelu_tanh_f<sizeof(T) == 2>(a[k]);
     store16<T>(dproj + row * H + pc * V, o);
   } else {
     float g[V], og[V];
@@ -227,11 +239,14 @@ extern "C" int sl_rmsnorm_bwd(const void* x, const void* weight, float eps, cons
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long want = (rows + 7) / 8;
   const bool narrow = C / (io_dtype == SL_F32 ? 4 : 8) <= 32 * RMS_MAXP_NARROW;
-  const long long cap = narrow ? 148 * 4 : 148 * 2;   // CTAs that walk the rows; the wide form holds one per SM
+  const long long cap = narrow ? 148 * 4 : 148 * 2;   // CTAs that walk the rows: all resident at once
   const unsigned grid = (unsigned)(want < cap ? want : cap);
-  const size_t smem = (size_t)C * sizeof(float) + (size_t)C * dtype_size(io_dtype);
+  const size_t smem = (size_t)8 * C * sizeof(float) + (size_t)C * dtype_size(io_dtype);   // 8 warps' dw rows + w
   SL_DISPATCH_DTYPE(io_dtype, T, {
     auto kern = narrow ? rmsnorm_bwd_kernel<T, RMS_MAXP_NARROW> : rmsnorm_bwd_kernel<T, RMS_MAXP>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return SL_ERR_LAUNCH_FAILED;
     kern<<<grid, 256, smem, st>>>(
         reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(weight), reinterpret_cast<const T*>(d_out),
         reinterpret_cast<T*>(d_x), d_weight, rows, C, eps);

@@ -1,5 +1,5 @@
-"""Channel-mixing FFN of a block (plain torch + library GEMMs; outside the scan
-hot path).  Same constructor surface and state_dict keys as the reference's
+"""Channel-mixing FFN of a block (library GEMMs; the activation runs on this
+package's row kernel on CUDA, plain torch elsewhere).  Same constructor surface and state_dict keys as the reference's
 ``SLinOSSMLP`` (slinoss/layers/mlp.py:37-166)."""
 
 from __future__ import annotations
@@ -60,6 +60,9 @@ class SLinOSSMLP(nn.Module):
         if x.shape[-1] != self.d_model:
             raise ValueError(f"Expected last dim {self.d_model}, got {int(x.shape[-1])}.")
         h = self.in_proj(x)
+        from ..ops.block import ffn_activation, ffn_activation_supported   # (ops.block imports nothing of layers)
+        if ffn_activation_supported(h, self.kind):
+            return self.out_proj(ffn_activation(h, self.kind))
         if self.kind == "swiglu":
             value, gate = h.chunk(2, dim=-1)
             return self.out_proj(value * F.silu(gate))

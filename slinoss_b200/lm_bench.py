@@ -40,6 +40,23 @@ def timed_steps(trainer, ids, steps, warmup, barrier):
     return e0.elapsed_time(e1) / steps, [float(x) for x in losses]
 
 
+def kernel_table(trainer, ids, rows: int, steps: int = 2) -> None:
+    """Device time per kernel over ``steps`` training steps: ms per step, share, launches per step."""
+    import sys
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(steps):
+            trainer.step(ids)
+        torch.cuda.synchronize()
+    table = [(e.device_time_total / (1e3 * steps), e.count // steps, e.key)
+             for e in prof.key_averages() if e.device_time_total > 0 and e.device_type.name == "CUDA"]
+    table.sort(reverse=True)
+    total = sum(t for t, _, _ in table)
+    print(f"device time per step {total:.1f} ms", file=sys.stderr)
+    for t, n, key in table[:rows]:
+        print(f"{t:8.2f} ms {100 * t / total:5.1f}% x{n:5d} {key[:120]}", file=sys.stderr)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=0, help="informational; the launcher sets WORLD_SIZE")
@@ -53,6 +70,9 @@ def main():
     ap.add_argument("--bucket-mb", type=int, default=32)
     ap.add_argument("--ffn-remat", choices=["full", "rows", "none"], default=None,
                     help="what the FFN branch rebuilds in the backward pass (default: the block's own)")
+    ap.add_argument("--kernel-table", type=int, default=0, metavar="ROWS",
+                    help="after the timed steps, profile two more steps (torch profiler) on rank 0 and print "
+                         "the ROWS kernels with the most device time to stderr")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -96,6 +116,8 @@ def main():
     else:
         n_buckets = 0
     mem_gb = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    if args.kernel_table > 0 and rank == 0 and world == 1:
+        kernel_table(trainer, ids, args.kernel_table)
     if rank == 0:
         tokens = world * args.batch_per_gpu * args.seq
         line = {

@@ -336,6 +336,26 @@ def measure_scan(iters, dev):
                                                chunk_size=64), iters), bht * 1456, name)]
 
 
+def measure_ffn_rows(iters, dev, rows=16384, C=2048, hidden=8192):
+    """Row-wise kernels of the FFN branch at the stacked-LM size: 4 x 4096 rows of d_model 2048, hidden 8192."""
+    from . import _C
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(rows, C, generator=g).to(torch.bfloat16).to(dev)
+    dy = torch.randn(rows, C, generator=g).to(torch.bfloat16).to(dev)
+    w = torch.ones(C, dtype=torch.bfloat16, device=dev)
+    proj = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).to(dev)
+    dh = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).to(dev)
+    name = f"config 4 rows: {rows} x d_model {C} (hidden {hidden}), bf16"
+    rc, rh = rows * C * 2, rows * hidden * 2
+    return [report("sl_rmsnorm_fwd", time_ms(lambda: _C.rmsnorm_fwd(x, w, 1e-5), iters), 2 * rc, name),
+            report("sl_rmsnorm_bwd (includes zeroing of d_weight)",
+                   time_ms(lambda: _C.rmsnorm_bwd(x, w, 1e-5, dy), iters), 3 * rc, name),
+            report("sl_ffn_activation_fwd (GELU)", time_ms(lambda: _C.ffn_activation_fwd(proj, "gelu"), iters),
+                   2 * rh, name),
+            report("sl_ffn_activation_bwd (GELU)", time_ms(lambda: _C.ffn_activation_bwd(proj, dh, "gelu"), iters),
+                   3 * rh, name)]
+
+
 def measure_scan_n128(iters, dev):
     """The config-1 streams with 128 state columns (the mixer's default d_state): two passes over the
     column blocks of B and C."""
@@ -353,13 +373,13 @@ def measure_scan_n128(iters, dev):
                                                chunk_size=64, saved=(st, fin)), iters), bht * 2480, name)]
 
 
-WHAT = {"scan_n128": measure_scan_n128, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
+WHAT = {"scan_n128": measure_scan_n128, "ffn_rows": measure_ffn_rows, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
         "scanprep": measure_scanprep, "tail": measure_tail, "mixer": measure_mixer, "scan": measure_scan}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="decode,decode_sequence,mixer_step,scanprep,tail,mixer,scan,scan_n128")
+    ap.add_argument("--what", default="decode,decode_sequence,mixer_step,scanprep,tail,mixer,scan,scan_n128,ffn_rows")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():

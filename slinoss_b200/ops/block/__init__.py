@@ -32,6 +32,37 @@ def residual_add(residual, branch, in_fp32: bool):
     return residual.to(dt).add(branch.to(dt)).to(dtype=residual.dtype)
 
 
+class _FFNActivationFn(torch.autograd.Function):
+    """The FFN activation on the row kernels, keeping the projection for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, projected, kind):
+        projected = projected.contiguous()
+        ctx.save_for_backward(projected)
+        ctx.kind = kind
+        return _C.ffn_activation_fwd(projected, kind)
+
+    @staticmethod
+    def backward(ctx, d_hidden):
+        (projected,) = ctx.saved_tensors
+        return _C.ffn_activation_bwd(projected, d_hidden.contiguous(), ctx.kind), None
+
+
+def ffn_activation_supported(projected, kind: str) -> bool:
+    if not projected.is_cuda or projected.dtype not in _C._DTYPE_CODE or torch.is_autocast_enabled():
+        return False
+    width = int(projected.shape[-1])
+    hidden = width // 2 if kind == "swiglu" else width
+    v = 4 if projected.dtype == torch.float32 else 8
+    return kind in _C.FFN_KINDS and projected.numel() > 0 and hidden % v == 0
+
+
+def ffn_activation(projected, kind: str):
+    """``gelu(projected, tanh form)`` or ``value * silu(gate)`` of ``projected = [value | gate]`` on the CUDA
+    row kernels (differentiable)."""
+    return _FFNActivationFn.apply(projected, kind)
+
+
 class _FFNResidualFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, norm_w, w1, b1, w2, b2, eps, kind, in_fp32, keep_projection):
@@ -98,4 +129,4 @@ def ffn_residual(x, norm, ffn, *, residual_in_fp32: bool = True, remat: str = "f
                                 remat == "rows")
 
 
-__all__ = ["ffn_residual", "ffn_residual_supported", "residual_add"]
+__all__ = ["ffn_activation", "ffn_activation_supported", "ffn_residual", "ffn_residual_supported", "residual_add"]

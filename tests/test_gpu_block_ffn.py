@@ -102,7 +102,7 @@ def test_ffn_branch_of_the_block_rematerialised_against_plain_autograd(dtype, ki
     out_f, dx_f, g_f = run(True)
     assert _C.kernel_launches() - launches == 6      # norm, act; norm, act, act', norm'
     out_p, dx_p, g_p = run(False)
-    assert _C.kernel_launches() - launches == 6 + 2  # the plain path: the norm's forward and backward only
+    assert _C.kernel_launches() - launches == 6 + 4  # the plain path: norm and activation, forward and backward
 
     # float64 evaluation of the same expression
     blk64 = _block(kind, bias, dtype, remat="none").double()
@@ -138,7 +138,7 @@ def test_plain_path_is_kept_for_layernorm_dropout_and_autocast():
     n0 = _C.kernel_launches()
     blk.ffn_remat = "none"
     blk._ffn_residual(x)
-    assert _C.kernel_launches() == n0 + 1        # the norm alone
+    assert _C.kernel_launches() == n0 + 2        # the norm and the activation
     blk.ffn_remat = "full"
     assert block_mod.ffn_residual_supported(x, blk.ffn_norm, blk.ffn)
     assert not block_mod.ffn_residual_supported(x.bfloat16(), blk.ffn_norm, blk.ffn)
@@ -149,7 +149,7 @@ def test_plain_path_is_kept_for_layernorm_dropout_and_autocast():
     blk.train()
     n0 = _C.kernel_launches()
     blk._ffn_residual(x)
-    assert _C.kernel_launches() == n0 + 1
+    assert _C.kernel_launches() == n0 + 2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -172,3 +172,23 @@ def test_rmsnorm_module_runs_on_the_row_kernels_and_matches_torch(dtype):
     assert rel(norm.weight.grad, w64.grad) <= TOL[dtype]
     # rows in another type than the weight: computed in the weight's type, returned in the rows'
     assert norm(x.detach().double()).dtype == torch.float64
+
+
+@pytest.mark.parametrize("kind", ["gelu", "swiglu"])
+def test_mlp_module_runs_its_activation_on_the_row_kernel(kind):
+    torch.manual_seed(7)
+    mlp = sb.SLinOSSMLP(256, kind=kind, expand=2.0, multiple_of=64, bias=True, device=DEV, dtype=torch.float32)
+    x = torch.randn(3, 17, 256, device=DEV, requires_grad=True)
+    dy = torch.randn(3, 17, 256, device=DEV)
+    n0 = _C.kernel_launches()
+    out = mlp(x)
+    out.backward(dy)
+    assert _C.kernel_launches() - n0 == 2
+    m64 = sb.SLinOSSMLP(256, kind=kind, expand=2.0, multiple_of=64, bias=True, device=DEV, dtype=torch.float64)
+    m64.load_state_dict({k: v.double() for k, v in mlp.state_dict().items()})
+    x64 = x.detach().double().requires_grad_()
+    out64 = m64(x64)
+    out64.backward(dy.double())
+    assert rel(out, out64) <= 1e-5 and rel(x.grad, x64.grad) <= 1e-5
+    for (n, p), q in zip(mlp.named_parameters(), m64.parameters()):
+        assert rel(p.grad, q.grad) <= 1e-5, n
