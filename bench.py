@@ -447,6 +447,8 @@ def main():
                                  "frac": ab["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak}},
             "clocks": clocks,
             "kernel_path": args.path,
+            # 0 unless a bounded device-side wait of the tensor-core kernels expired during this run
+            "device_status": _C.device_status(),
         }
         if others is not None:
             line["others"] = others

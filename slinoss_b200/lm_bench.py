@@ -23,6 +23,7 @@ import os
 import torch
 
 from . import shard
+from . import _C
 from .lm import DataParallelTrainer, SLinOSSLM, lm_stack_config
 
 
@@ -134,6 +135,7 @@ def main():
                           "bytes": 2 * n_params, "backend": "nccl" if world > 1 else None},
             "loss_first": losses[0], "loss_last": losses[args.warmup + args.steps - 1],
             "peak_memory_gb": mem_gb,
+            "device_status": _C.device_status(),   # 0 unless a bounded device-side wait expired
         }
         text = json.dumps(line)
         print(text, flush=True)
