@@ -67,26 +67,87 @@ __global__ void __launch_bounds__(256, 4) mixer_step_kernel(StepParams p) {
   const int g = h / (p.H / p.G);
   const size_t bg = (size_t)b * p.G + g;
 
-  // ---- A. conv update of this head's channels ------------------------------------------------
-  for (int pp = tid; pp < p.P; pp += blockDim.x) {
-    const int c = h * p.P + pp;
-    const T* wv = reinterpret_cast<const T*>(p.conv_w);
-    T* st = reinterpret_cast<T*>(p.conv_state) + ((size_t)b * C + c) * (p.W - 1);
-    const float x = to_f32(reinterpret_cast<const T*>(p.value)[(size_t)b * p.value_stride + c]);
-    float u = x;
-    if (wv) {
-      float a = p.conv_b ? to_f32(reinterpret_cast<const T*>(p.conv_b)[c]) : 0.f;
-      float win[4] = {0.f, 0.f, 0.f, 0.f};      // the carried inputs, oldest first
-      for (int j = 0; j < p.W - 1; ++j) { win[j] = to_f32(st[j]); a += to_f32(wv[(size_t)c * p.W + j]) * win[j]; }
-      a += to_f32(wv[(size_t)c * p.W + p.W - 1]) * x;
-      u = round_io<T>(silu_f(a));
-      for (int j = 0; j + 1 < p.W - 1; ++j) st[j] = from_f32<T>(win[j + 1]);
-      if (p.W > 1) st[p.W - 2] = from_f32<T>(x);
+  // ---- requests.  Nothing below depends on anything but the inputs until phase D, so every global value
+  // the phases A, C, D, E and F read is requested here, ahead of any arithmetic: the CTA then pays for one
+  // round trip to memory instead of one per phase (the phases are separated by barriers, and a CTA per
+  // (batch, head) has too little work to hide five of them).
+  float* state = p.state + (size_t)bh * p.P * D;
+  const bool rows8 = D == 128 && (p.P % (8 * nw)) == 0;   // N = 64: a state row is one float4 per lane
+  float4 z[8];
+  if (rows8) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) z[r] = reinterpret_cast<const float4*>(state + (size_t)(8 * w + r) * D)[lane];
+  }
+  const bool one_pass = p.P <= (int)blockDim.x && p.N <= 64;   // one channel / one b pair per thread
+  const T* convw = reinterpret_cast<const T*>(p.conv_w);
+  float r_x = 0.f, r_bias = 0.f, r_win[3] = {0.f, 0.f, 0.f}, r_wgt[4] = {0.f, 0.f, 0.f, 0.f};
+  float r_up = 0.f, r_gate = 0.f, r_dsk = 0.f, r_bp[2] = {0.f, 0.f}, r_bc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (one_pass) {
+    if (tid < p.P) {
+      const int c = h * p.P + tid;
+      r_x = to_f32(reinterpret_cast<const T*>(p.value)[(size_t)b * p.value_stride + c]);
+      r_gate = to_f32(reinterpret_cast<const T*>(p.gate)[(size_t)b * p.gate_stride + c]);
+      r_up = to_f32(reinterpret_cast<const T*>(p.u_prev)[(size_t)bh * p.P + tid]);
+      if (p.d_skip) r_dsk = p.d_skip[h];
+      if (convw) {
+        const T* st = reinterpret_cast<const T*>(p.conv_state) + ((size_t)b * C + c) * (p.W - 1);
+        if (p.conv_b) r_bias = to_f32(reinterpret_cast<const T*>(p.conv_b)[c]);
+        for (int j = 0; j < p.W - 1; ++j) r_win[j] = to_f32(st[j]);
+        for (int j = 0; j < p.W; ++j) r_wgt[j] = to_f32(convw[(size_t)c * p.W + j]);
+      }
     }
-    T* up = reinterpret_cast<T*>(p.u_prev) + (size_t)bh * p.P + pp;
-    s_u[pp] = u;
-    s_up[pp] = to_f32(*up);
-    *up = from_f32<T>(u);
+    if (w == 2 || w == 3) {
+      const T* src = reinterpret_cast<const T*>(p.bc) + bg * 4 * p.N + (size_t)(2 * (w - 2)) * p.N;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int n = lane + 32 * q;
+        if (n < p.N) { r_bc[2 * q] = to_f32(src[n]); r_bc[2 * q + 1] = to_f32(src[p.N + n]); }
+      }
+    }
+    if (tid >= 128 && tid < 128 + p.N && p.b_prev_in) {   // (warps 4, 5: not the ones busy with b and c)
+      const T* bpin = reinterpret_cast<const T*>(p.b_prev_in) + bg * D + 2 * (tid - 128);
+      r_bp[0] = to_f32(bpin[0]); r_bp[1] = to_f32(bpin[1]);
+    }
+  }
+
+  // ---- A. conv update of this head's channels ------------------------------------------------
+  if (one_pass) {
+    if (tid < p.P) {
+      const int c = h * p.P + tid;
+      float u = r_x;
+      if (convw) {
+        T* st = reinterpret_cast<T*>(p.conv_state) + ((size_t)b * C + c) * (p.W - 1);
+        float a = r_bias;
+        for (int j = 0; j < p.W - 1; ++j) a += r_wgt[j] * r_win[j];
+        a += r_wgt[p.W - 1] * r_x;
+        u = round_io<T>(silu_f(a));
+        for (int j = 0; j + 1 < p.W - 1; ++j) st[j] = from_f32<T>(r_win[j + 1]);
+        if (p.W > 1) st[p.W - 2] = from_f32<T>(r_x);
+      }
+      s_u[tid] = u;
+      s_up[tid] = r_up;
+      reinterpret_cast<T*>(p.u_prev)[(size_t)bh * p.P + tid] = from_f32<T>(u);
+    }
+  } else {
+    for (int pp = tid; pp < p.P; pp += blockDim.x) {
+      const int c = h * p.P + pp;
+      T* st = reinterpret_cast<T*>(p.conv_state) + ((size_t)b * C + c) * (p.W - 1);
+      const float x = to_f32(reinterpret_cast<const T*>(p.value)[(size_t)b * p.value_stride + c]);
+      float u = x;
+      if (convw) {
+        float a = p.conv_b ? to_f32(reinterpret_cast<const T*>(p.conv_b)[c]) : 0.f;
+        float win[4] = {0.f, 0.f, 0.f, 0.f};      // the carried inputs, oldest first
+        for (int j = 0; j < p.W - 1; ++j) { win[j] = to_f32(st[j]); a += to_f32(convw[(size_t)c * p.W + j]) * win[j]; }
+        a += to_f32(convw[(size_t)c * p.W + p.W - 1]) * x;
+        u = round_io<T>(silu_f(a));
+        for (int j = 0; j + 1 < p.W - 1; ++j) st[j] = from_f32<T>(win[j + 1]);
+        if (p.W > 1) st[p.W - 2] = from_f32<T>(x);
+      }
+      T* up = reinterpret_cast<T*>(p.u_prev) + (size_t)bh * p.P + pp;
+      s_u[pp] = u;
+      s_up[pp] = to_f32(*up);
+      *up = from_f32<T>(u);
+    }
   }
   // ---- B. transition and taps of this head (one thread; float64 inside) ------------------------
   if (tid == blockDim.x - 1) {
@@ -102,18 +163,39 @@ __global__ void __launch_bounds__(256, 4) mixer_step_kernel(StepParams p) {
   if (w == 2 || w == 3) {
     const int which = w - 2;      // 0: b (rows 0, 1 of bc), 1: c (rows 2, 3)
     const T* src = reinterpret_cast<const T*>(p.bc) + bg * 4 * p.N + (size_t)(2 * which) * p.N;
-    float ss = 0.f;
-    for (int n = lane; n < p.N; n += 32) { const float a = softplus_f(to_f32(src[n])); ss += a * a; }
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(fmaxf(ss / (float)p.N, p.cfg.eps));
     float* dst = which ? s_c : s_b;
-    for (int n = lane; n < p.N; n += 32) {
-      const float a = softplus_f(to_f32(src[n])) * inv;
-      const float ph = 3.14159265358979323846f * tanhf(to_f32(src[p.N + n]));
-      float sn, cs;
-      sincosf(ph, &sn, &cs);
-      dst[2 * n] = round_io<T>(a * cs);
-      dst[2 * n + 1] = round_io<T>(a * sn);
+    float ss = 0.f;
+    if (one_pass) {
+      float amp[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        amp[q] = lane + 32 * q < p.N ? softplus_f(r_bc[2 * q]) : 0.f;
+        ss += amp[q] * amp[q];
+      }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(fmaxf(ss / (float)p.N, p.cfg.eps));
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int n = lane + 32 * q;
+        if (n < p.N) {
+          float sn, cs;
+          sincosf(3.14159265358979323846f * tanhf(r_bc[2 * q + 1]), &sn, &cs);
+          dst[2 * n] = round_io<T>(amp[q] * inv * cs);
+          dst[2 * n + 1] = round_io<T>(amp[q] * inv * sn);
+        }
+      }
+    } else {
+      for (int n = lane; n < p.N; n += 32) { const float a = softplus_f(to_f32(src[n])); ss += a * a; }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(fmaxf(ss / (float)p.N, p.cfg.eps));
+      for (int n = lane; n < p.N; n += 32) {
+        const float a = softplus_f(to_f32(src[n])) * inv;
+        const float ph = 3.14159265358979323846f * tanhf(to_f32(src[p.N + n]));
+        float sn, cs;
+        sincosf(ph, &sn, &cs);
+        dst[2 * n] = round_io<T>(a * cs);
+        dst[2 * n + 1] = round_io<T>(a * sn);
+      }
     }
   }
   __syncthreads();
@@ -122,29 +204,37 @@ __global__ void __launch_bounds__(256, 4) mixer_step_kernel(StepParams p) {
     const cf kp = {s_coef[2], s_coef[3]}, kc = {s_coef[4], s_coef[5]};
     const T* bpin = reinterpret_cast<const T*>(p.b_prev_in);
     T* bpout = reinterpret_cast<T*>(p.b_prev_out);
-    for (int n = tid; n < p.N; n += blockDim.x) {
-      cf bp = {0.f, 0.f};
-      if (bpin) bp = {to_f32(bpin[bg * D + 2 * n]), to_f32(bpin[bg * D + 2 * n + 1])};
+    const bool hand_on = h % (p.H / p.G) == 0;
+    auto taps = [&](int n, cf bp) {
       const cf bt = {s_b[2 * n], s_b[2 * n + 1]};
       const cf a = cmul(kp, bp), c2 = cmul(kc, bt);
       s_bp[2 * n] = a.re; s_bp[2 * n + 1] = a.im;
       s_bc[2 * n] = c2.re; s_bc[2 * n + 1] = c2.im;
-      if (h % (p.H / p.G) == 0) { bpout[bg * D + 2 * n] = from_f32<T>(bt.re); bpout[bg * D + 2 * n + 1] = from_f32<T>(bt.im); }
+      if (hand_on) { bpout[bg * D + 2 * n] = from_f32<T>(bt.re); bpout[bg * D + 2 * n + 1] = from_f32<T>(bt.im); }
+    };
+    if (one_pass) {
+      if (tid >= 128 && tid < 128 + p.N) taps(tid - 128, cf{r_bp[0], r_bp[1]});
+    } else {
+      for (int n = tid; n < p.N; n += blockDim.x) {
+        cf bp = {0.f, 0.f};
+        if (bpin) bp = {to_f32(bpin[bg * D + 2 * n]), to_f32(bpin[bg * D + 2 * n + 1])};
+        taps(n, bp);
+      }
     }
   }
   __syncthreads();
   // ---- E. state update and read-out --------------------------------------------------------------
   const float mr = s_coef[0], mi = s_coef[1];
-  float* state = p.state + (size_t)bh * p.P * D;
-  if (D == 128 && (p.P % (8 * nw)) == 0) {
-    // N = 64: a state row is one float4 per lane; a warp takes 8 rows at a time, all loads first
+  if (rows8) {
+    // a warp takes 8 rows at a time, all loads first (the first 8 were requested at the top)
     const float4 a = reinterpret_cast<const float4*>(s_bp)[lane];
     const float4 c = reinterpret_cast<const float4*>(s_bc)[lane];
     const float4 cc = reinterpret_cast<const float4*>(s_c)[lane];
     for (int p0 = 8 * w; p0 < p.P; p0 += 8 * nw) {
-      float4 z[8];
+      if (p0 != 8 * w) {
 #pragma unroll
-      for (int r = 0; r < 8; ++r) z[r] = reinterpret_cast<const float4*>(state + (size_t)(p0 + r) * D)[lane];
+        for (int r = 0; r < 8; ++r) z[r] = reinterpret_cast<const float4*>(state + (size_t)(p0 + r) * D)[lane];
+      }
       float acc[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
@@ -189,8 +279,8 @@ __global__ void __launch_bounds__(256, 4) mixer_step_kernel(StepParams p) {
   for (int pp = tid; pp < p.P; pp += blockDim.x) {
     const int c = h * p.P + pp;
     float pre = s_y[pp];
-    if (p.d_skip) pre = round_io<T>(pre + s_u[pp] * p.d_skip[h]);
-    const float gt = to_f32(reinterpret_cast<const T*>(p.gate)[(size_t)b * p.gate_stride + c]);
+    if (p.d_skip) pre = round_io<T>(pre + s_u[pp] * (one_pass ? r_dsk : p.d_skip[h]));
+    const float gt = one_pass ? r_gate : to_f32(reinterpret_cast<const T*>(p.gate)[(size_t)b * p.gate_stride + c]);
     const float hv = round_io<T>(pre * silu_f(gt));
     p.hid[(size_t)b * C + c] = hv;
     ss += hv * hv;
