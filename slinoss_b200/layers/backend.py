@@ -134,6 +134,7 @@ class B200MixerDecodeBackend:
     def supports(self, owner, *, batch_size, device, dtype) -> bool:
         return device.type == "cuda" and dtype in (torch.float32, torch.bfloat16, torch.float16)
 
+    @torch.compiler.disable
     def fused_step(self, owner, gate, value_raw, params, bc, state, *, normed=None, workspace=None):
         """``gate, value_raw (batch, d_inner)`` (row-strided views are fine), ``params (batch, 3H)``,
         ``bc (batch, G*4*N)``; ``state`` is the mixer's decode state (conv window, float32 scan

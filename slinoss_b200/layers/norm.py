@@ -27,6 +27,7 @@ class _RMSNormFn(torch.autograd.Function):
                 d_w.to(weight.dtype) if ctx.needs_input_grad[1] else None, None)
 
 
+@torch.compiler.disable
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """RMSNorm over the last axis on the CUDA row kernels (same type for rows and weight)."""
     return _RMSNormFn.apply(x, weight, float(eps))

@@ -57,6 +57,7 @@ def ffn_activation_supported(projected, kind: str) -> bool:
     return kind in _C.FFN_KINDS and projected.numel() > 0 and hidden % v == 0
 
 
+@torch.compiler.disable
 def ffn_activation(projected, kind: str):
     """``gelu(projected, tanh form)`` or ``value * silu(gate)`` of ``projected = [value | gate]`` on the CUDA
     row kernels (differentiable)."""
@@ -119,6 +120,7 @@ def ffn_residual_supported(x, norm, ffn) -> bool:
     return _C.rmsnorm_supported(int(x.shape[-1]), x.dtype) and ffn.hidden_dim % v == 0 and x.numel() > 0
 
 
+@torch.compiler.disable
 def ffn_residual(x, norm, ffn, *, residual_in_fp32: bool = True, remat: str = "full"):
     """``x + ffn(norm(x))`` through the rematerialising op (see the module docstring)."""
     if remat not in ("full", "rows"):

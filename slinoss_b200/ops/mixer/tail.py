@@ -53,6 +53,7 @@ class _GatedNormFn(torch.autograd.Function):
                 None if d_d_skip is None else d_d_skip.to(dsd), d_w.to(wd), None)
 
 
+@torch.compiler.disable
 def mixer_gated_norm(scan_output, gate, norm_weight, eps, *, skip_input=None, d_skip=None):
     """Row-wise part of the tail -> ``(batch, T, heads*P)`` in scan_output's dtype."""
     _, heads, _, _ = _dims(scan_output, gate)

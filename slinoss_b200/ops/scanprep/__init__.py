@@ -79,6 +79,7 @@ class _ConvScanPrepFn(torch.autograd.Function):
                 g["d_theta_mod_bias"], g["d_theta_bias"], None, None)
 
 
+@torch.compiler.disable
 def conv_scanprep_b200(owner, value, params, bc, *, conv_weight=None, conv_bias=None,
                        conv_state=None, want_state=False):
     """``owner`` is the SLinOSSScanPrep module (bounds, biases, head geometry).
@@ -90,6 +91,7 @@ def conv_scanprep_b200(owner, value, params, bc, *, conv_weight=None, conv_bias=
                                  owner.theta_bias, owner, want_state)
 
 
+@torch.compiler.disable
 def scanprep_b200(owner, value, params, bc):
     """Scan preparation without the convolution.  Returns ``(U, M, K, B, C)``."""
     return conv_scanprep_b200(owner, value, params, bc)[:5]
@@ -126,6 +128,7 @@ class _ConvFn(torch.autograd.Function):
                 None)
 
 
+@torch.compiler.disable
 def causal_conv_silu_b200(x, weight, bias, conv_state=None, *, want_state=True):
     """``SiLU(depthwise causal conv1d(x) + bias)`` for channel-last ``x (batch,T,C)``,
     ``weight (C,d_conv)``, optional left state ``(batch,C,d_conv-1)``.

@@ -185,6 +185,7 @@ class _ScanFn(torch.autograd.Function):
         return (*res, None, None, None, None, None)
 
 
+@torch.compiler.disable
 def v2x2ssd_cute(U, M, K, B, C, *, chunk_size, initial_states=None, B_prev=None, U_prev=None,
                  compute_dtype=None, output_dtype=None, return_state=False, path="auto",
                  save_chunk_states=True):
@@ -221,6 +222,7 @@ def v2x2ssd_cute(U, M, K, B, C, *, chunk_size, initial_states=None, B_prev=None,
             U[:, :, -1, :].to(dtype=odtype).contiguous())
 
 
+@torch.compiler.disable
 def v2x2ssd(U, M, K, B, C, *, chunk_size=64, initial_states=None, B_prev=None, U_prev=None,
             compute_dtype=None, output_dtype=None, path="auto"):
     """Same call and 4-tuple result as the reference's ``v2x2ssd``."""
@@ -229,6 +231,7 @@ def v2x2ssd(U, M, K, B, C, *, chunk_size=64, initial_states=None, B_prev=None, U
                         output_dtype=output_dtype, return_state=True, path=path)
 
 
+@torch.compiler.disable
 def v2x2ssd_decode(U, M, K, B, C, *, state, B_prev=None, U_prev=None, output_dtype=None,
                    inplace=False):
     """One decode token.  ``U (batch,heads,P)``, ``M (batch,heads,2)``, ``K (batch,heads,2,2)``,
