@@ -81,3 +81,15 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_C, "_LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="there is no fallback path"):
         _C.lib()
+
+
+def test_alias_makes_reference_style_imports_resolve_to_this_package():
+    import subprocess
+    import sys
+    code = ("import slinoss_b200.alias as a; a.install(); import slinoss; "
+            "from slinoss.ops.v2x2ssd import v2x2ssd; from slinoss.layers import SLinOSSMixer; "
+            "from slinoss.blocks import SLinOSSStack; import slinoss_b200 as sb; "
+            "import importlib; assert SLinOSSMixer is sb.SLinOSSMixer and v2x2ssd is importlib.import_module('slinoss_b200.ops.v2x2ssd').v2x2ssd; "
+            "a.uninstall(); import sys; assert 'slinoss' not in sys.modules; print('ok')")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(ROOT))
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stderr
