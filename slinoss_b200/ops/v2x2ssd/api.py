@@ -134,6 +134,7 @@ class _ScanFn(torch.autograd.Function):
     def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, chunk_size, odtype,
                 return_state, path, save_states):
         args = _prep(U, M, K, B, C, initial_states, B_prev, U_prev)
+        ctx.set_materialize_grads(False)      # an unused output arrives as None in backward, not as zeros
         y_dtype = odtype if odtype in _IO_DTYPES else torch.float32
         out = _C.scan_fwd(*args, chunk_size=chunk_size, y_dtype=y_dtype, want_final=return_state,
                           path=path, save_states=save_states)
@@ -163,8 +164,15 @@ class _ScanFn(torch.autograd.Function):
             _, d_final, dB_last, dU_last = grads
         out = [None] * 8
         if dY is not None or d_final is not None:
+            half = U.dtype in (torch.bfloat16, torch.float16) and ctx.path != "simt"
+            if dY is None and half:
+                dY = torch.zeros_like(U)      # only the end state was used: zeros keep the tensor-core sweep
             if dY is not None:
-                if dY.dtype not in _IO_DTYPES:
+                if half and dY.dtype != U.dtype:
+                    # a float32 output was asked of 16-bit operands: the tensor-core sweep takes dY as a 16-bit
+                    # operand like U, B and C (the exact sweeps would keep it in float32 at ~20x the time)
+                    dY = dY.to(U.dtype)
+                elif dY.dtype not in _IO_DTYPES:
                     dY = dY.to(torch.float32)
                 dY = dY.contiguous()
             if d_final is not None:

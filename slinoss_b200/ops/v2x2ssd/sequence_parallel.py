@@ -1,0 +1,124 @@
+"""The scan over a sequence that is split across ranks (one contiguous time slice per rank).
+
+The recurrence is linear in its state: over a slice with transition product ``Pi = prod_t m_t`` the end
+state is ``Pi * z_start + f0``, where ``f0`` is the end state of the same slice started from zero.  So a
+sequence sharded over W ranks needs ONE exchange of small per-(batch, head) tensors:
+
+    pass A   every rank scans its slice from a zero state                          -> f0_r   (and Pi_r from M)
+    exchange all_gather of (f0_r, Pi_r) and of each slice's last token (b, u)      (state-sized, not T-sized)
+             z_start_r = sum_{q < r} (prod_{q < s < r} Pi_s) f0_q                  (W - 1 complex scalings)
+    pass B   every rank scans its slice again from z_start_r                       -> Y_r, end state
+
+which is the associative ``(prod m, Z)`` exchange the reference's scope notes describe for long contexts
+(its own decomposition has the same shape inside one device: ``chunk_increment`` -> ``state_passing`` ->
+``chunk_scan``, slinoss/ops/v2x2ssd/reference.py:992-1264).  Both passes are the ordinary differentiable op;
+the exchange is differentiable too (gather forward, sum-reduce backward), so ``backward()`` works through
+the whole thing and every rank must call it (the exchange's backward is a collective).  The price is a
+second pass over the slice; nothing of size T crosses the link.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .api import v2x2ssd_cute
+
+
+class _Gather(torch.autograd.Function):
+    """``stack(all_gather(x))`` forward; backward sums the ranks' gradients of the stack and keeps the
+    slot of this rank (all_reduce: available in every backend)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        world = dist.get_world_size(group)
+        ctx.group, ctx.rank = group, dist.get_rank(group)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.stack(parts)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        return g[ctx.rank], None
+
+
+def _scale_state(pi, z):
+    """Complex scalar ``pi (batch, heads, 2)`` times the interleaved complex state ``z (batch, heads, P, 2N)``."""
+    zz = z.reshape(*z.shape[:-1], -1, 2)
+    pr, pim = pi[..., 0, None, None], pi[..., 1, None, None]
+    out = torch.stack((pr * zz[..., 0] - pim * zz[..., 1], pr * zz[..., 1] + pim * zz[..., 0]), -1)
+    return out.reshape(z.shape)
+
+
+def transition_product(M):
+    """``prod_t m_t`` per (batch, heads) as (re, im), formed from summed log-magnitudes and summed angles in
+    float64 (never as a running product of small numbers)."""
+    m = M.double()
+    logmag = 0.5 * torch.log(m[..., 0] ** 2 + m[..., 1] ** 2).sum(-1)
+    angle = torch.atan2(m[..., 1], m[..., 0]).sum(-1)
+    mag = torch.exp(logmag)
+    return torch.stack((mag * torch.cos(angle), mag * torch.sin(angle)), -1).float()
+
+
+@torch.compiler.disable
+def v2x2ssd_sequence_parallel(U, M, K, B, C, *, chunk_size=64, group=None, initial_states=None, B_prev=None,
+                              U_prev=None, output_dtype=None, path="auto", single_rank_exchange=False):
+    """Scan of a sequence whose time axis is sharded over the ranks of ``group`` in rank order.
+
+    Arguments are this rank's slice, in the layouts of ``v2x2ssd``; ``initial_states``, ``B_prev`` and
+    ``U_prev`` describe what precedes the WHOLE sequence and are read on rank 0 only.  Returns
+    ``(Y, end_state, B_last, U_last)`` of this rank's slice (``end_state`` float32); the last rank's are those of
+    the whole sequence.  Without an initialised process group (or with one rank) this is the plain op, unless
+    ``single_rank_exchange`` asks for the two passes and the exchange anyway (a group of one: for tests and
+    profiles of the path on a single device)."""
+    if not (dist.is_available() and dist.is_initialized()) or \
+            (dist.get_world_size(group) == 1 and not single_rank_exchange):
+        Y, fin, bl, ul = v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=initial_states,
+                                      B_prev=B_prev, U_prev=U_prev, output_dtype=output_dtype,
+                                      return_state=True, path=path)
+        return Y, fin.float(), bl, ul
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if U.shape[2] < 1:
+        raise ValueError("every rank needs at least one token of the sequence.")
+    # ---- the token before each slice: the previous rank's last (b, u) --------------------------------
+    b_all = _Gather.apply(B[:, :, -1, :].contiguous(), group)          # (W, batch, groups, 2N)
+    u_all = _Gather.apply(U[:, :, -1, :].contiguous(), group)          # (W, batch, heads, P)
+    pick = torch.zeros(world, device=U.device, dtype=b_all.dtype)
+    if rank > 0:
+        pick[rank - 1] = 1
+    Bp = torch.einsum("w,w...->...", pick, b_all)                      # zeros on rank 0, connected on every rank
+    Up = torch.einsum("w,w...->...", pick.to(u_all.dtype), u_all)
+    z_first = None
+    if rank == 0:
+        if B_prev is not None:
+            Bp, Up = Bp + B_prev, Up + U_prev
+        z_first = initial_states
+    # ---- pass A: the slice from a zero state ------------------------------------------------------------
+    _, f0, _, _ = v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=z_first, B_prev=Bp, U_prev=Up,
+                               output_dtype=torch.float32, return_state=True, path=path)
+    pi = transition_product(M)
+    f_all = _Gather.apply(f0.float().contiguous(), group)              # (W, batch, heads, P, 2N)
+    pi_all = _Gather.apply(pi.contiguous(), group)                     # (W, batch, heads, 2)
+    # ---- the state at the start of this rank's slice ------------------------------------------------------
+    carry = torch.zeros_like(f_all[0])
+    start = end = None
+    for q in range(world):
+        if q == rank:
+            start = carry
+        carry = _scale_state(pi_all[q], carry) + f_all[q]
+        if q == rank:
+            end = carry                                                # float32 end state of this slice
+    # keep every rank's autograd graph attached to both gathers (whose backward is a collective), whatever
+    # part of them this rank's result uses
+    start = start + 0.0 * (f_all.sum(0) + _scale_state(pi_all.sum(0), torch.ones_like(carry)))
+    if rank == 0 and initial_states is not None:
+        start = start + initial_states.float()
+    # ---- pass B: the slice from its true start state -------------------------------------------------------
+    Y = v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=start, B_prev=Bp, U_prev=Up,
+                     output_dtype=output_dtype, return_state=False, path=path)
+    return Y, end, B[:, :, -1, :], U[:, :, -1, :]
+
+
+__all__ = ["transition_product", "v2x2ssd_sequence_parallel"]

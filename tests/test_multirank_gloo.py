@@ -183,3 +183,49 @@ def test_single_process_meaning_without_a_group():
     shard.allreduce_mean_(g)
     assert torch.equal(g[0], torch.ones(3))
     assert shard.rank_seed(5, 0) != shard.rank_seed(5, 1)
+
+
+# ---------------------------------------------------------------------------------------
+def _seqpar_worker(rank, store_path, out_path):
+    _init(rank, store_path)
+    from oracle import scan_np
+    from slinoss_b200.ops.v2x2ssd import v2x2ssd_sequence_parallel
+    from slinoss_b200.synthetic import make_scan_case
+    try:
+        full = make_scan_case(2, 4, 56, 4, 4, groups=2, seed=5, with_init=True, streaming=True)
+        cut = [0, 24, 56]                                           # ragged: 24 tokens on rank 0, 32 on rank 1
+        sl = slice(cut[rank], cut[rank + 1])
+        leaves = [t[:, :, sl].clone().requires_grad_(True) for t in full.tensors()]
+        extra = [t.clone().requires_grad_(True) for t in (full.initial_states, full.B_prev, full.U_prev)]
+        Y, end, b_last, u_last = v2x2ssd_sequence_parallel(
+            *leaves, chunk_size=16, initial_states=extra[0], B_prev=extra[1], U_prev=extra[2])
+        gen = torch.Generator().manual_seed(9)
+        d_end = torch.randn(end.shape, generator=gen)
+        loss = (Y * full.dY[:, :, sl]).sum()
+        if rank == WORLD - 1:
+            loss = loss + (end * d_end).sum()                        # gradient of the whole sequence's end state
+        grads = torch.autograd.grad(loss, leaves + extra, allow_unused=True)   # every rank: the exchange's backward is a collective
+        gathered = [None] * WORLD
+        dist.all_gather_object(gathered, [Y.detach().numpy(), end.detach().numpy()]
+                               + [None if g is None else g.numpy() for g in grads])
+        if rank == 0:
+            n = lambda t: t.double().numpy()
+            ins = [n(t) for t in full.tensors()]
+            kw = dict(initial_states=n(full.initial_states), B_prev=n(full.B_prev), U_prev=n(full.U_prev))
+            wY, wfin, _, _ = scan_np.v2x2ssm(*ins, **kw)
+            wg = scan_np.v2x2ssd_bwd(*ins, n(full.dY), d_final_state=n(d_end), **kw)
+            errs = [_rel(np.concatenate([g[0] for g in gathered], axis=2), wY), _rel(gathered[1][1], wfin)]
+            for i, k in enumerate("UMKBC"):
+                errs.append(_rel(np.concatenate([g[2 + i] for g in gathered], axis=2), wg[k]))
+            for i, k in enumerate(("initial_states", "B_prev", "U_prev")):
+                errs.append(_rel(gathered[0][7 + i], wg[k]))        # what precedes the sequence lives on rank 0
+            np.savez(out_path, errs=np.array(errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_sharded_over_two_ranks_equals_the_whole_sequence(tmp_path):
+    store, out = tmp_path / "store", tmp_path / "out.npz"
+    mp.spawn(_seqpar_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
+    errs = np.load(out)["errs"]
+    assert errs.max() <= 2e-5, errs
