@@ -17,6 +17,8 @@
 // gradients are reduced per CTA and accumulated with float atomics.
 #include <type_traits>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sl {
@@ -814,6 +816,65 @@ int check_common(int batch, int heads, int groups, int T, int P, int N, int io_d
   return SL_OK;
 }
 
+// ---- the three parts of a call (value, B/C, coefficients) touch disjoint tensors -----------------------
+// For sequence-sized calls they are launched on three streams between a fork and a join on the caller's
+// stream: the B/C kernels are bound by instruction issue, the value kernels by latency, and each leaves most
+// of the DRAM bandwidth idle, so they overlap well.  The side streams and events are created on the first
+// such call of a device (do that call outside stream capture); fork and join are ordinary event
+// dependencies, so a captured call records them as edges of the graph.  SLINOSS_B200_SERIAL_PARTS=1 keeps
+// every part on the caller's stream.
+struct PartStreams {
+  cudaStream_t side[2];
+  cudaEvent_t start, done[2];
+  bool tried, ok;
+};
+PartStreams* part_streams() {
+  static PartStreams table[16];
+  static std::mutex guard;   // forward and backward may arrive from different host threads
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  std::lock_guard<std::mutex> lock(guard);
+  PartStreams& ps = table[dev];
+  if (!ps.tried) {
+    ps.tried = true;
+    const char* e = getenv("SLINOSS_B200_SERIAL_PARTS");
+    ps.ok = !(e && e[0] == '1');
+    for (int i = 0; i < 2 && ps.ok; ++i)
+      ps.ok = cudaStreamCreateWithFlags(&ps.side[i], cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ps.done[i], cudaEventDisableTiming) == cudaSuccess;
+    ps.ok = ps.ok && cudaEventCreateWithFlags(&ps.start, cudaEventDisableTiming) == cudaSuccess;
+    if (!ps.ok) cudaGetLastError();
+  }
+  return ps.ok ? &ps : nullptr;
+}
+// Streams of the (value, B/C, coefficient) parts of one call; join() orders the caller's stream after all.
+struct PartFork {
+  cudaStream_t v, b, c;
+  PartStreams* ps = nullptr;
+  cudaStream_t main;
+  PartFork(cudaStream_t st, int parts, long long rows) : v(st), b(st), c(st), main(st) {
+    if (parts < 2 || rows < 2048) return;
+    ps = part_streams();
+    if (!ps) return;
+    if (cudaEventRecord(ps->start, st) != cudaSuccess || cudaStreamWaitEvent(ps->side[0], ps->start, 0) != cudaSuccess ||
+        cudaStreamWaitEvent(ps->side[1], ps->start, 0) != cudaSuccess) {
+      cudaGetLastError();
+      ps = nullptr;
+      return;
+    }
+    b = ps->side[0];
+    c = ps->side[1];
+  }
+  void join() {
+    if (!ps) return;
+    for (int i = 0; i < 2; ++i) {
+      cudaEventRecord(ps->done[i], ps->side[i]);
+      cudaStreamWaitEvent(main, ps->done[i], 0);
+    }
+    ps = nullptr;
+  }
+};
+
 }  // namespace
 }  // namespace sl
 
@@ -830,8 +891,15 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
   using namespace sl;
   if (int e = check_common(batch, heads, groups, T, P, N, io_dtype, conv_weight ? d_conv : 1)) return e;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (value && !U) return SL_ERR_NULL_POINTER;
+  if (bc && (!Bo || !Co || !cfg)) return SL_ERR_NULL_POINTER;
+  if (params) {
+    if (!M || !K || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias || !theta_bias || !theta_sign)
+      return SL_ERR_NULL_POINTER;
+    if (!aligned(M, 8) || !aligned(K, 16)) return SL_ERR_BAD_ALIGNMENT;
+  }
+  PartFork fork(st, (value != nullptr) + (bc != nullptr) + (params != nullptr), (long long)batch * T);
   if (value) {
-    if (!U) return SL_ERR_NULL_POINTER;
     ValueParams p{};
     p.x = value; p.w = conv_weight; p.bias = conv_bias; p.state_in = conv_state_in;
     p.state_out = conv_state_out; p.U = U; p.xs = value_row_stride;
@@ -840,40 +908,37 @@ extern "C" int sl_scanprep_conv_fwd(const void* value, int64_t value_row_stride,
     const int vf = CONV_V;   // 4 channels per thread (8- or 16-byte pieces)
     if (value_vec_ok(p, nullptr, nullptr, vf)) {
       dim3 grid((p.C + 32 * vf - 1) / (32 * vf), (T + CONV_SUB * CONV_TT - 1) / (CONV_SUB * CONV_TT), batch);
-      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_vec_kernel<Tt, CONV_V><<<grid, 256, 0, st>>>(p); });
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_vec_kernel<Tt, CONV_V><<<grid, 256, 0, fork.v>>>(p); });
     } else {
       dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
-      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, st>>>(p); });
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_fwd_kernel<Tt><<<grid, 256, 0, fork.v>>>(p); });
     }
     note_launches(1);
   }
   if (bc) {
-    if (!Bo || !Co || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
     const dim3 vgrid((T + 7) / 8, (groups + BC_GCH - 1) / BC_GCH, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
       if (bc_vec_ok(batch, groups, N, bc, Bo, Co, nullptr))
-        bc_fwd_vec_kernel<Tt><<<vgrid, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
+        bc_fwd_vec_kernel<Tt><<<vgrid, 256, 0, fork.b>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
                                                      reinterpret_cast<Tt*>(Co), T, groups, N, cfg->eps);
       else
-        bc_fwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
+        bc_fwd_kernel<Tt><<<blocks, 256, 0, fork.b>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<Tt*>(Bo),
                                                   reinterpret_cast<Tt*>(Co), batch, T, groups, N, cfg->eps);
     });
     note_launches(1);
   }
   if (params) {
-    if (!M || !K || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias || !theta_bias || !theta_sign)
-      return SL_ERR_NULL_POINTER;
-    if (!aligned(M, 8) || !aligned(K, 16)) return SL_ERR_BAD_ALIGNMENT;
     CoeffParams p{};
     p.params = params; p.dt_bias = dt_bias; p.alpha_bias = alpha_bias;
     p.theta_mod_bias = theta_mod_bias; p.theta_bias = theta_bias; p.theta_sign = theta_sign;
     p.cfg = *cfg; p.M = M; p.K = K; p.batch = batch; p.T = T; p.H = heads;
     dim3 grid((T + 127) / 128, heads, batch);
-    SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_fwd_kernel<Tt><<<grid, 128, 0, st>>>(p); });
+    SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_fwd_kernel<Tt><<<grid, 128, 0, fork.c>>>(p); });
     note_launches(1);
   }
+  fork.join();
   return launch_status();
 }
 
@@ -890,9 +955,16 @@ extern "C" int sl_scanprep_conv_bwd(
   using namespace sl;
   if (int e = check_common(batch, heads, groups, T, P, N, io_dtype, conv_weight ? d_conv : 1)) return e;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dU && (!d_value || !value || (conv_weight && !d_conv_weight))) return SL_ERR_NULL_POINTER;
+  if (dBo && (!dCo || !bc || !d_bc || !cfg)) return SL_ERR_NULL_POINTER;
+  if (dM) {
+    if (!dK || !params || !d_params || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias ||
+        !theta_bias || !theta_sign)
+      return SL_ERR_NULL_POINTER;
+    if (!aligned(dM, 8) || !aligned(dK, 16)) return SL_ERR_BAD_ALIGNMENT;
+  }
+  PartFork fork(st, (dU != nullptr) + (dBo != nullptr) + (dM != nullptr), (long long)batch * T);
   if (dU) {
-    if (!d_value || !value) return SL_ERR_NULL_POINTER;
-    if (conv_weight && !d_conv_weight) return SL_ERR_NULL_POINTER;
     ValueBwdParams q{};
     ValueParams& p = q.f;
     p.x = value; p.w = conv_weight; p.bias = conv_bias; p.state_in = conv_state_in;
@@ -903,36 +975,31 @@ extern "C" int sl_scanprep_conv_bwd(
     pv.U = const_cast<void*>(dU);
     if (value_vec_ok(pv, d_value, nullptr)) {
       dim3 grid((p.C + 32 * CONV_V - 1) / (32 * CONV_V), (T + CONV_SUB * CONV_TT - 1) / (CONV_SUB * CONV_TT), batch);
-      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_vec_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_vec_kernel<Tt><<<grid, 256, 0, fork.v>>>(q); });
     } else {
       dim3 grid((p.C + 255) / 256, (T + CONV_TT - 1) / CONV_TT, batch);
-      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_kernel<Tt><<<grid, 256, 0, st>>>(q); });
+      SL_DISPATCH_DTYPE(io_dtype, Tt, { value_bwd_kernel<Tt><<<grid, 256, 0, fork.v>>>(q); });
     }
     note_launches(1);
   }
   if (dBo) {
-    if (!dCo || !bc || !d_bc || !cfg) return SL_ERR_NULL_POINTER;
     const long long rows = (long long)batch * T * groups;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
     const dim3 vgrid((T + 7) / 8, (groups + BC_GCH - 1) / BC_GCH, batch);
     SL_DISPATCH_DTYPE(io_dtype, Tt, {
       if (bc_vec_ok(batch, groups, N, bc, dBo, dCo, d_bc))
-        bc_bwd_vec_kernel<Tt><<<vgrid, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc),
+        bc_bwd_vec_kernel<Tt><<<vgrid, 256, 0, fork.b>>>(reinterpret_cast<const Tt*>(bc),
                                                      reinterpret_cast<const Tt*>(dBo),
                                                      reinterpret_cast<const Tt*>(dCo), reinterpret_cast<Tt*>(d_bc),
                                                      T, groups, N, cfg->eps);
       else
-        bc_bwd_kernel<Tt><<<blocks, 256, 0, st>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<const Tt*>(dBo),
+        bc_bwd_kernel<Tt><<<blocks, 256, 0, fork.b>>>(reinterpret_cast<const Tt*>(bc), reinterpret_cast<const Tt*>(dBo),
                                                   reinterpret_cast<const Tt*>(dCo), reinterpret_cast<Tt*>(d_bc),
                                                   batch, T, groups, N, cfg->eps);
     });
     note_launches(1);
   }
   if (dM) {
-    if (!dK || !params || !d_params || !cfg || !dt_bias || !alpha_bias || !theta_mod_bias ||
-        !theta_bias || !theta_sign)
-      return SL_ERR_NULL_POINTER;
-    if (!aligned(dM, 8) || !aligned(dK, 16)) return SL_ERR_BAD_ALIGNMENT;
     CoeffParams p{};
     p.params = params; p.dt_bias = dt_bias; p.alpha_bias = alpha_bias;
     p.theta_mod_bias = theta_mod_bias; p.theta_bias = theta_bias; p.theta_sign = theta_sign;
@@ -940,8 +1007,9 @@ extern "C" int sl_scanprep_conv_bwd(
     p.d_alpha_bias = d_alpha_bias; p.d_theta_mod_bias = d_theta_mod_bias;
     p.d_theta_bias = d_theta_bias; p.batch = batch; p.T = T; p.H = heads;
     dim3 grid((T + 127) / 128, heads, batch);
-    SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_bwd_kernel<Tt><<<grid, 128, 0, st>>>(p); });
+    SL_DISPATCH_DTYPE(io_dtype, Tt, { coeff_bwd_kernel<Tt><<<grid, 128, 0, fork.c>>>(p); });
     note_launches(1);
   }
+  fork.join();
   return launch_status();
 }
