@@ -827,6 +827,7 @@ struct PartStreams {
   cudaStream_t side[2];
   cudaEvent_t start, done[2];
   bool tried, ok;
+  std::mutex in_use;   // held from fork to join: the events are shared by all calls on the device
 };
 PartStreams* part_streams() {
   static PartStreams table[16];
@@ -852,13 +853,16 @@ struct PartFork {
   cudaStream_t v, b, c;
   PartStreams* ps = nullptr;
   cudaStream_t main;
+  ~PartFork() { join(); }
   PartFork(cudaStream_t st, int parts, long long rows) : v(st), b(st), c(st), main(st) {
     if (parts < 2 || rows < 2048) return;
     ps = part_streams();
     if (!ps) return;
+    ps->in_use.lock();
     if (cudaEventRecord(ps->start, st) != cudaSuccess || cudaStreamWaitEvent(ps->side[0], ps->start, 0) != cudaSuccess ||
         cudaStreamWaitEvent(ps->side[1], ps->start, 0) != cudaSuccess) {
       cudaGetLastError();
+      ps->in_use.unlock();
       ps = nullptr;
       return;
     }
@@ -871,6 +875,7 @@ struct PartFork {
       cudaEventRecord(ps->done[i], ps->side[i]);
       cudaStreamWaitEvent(main, ps->done[i], 0);
     }
+    ps->in_use.unlock();
     ps = nullptr;
   }
 };
