@@ -12,6 +12,62 @@
 namespace sl {
 namespace {
 
+// State update and read-out of a warp's rows when a state row is KQ float4 per lane (2N = 128 KQ): 8 / KQ rows
+// at a time, all loads first.
+template <int KQ, typename TIn, typename TY>
+__device__ __forceinline__ void decode_rows(const TIn* __restrict__ U, const TIn* __restrict__ Uprev,
+                                            const float* state_in, float* state_out, TY* __restrict__ Y,
+                                            const float* s_bp, const float* s_bc, const float* s_c, float mr,
+                                            float mi, size_t bh, int P, int lane, int w, int nw) {
+  constexpr int R = 8 / KQ;
+  constexpr int D = 128 * KQ;
+  float4 a[KQ], c[KQ], cc[KQ];
+#pragma unroll
+  for (int q = 0; q < KQ; ++q) {
+    a[q] = reinterpret_cast<const float4*>(s_bp)[lane + 32 * q];
+    c[q] = reinterpret_cast<const float4*>(s_bc)[lane + 32 * q];
+    cc[q] = reinterpret_cast<const float4*>(s_c)[lane + 32 * q];
+  }
+  for (int p0 = R * w; p0 < P; p0 += R * nw) {
+    float4 z[R][KQ];
+    float u[R], up[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int q = 0; q < KQ; ++q)
+        z[r][q] = reinterpret_cast<const float4*>(state_in + (bh * P + p0 + r) * D)[lane + 32 * q];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      u[r] = to_f32(U[bh * P + p0 + r]);
+      up[r] = Uprev ? to_f32(Uprev[bh * P + p0 + r]) : 0.f;
+    }
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      acc[r] = 0.f;
+#pragma unroll
+      for (int q = 0; q < KQ; ++q) {
+        const float4 zz = z[r][q];
+        float4 o;
+        o.x = mr * zz.x - mi * zz.y + up[r] * a[q].x + u[r] * c[q].x;
+        o.y = mr * zz.y + mi * zz.x + up[r] * a[q].y + u[r] * c[q].y;
+        o.z = mr * zz.z - mi * zz.w + up[r] * a[q].z + u[r] * c[q].z;
+        o.w = mr * zz.w + mi * zz.z + up[r] * a[q].w + u[r] * c[q].w;
+        reinterpret_cast<float4*>(state_out + (bh * P + p0 + r) * D)[lane + 32 * q] = o;
+        acc[r] += cc[q].x * o.x + cc[q].y * o.y + cc[q].z * o.z + cc[q].w * o.w;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
+    if (lane < R) {
+      float v = acc[0];
+#pragma unroll
+      for (int r = 1; r < R; ++r) v = lane == r ? acc[r] : v;
+      Y[bh * P + p0 + lane] = from_f32<TY>(v);
+    }
+  }
+}
+
 template <typename TIn, typename TY>
 __global__ void __launch_bounds__(256) decode_kernel(
     const TIn* __restrict__ U, const float* __restrict__ M, const float* __restrict__ K,
@@ -40,43 +96,16 @@ __global__ void __launch_bounds__(256) decode_kernel(
   __syncthreads();
   const float mr = M[bh * 2], mi = M[bh * 2 + 1];
   const bool vec4 = (N % 2) == 0;
+  // N = 64 / N = 128: a state row is one / two float4 per lane.  A warp takes 8 / 4 consecutive rows at a
+  // time and issues all 8 loads before any arithmetic, so 4 KB per warp are in flight.  (Measured and not
+  // kept, both because the extra registers cost the third resident CTA per SM: requesting the first rows
+  // ahead of the staging above, 96 -> 124 us; two streams per CTA at N = 64, 96 -> 114 us.)
   if (D == 128 && (P % (8 * nw)) == 0) {
-    // N = 64: a state row is one float4 per lane.  A warp takes 8 consecutive rows at a time and
-    // issues all 8 loads before any arithmetic, so 4 KB per warp are in flight.
-    const float4 a = reinterpret_cast<const float4*>(s_bp)[lane];
-    const float4 c = reinterpret_cast<const float4*>(s_bc)[lane];
-    const float4 cc = reinterpret_cast<const float4*>(s_c)[lane];
-    for (int p0 = 8 * w; p0 < P; p0 += 8 * nw) {
-      float4 z[8];
-      float u[8], up[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        z[r] = reinterpret_cast<const float4*>(state_in + (bh * P + p0 + r) * D)[lane];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        u[r] = to_f32(U[bh * P + p0 + r]);
-        up[r] = Uprev ? to_f32(Uprev[bh * P + p0 + r]) : 0.f;
-      }
-      float acc[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        float4 o;
-        o.x = mr * z[r].x - mi * z[r].y + up[r] * a.x + u[r] * c.x;
-        o.y = mr * z[r].y + mi * z[r].x + up[r] * a.y + u[r] * c.y;
-        o.z = mr * z[r].z - mi * z[r].w + up[r] * a.z + u[r] * c.z;
-        o.w = mr * z[r].w + mi * z[r].z + up[r] * a.w + u[r] * c.w;
-        reinterpret_cast<float4*>(state_out + (bh * P + p0 + r) * D)[lane] = o;
-        acc[r] = cc.x * o.x + cc.y * o.y + cc.z * o.z + cc.w * o.w;
-      }
-#pragma unroll
-      for (int r = 0; r < 8; ++r) acc[r] = warp_sum(acc[r]);
-      if (lane < 8) {
-        float v = acc[0];
-#pragma unroll
-        for (int r = 1; r < 8; ++r) v = lane == r ? acc[r] : v;
-        Y[bh * P + p0 + lane] = from_f32<TY>(v);
-      }
-    }
+    decode_rows<1>(U, Uprev, state_in, state_out, Y, s_bp, s_bc, s_c, mr, mi, bh, P, lane, w, nw);
+    return;
+  }
+  if (D == 256 && (P % (4 * nw)) == 0) {
+    decode_rows<2>(U, Uprev, state_in, state_out, Y, s_bp, s_bc, s_c, mr, mi, bh, P, lane, w, nw);
     return;
   }
 #pragma unroll 2

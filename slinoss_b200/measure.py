@@ -70,11 +70,11 @@ def report(name, ms, algo_bytes, config, extra=None):
 
 
 # ---------------------------------------------------------------------------------------
-def measure_decode(iters, dev, batch=None):
-    """Config 3: batch 256, heads 32, P 64, N 64, bf16 vectors, float32 state."""
+def measure_decode(iters, dev, batch=None, N=64):
+    """Config 3: batch 256, heads 32, P 64, N 64 (or the mixer's default 128), bf16 vectors, float32 state."""
     from . import _C
     g = torch.Generator().manual_seed(0)
-    b, h, P, N = 256, 32, 64, 64
+    b, h, P = (256 if N == 64 else 128), 32, 64
     r = lambda *s: torch.randn(*s, generator=g)
     U = r(b, h, P).to(torch.bfloat16).to(dev)
     Bv = (r(b, h, 2 * N) / N ** 0.5).to(torch.bfloat16).to(dev)
@@ -86,7 +86,7 @@ def measure_decode(iters, dev, batch=None):
     state = (0.1 * r(b, h, P, 2 * N)).to(dev)
     state2 = torch.empty_like(state)
     Bp, Up = torch.zeros_like(Bv), torch.zeros_like(U)
-    cfg = "config 3: batch 256 x heads 32 x P 64 x N 64, one token"
+    cfg = f"config 3: batch {b} x heads 32 x P 64 x N {N}, one token"
 
     def out_of_place():
         _C.scan_decode(U, M, K, Bv, Cv, state, Bp, Up, y_dtype=torch.bfloat16, state_out=state2)
@@ -373,7 +373,7 @@ def measure_scan_n128(iters, dev):
                                                chunk_size=64, saved=(st, fin)), iters), bht * 2480, name)]
 
 
-WHAT = {"scan_n128": measure_scan_n128, "ffn_rows": measure_ffn_rows, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
+WHAT = {"decode_n128": lambda iters, dev: measure_decode(iters, dev, N=128), "scan_n128": measure_scan_n128, "ffn_rows": measure_ffn_rows, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
         "scanprep": measure_scanprep, "tail": measure_tail, "mixer": measure_mixer, "scan": measure_scan}
 
 

@@ -146,8 +146,9 @@ def test_segmented_equals_full_pass():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_decode_equals_forward_tokenwise(dtype):
-    case = make_scan_case(3, 4, 6, 64, 64, groups=2, dtype=dtype, streaming=True, with_init=True)
+@pytest.mark.parametrize("N", [64, 128])           # one / two float4 of a state row per lane
+def test_decode_equals_forward_tokenwise(dtype, N):
+    case = make_scan_case(3, 4, 6, 64, N, groups=2, dtype=dtype, streaming=True, with_init=True)
     wY, wfin, _, _ = _oracle_fwd(case)
     c = case.to(DEV)
     state, bp, up = c.initial_states.clone(), c.B_prev, c.U_prev
