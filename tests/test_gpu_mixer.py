@@ -343,3 +343,31 @@ def test_stack_trains_one_step():
         opt.step()
         losses.append(float(loss.detach()))
     assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mixer_with_its_default_state_width_of_128(dtype):
+    """``SLinOSSMixer``'s default ``d_state`` is 128: the two-pass tensor-core scan (16-bit) or the exact scan
+    (float32) in the forward and backward pass, the generic loops of the fused decode step; token by token ==
+    forward pass, and the 16-bit run against the same module in float32 on the exact kernels."""
+    torch.manual_seed(11)
+    m = sb.SLinOSSMixer(256, d_head=64, d_conv=4, chunk_size=64).to(DEV).to(dtype)     # d_state = 128, expand = 2
+    assert m.d_state == 128
+    x = torch.randn(2, 70, 256, device=DEV, dtype=dtype, requires_grad=True)
+    out = m(x)
+    (gx,) = torch.autograd.grad(out.float().square().sum(), x)
+    with torch.no_grad():
+        state, ys = None, []
+        for t in range(6):
+            y, state = m.step(x[:, t], state)
+            ys.append(y)
+    t_step = 5e-5 if dtype == torch.float32 else 2e-2
+    assert rel(torch.stack(ys, 1), out[:, :6]) <= t_step
+    # the same module in float32 on the exact kernels is the yardstick for the 16-bit run
+    if dtype != torch.float32:
+        m32 = sb.SLinOSSMixer(256, d_head=64, d_conv=4, chunk_size=64).to(DEV)
+        m32.load_state_dict({k: v.float() for k, v in m.state_dict().items()})
+        x32 = x.detach().float().requires_grad_()
+        out32 = m32(x32)
+        (gx32,) = torch.autograd.grad(out32.square().sum(), x32)
+        assert rel(out, out32) <= 3e-2 and rel(gx, gx32) <= 6e-2
