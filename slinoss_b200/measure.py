@@ -327,7 +327,17 @@ def measure_scan(iters, dev):
                       time_ms(lambda: _C.scan_bwd(g.U, g.M, g.K, g.B, g.C, g.initial_states, g.B_prev, g.U_prev,
                                                   g.dY, None, chunk_size=64, saved=(gst, gfin)), iters),
                       gbytes, gname)]
-    return grouped + [report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name),
+    # the same step through the public op and autograd (device-resident tensors): what a training loop calls
+    from .ops.v2x2ssd import v2x2ssd_cute
+    leaves = [t.clone().requires_grad_(True) for t in c.tensors()]
+
+    def op_step():
+        Y = v2x2ssd_cute(*leaves, chunk_size=64)
+        torch.autograd.grad(Y, leaves, c.dY)
+
+    through_op = [report("v2x2ssd_cute forward + torch.autograd.grad (public op, tensors on the device)",
+                         time_ms(op_step, iters), bht * (792 + 1456), name)]
+    return grouped + through_op + [report("sl_v2x2ssd_fwd (saving chunk states)", time_ms(fwd, iters), bht * 792, name),
             report("sl_v2x2ssd_bwd (saved chunk states)",
                    time_ms(lambda: _C.scan_bwd(c.U, c.M, c.K, c.B, c.C, None, None, None, c.dY, None,
                                                chunk_size=64, saved=(st, fin)), iters), bht * 1456, name),
