@@ -112,6 +112,10 @@ SL_API size_t sl_workspace_bytes(int kind, int batch, int heads, int groups, int
  *   U, B, C, B_prev, U_prev : io_dtype;  Y : y_dtype;  M, K, states : float32.
  *   initial_states, B_prev, U_prev, final_state may be NULL (B_prev and U_prev
  *   together).  T must be >= 1 (T == 0 is answered by the host wrapper).
+ *   Precondition of the tensor-core path: every transition is non-zero (|m_t| > 0; the kernels form
+ *   log|m| and kp/m and do not check: a zero gives NaN/Inf).  The reference rejects it in its chunked
+ *   paths (slinoss/ops/v2x2ssd/reference.py:509-517); SL_PATH_SIMT computes through it.  With bfloat16
+ *   operands dM (= S / conj(m)) keeps the 16-bit tolerance down to |m| of about 0.3.
  *   chunk_states (optional, sl_workspace_bytes(SL_WS_SCAN_STATES, ...) bytes): when given
  *   together with final_state, the tensor-core path stores the state at the start of every
  *   64-token chunk there; handing both to sl_v2x2ssd_bwd saves its state pre-sweep.  The
@@ -159,7 +163,11 @@ SL_API int sl_v2x2ssd_bwd(const void* U, const float* M, const float* K, const v
  *   - the array keeps the previous call's contents; each call itself clears the
  *     part it accumulates into, so results never depend on them;
  *   - the first call on each device looks up the array's device address on the host;
- *     issue that first call before starting any stream capture.
+ *     issue that first call before starting any stream capture;
+ *   - the array used is the CURRENT device's (cudaGetDevice at the time of the call): the stream
+ *     passed in must belong to that device;
+ *   - if the address lookup fails, the call returns SL_ERR_LAUNCH_FAILED and sl_last_cuda_error()
+ *     gives the runtime's reason.
  */
 #define SL_STATIC_SCRATCH_BYTES (64u << 20)
 SL_API size_t sl_static_scratch_bytes(void);

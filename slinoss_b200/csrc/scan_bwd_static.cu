@@ -40,8 +40,10 @@ int scratch_address(void** out) {
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (g_scratch_ptr[dev] == nullptr) {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {   // e.g. the module's 64 MiB array could not be placed on this device
       cudaGetLastError();
+      sl::note_cuda_error(e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol);   // for sl_last_cuda_error()
       return SL_ERR_LAUNCH_FAILED;
     }
     g_scratch_ptr[dev] = p;

@@ -14,7 +14,7 @@ All of them are differentiable through ``torch.autograd`` (decode excepted) and
 run only on CUDA tensors: there is no CPU path in this package.
 """
 
-from .api import v2x2ssd, v2x2ssd_cute, v2x2ssd_decode
+from .api import assert_nonzero_transitions, v2x2ssd, v2x2ssd_cute, v2x2ssd_decode
 from .sequence_parallel import v2x2ssd_sequence_parallel
 
-__all__ = ["v2x2ssd", "v2x2ssd_cute", "v2x2ssd_decode", "v2x2ssd_sequence_parallel"]
+__all__ = ["assert_nonzero_transitions", "v2x2ssd", "v2x2ssd_cute", "v2x2ssd_decode", "v2x2ssd_sequence_parallel"]

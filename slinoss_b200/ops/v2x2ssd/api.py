@@ -125,6 +125,20 @@ def _prep(U, M, K, B, C, initial_states, B_prev, U_prev):
             cast(initial_states, torch.float32), cast(B_prev, io), cast(U_prev, io))
 
 
+def assert_nonzero_transitions(M: torch.Tensor) -> None:
+    """Raise the reference's error for an exact-zero transition (slinoss/ops/v2x2ssd/reference.py:509-517).
+
+    ``|m_t| > 0`` is a precondition of the chunked (tensor-core) kernels: they form ``log|m|`` and, in the
+    merged-tap form, ``kp_{t+1} / m_{t+1}``; a zero transition yields NaN or Inf there (the exact path computes
+    a forward pass through it, with dM = 0 at that token).  The ops do not check it themselves, because the
+    check synchronises the device (the reference's torch path does it on every call); call this where the
+    transitions do not come from the scan preparation, whose radius is bounded below by ``r_min``."""
+    if bool((M[..., 0] == 0).logical_and(M[..., 1] == 0).any()):
+        raise ValueError(
+            "M must be strictly nonzero in chunked scan paths. Exact-zero transitions are outside the "
+            "SLinOSS operating region; use v2x2ssm if you need arbitrary zero-transition behavior.")
+
+
 class _ScanFn(torch.autograd.Function):
     """Saves the inputs (same saved set as slinoss/ops/v2x2ssd/cute/autograd.py:110-118)
     and, optionally, the 16-bit chunk-start states of the tensor-core path, which spare the
