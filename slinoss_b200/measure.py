@@ -271,7 +271,7 @@ def measure_mixer(iters, dev, batch=8):
                   "config": f"x ({batch}, 2048, 1024) bf16, d_inner 2048, 32 heads x 64, N 64, d_conv 4"})]
 
 
-def measure_mixer_step(iters, dev, batch=256):
+def measure_mixer_step(iters, dev, batch=256, N=64):
     """One decode token of the whole mixer (d_model 1024, 32 heads x 64, N 64, conv width 4, bf16) at
     the decode configuration's batch: in_proj, the one-launch fused step, out_proj.  Eager through
     ``SLinOSSMixer.step`` and replayed from the CUDA-graph engine; the traffic that bounds it is the
@@ -279,10 +279,10 @@ def measure_mixer_step(iters, dev, batch=256):
     import slinoss_b200 as sb
     from .engine import MixerDecodeEngine
     torch.manual_seed(0)
-    m = sb.SLinOSSMixer(1024, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(dev).to(torch.bfloat16)
+    m = sb.SLinOSSMixer(1024, d_state=N, expand=2, d_head=64, d_conv=4, chunk_size=64).to(dev).to(torch.bfloat16)
     x = torch.randn(batch, 1024, device=dev, dtype=torch.bfloat16)
-    algo = 2 * batch * 32 * 64 * 128 * 4
-    cfg = f"SLinOSSMixer.step: batch {batch}, d_model 1024, 32 heads x 64, N 64, d_conv 4, bf16"
+    algo = 2 * batch * 32 * 64 * 2 * N * 4
+    cfg = f"SLinOSSMixer.step: batch {batch}, d_model 1024, 32 heads x 64, N {N}, d_conv 4, bf16"
     lines = []
     with torch.no_grad():
         _, state = m.step(x, None)
@@ -383,7 +383,7 @@ def measure_scan_n128(iters, dev):
                                                chunk_size=64, saved=(st, fin)), iters), bht * 2480, name)]
 
 
-WHAT = {"decode_n128": lambda iters, dev: measure_decode(iters, dev, N=128), "scan_n128": measure_scan_n128, "ffn_rows": measure_ffn_rows, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
+WHAT = {"mixer_step_n128": lambda iters, dev: measure_mixer_step(iters, dev, batch=128, N=128), "decode_n128": lambda iters, dev: measure_decode(iters, dev, N=128), "scan_n128": measure_scan_n128, "ffn_rows": measure_ffn_rows, "decode": measure_decode, "decode_sequence": measure_decode_sequence, "mixer_step": measure_mixer_step,
         "scanprep": measure_scanprep, "tail": measure_tail, "mixer": measure_mixer, "scan": measure_scan}
 
 
