@@ -25,7 +25,8 @@ JSON line:
                         headline legs: config 3 (decode of 1024 consecutive tokens, eager and as
                         one CUDA graph) and config 2 (the mixer layer forward+backward and its four
                         row-kernel calls; under --gpus N every rank owns batch 8/N of it) and, at
-                        N=1, the config-1 streams with 128 state columns (the mixer's default)
+                        N=1, the config-1 streams with 128 state columns (the mixer's default) and the
+                        CPU restatement of configs 3 and 2 timed on the host cores (bounded samples)
 
 ``--impl reference`` times only that CPU port on WHOLE steps of the same workload with all host
 threads (set explicitly: a launcher may export OMP_NUM_THREADS=1) and prints the same line with
@@ -43,6 +44,7 @@ import sys
 import time
 from pathlib import Path
 
+import numpy as np
 import torch
 
 ROOT = Path(__file__).resolve().parent
@@ -164,6 +166,59 @@ def cpu_baseline(sample_heads: int = 16, repeats: int = 1) -> dict:
             "kind": "port",
             "sample": f"fwd+bwd of batch 1 x {sample_heads} heads x T {c['T']} (1/{scale:.0f} of a step) "
                       f"in {best:.2f} s, scaled linearly", "sample_seconds": best}
+
+
+def cpu_baseline_others() -> dict:
+    """The CPU restatement of configs 3 and 2 timed on the host cores on bounded samples (seconds each):
+    decode = the C/OpenMP port's one-token update over a carried state; the mixer's row-wise stages (conv +
+    scan preparation, gated RMSNorm tail) = the torch CPU oracle, forward + backward."""
+    from oracle import mixer_torch as mt
+    from oracle import scan_c
+    cores = scan_c.set_num_threads(os.cpu_count() or 1)
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    r = lambda *sh: torch.randn(*sh, generator=g)
+    # ---- config 3: one token, batch 16 of 256 (state 16 x 32 x 64 x 128 float32)
+    b, h, P, N = 16, 32, 64, 64
+    state = (0.1 * r(b, h, P, 2 * N)).numpy()
+    args = [r(b, h, 1, P).numpy(), torch.stack([0.95 * torch.ones(b, h, 1), 0.1 * torch.ones(b, h, 1)], -1).numpy(),
+            (0.05 * r(b, h, 1, 2, 2)).numpy(), (r(b, h, 1, 2 * N) / 8).numpy(), (r(b, h, 1, 2 * N) / 8).numpy()]
+    bp, up = np.zeros((b, h, 2 * N), np.float32), np.zeros((b, h, P), np.float32)
+    steps, t0 = 0, time.perf_counter()
+    while steps < 8 or time.perf_counter() - t0 < 2.0:
+        _, state = scan_c.forward(*args, initial_states=state, B_prev=bp, U_prev=up)
+        steps += 1
+    dec_s = (time.perf_counter() - t0) / steps
+    # ---- config 2: batch 1 x T 512 of the 8 x 2048 rows (d_inner 2048 = 32 heads x 64, N 64)
+    T, H = 512, 32
+    cfg = {"dt_min": 5e-3, "dt_max": 1e-1, "alpha_min": 0.0, "alpha_max": 20.0, "theta_init_min": 0.05,
+           "theta_init_max": 2.0, "theta_mod_scale": 1.0, "r_min": 0.8, "r_max": 1.0, "eps": 1e-8}
+    value, params, bc = r(1, T, H * P).requires_grad_(), r(1, T, 3 * H).requires_grad_(), r(1, T, H, 4, N).requires_grad_()
+    w, bias = (0.3 * r(H * P, 4)).requires_grad_(), r(H * P).requires_grad_()
+    biases = [r(H).requires_grad_() for _ in range(4)] + [torch.ones(H)]
+    gate, wn = r(1, T, H * P).requires_grad_(), torch.ones(H * P, requires_grad=True)
+    d_skip = torch.ones(H, requires_grad=True)
+
+    def rows_step():
+        v, _ = mt.causal_conv_silu(value, w, bias)
+        U, M, K, Bo, Co = mt.scanprep(v, params, bc, cfg, *biases, d_head=P)
+        out = mt.gated_rmsnorm(U, gate, wn, 1e-5, skip_input=U, d_skip=d_skip)    # (U stands in for the scan output)
+        (out.square().sum() + M.square().sum() + K.square().sum() + Bo.square().sum() + Co.square().sum()).backward()
+
+    rows_step()
+    n, t0 = 0, time.perf_counter()
+    while n < 2 or time.perf_counter() - t0 < 2.0:
+        rows_step()
+        n += 1
+    rows_s = (time.perf_counter() - t0) / n
+    return {"kind": "port", "cores": cores,
+            "config3_decode": {"value": 256 / (dec_s * 256 / b), "unit": "tokens/s",
+                               "sample": f"one-token update of batch {b} x 32 heads (1/16 of the batch), "
+                                         f"{dec_s * 1e3:.2f} ms, scaled linearly to batch 256"},
+            "config2_rows": {"value": 8 * 2048 / (rows_s * 8 * 2048 / T), "unit": "tokens/s",
+                             "sample": f"conv + scan preparation + gated RMSNorm tail, forward + backward, of 1 x {T} "
+                                       f"rows (1/32 of the rows), {rows_s * 1e3:.1f} ms, scaled linearly; "
+                                       "GEMMs and the scan itself not included"}}
 
 
 def run_reference_arm(args, rank):
@@ -407,6 +462,7 @@ def main():
                              + measure.measure_scanprep(10, dev, batch=bshare)
                              + measure.measure_tail(10, dev, batch=bshare),
             "scan_d_state_128": measure.measure_scan_n128(10, dev) if world == 1 else None,
+            "cpu_baseline": cpu_baseline_others() if (world == 1 and not args.no_cpu_baseline) else None,
             "note": "config 3: 1024 consecutive tokens, fresh inputs per token; config 2: batch "
                     f"{bshare} per GPU (8 sharded over {world} rank(s)); figures of rank 0's GPU",
         }
