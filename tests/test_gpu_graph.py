@@ -43,6 +43,7 @@ def _refill(dst_case, src_case):
 
 @pytest.mark.parametrize("path,dtype,shape", [
     ("tc", torch.bfloat16, (2, 3, 300, 64, 64)),      # tensor-core kernels, ragged last chunk
+    ("tc", torch.bfloat16, (2, 2, 200, 64, 128)),     # two column blocks: strided device copies inside the capture
     ("simt", torch.float32, (2, 2, 130, 32, 16)),     # float32-exact kernels
 ])
 def test_scan_forward_and_backward_replay_from_a_graph(path, dtype, shape):
@@ -114,3 +115,20 @@ def test_decode_steps_replay_from_a_graph_and_update_the_state_in_place():
     assert torch.equal(ys, want)
     assert torch.equal(state, eager_state)
     assert not torch.equal(state, state0)
+
+
+def test_mixer_forward_with_forked_row_kernels_replays_from_a_graph():
+    """A sequence-sized mixer forward launches the three scan-preparation kernels on side streams between a
+    fork and a join; inside a capture those become edges of the graph."""
+    import slinoss_b200 as sb
+    torch.manual_seed(0)
+    m = sb.SLinOSSMixer(256, d_state=64, expand=2, d_head=64, d_conv=4, chunk_size=64).to(DEV).to(torch.bfloat16)
+    x = torch.randn(2, 2048, 256, device=DEV, dtype=torch.bfloat16)      # batch * T >= the fork threshold
+    other = torch.randn_like(x)
+    with torch.no_grad():
+        graph, out = _capture(lambda: m(x))
+        x.copy_(other)
+        graph.replay()
+        torch.cuda.synchronize()
+        want = m(other)
+    assert torch.equal(out, want)
