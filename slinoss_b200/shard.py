@@ -126,10 +126,14 @@ class GradBucketReducer:
     which is the order in which the backward pass finishes their gradients.  A
     ``post_accumulate_grad`` hook counts the gradients of a bucket; the last one packs the bucket
     into its flat buffer on a side stream (ordered after the stream that produced the gradients)
-    and starts ``all_reduce(SUM)`` there without waiting.  ``finish()`` starts whatever is left
+    and starts the all-reduce there without waiting.  ``finish()`` starts whatever is left
     (a parameter that got no gradient counts as zeros, so that every rank issues the same
-    collectives), waits, writes ``sum / world`` back into every ``p.grad`` and orders the calling
-    stream after all of it.  With no process group the class does nothing (world size 1).
+    collectives), waits and orders the calling stream after all of it.  The averaged gradients are
+    left in ``p.grad`` as VIEWS of the buckets' flat buffers (no copy back: the buffers are refilled
+    by the next backward pass, by which time the optimizer has consumed them); the average is taken
+    by the collective itself where the backend has ``ReduceOp.AVG`` (NCCL), else by one in-place
+    division per bucket.  With a ``reduce_dtype`` other than the parameters' the result is copied
+    back instead.  With no process group the class does nothing (world size 1).
 
     Works with ``nccl`` (CUDA tensors, real overlap) and ``gloo`` (CPU tensors)."""
 
@@ -142,6 +146,8 @@ class GradBucketReducer:
         self._bucket_of: dict[int, dict] = {}
         self._hooks = []
         self._stream = None
+        # the collective averages by itself where the backend can (NCCL); gloo has no AVG
+        self._avg = _active(group) and dist.get_backend(group) == "nccl"
         open_bucket: dict = {}
         for p in reversed(self.params):
             dt = reduce_dtype or p.dtype
@@ -190,7 +196,8 @@ class GradBucketReducer:
                 else:
                     dst.copy_(p.grad.reshape(-1))
                 off += n
-            b["handle"] = dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            op = dist.ReduceOp.AVG if self._avg else dist.ReduceOp.SUM
+            b["handle"] = dist.all_reduce(b["flat"], op=op, group=self.group, async_op=True)
 
         if side is None:
             pack_and_start()
@@ -214,11 +221,17 @@ class GradBucketReducer:
             ctx = torch.cuda.stream(side) if side is not None else _NullContext()
             with ctx:
                 b["handle"].wait()
+                if not self._avg:
+                    b["flat"].div_(n)
                 off = 0
                 for p in b["params"]:
                     k = p.numel()
+                    piece = b["flat"][off:off + k].view(p.shape)
                     if p.grad is not None:
-                        p.grad.copy_((b["flat"][off:off + k] / n).view_as(p.grad))
+                        if piece.dtype == p.dtype:
+                            p.grad = piece              # a view of the bucket: no copy back
+                        else:
+                            p.grad.copy_(piece)
                     off += k
             b["handle"], b["ready"] = None, 0
         if self._stream is not None:
