@@ -139,14 +139,23 @@ def _lm_worker(rank, store_path, out_path):
         reducer = shard.GradBucketReducer(model.parameters(), bucket_bytes=2048)
         bucketed = grads_of(mine, reducer)
         again = grads_of(mine, reducer)                        # the reducer is reusable step after step
+        # the averaged gradients are left as views of the buckets (no copy back)
+        b0 = reducer.buckets[0]
+        lo, hi = b0["flat"].data_ptr(), b0["flat"].data_ptr() + b0["flat"].numel() * b0["flat"].element_size()
+        views = all(lo <= q.grad.data_ptr() < hi for q in b0["params"] if q.grad is not None)
         reducer.remove()
+        wide = shard.GradBucketReducer(model.parameters(), bucket_bytes=4096, reduce_dtype=torch.float64)
+        in_double = grads_of(mine, wide)                       # summed in another type: copied back instead
+        wide.remove()
+        errs_wide = [_rel(a.numpy(), b.numpy()) for a, b in zip(in_double, flat) if b is not None]
         pairs = [(a, b, c, d) for a, b, c, d in zip(bucketed, flat, full, again) if c is not None]
         errs_flat = [_rel(a.numpy(), b.numpy()) for a, b, _, _ in pairs]
         errs_full = [_rel(a.numpy(), c.numpy()) for a, _, c, _ in pairs]
         errs_again = [_rel(a.numpy(), d.numpy()) for a, _, _, d in pairs]
         if rank == 0:
             np.savez(out_path, errs_flat=np.array(errs_flat), errs_full=np.array(errs_full),
-                     errs_again=np.array(errs_again), n_buckets=len(reducer.buckets))
+                     errs_again=np.array(errs_again), n_buckets=len(reducer.buckets), views=views,
+                     errs_wide=np.array(errs_wide))
     finally:
         dist.destroy_process_group()
 
@@ -158,6 +167,7 @@ def test_bucketed_gradient_allreduce_equals_flat_averaging_and_the_full_batch(tm
     assert int(r["n_buckets"]) > 10
     assert r["errs_flat"].max() <= 1e-6, r["errs_flat"]       # same sums, same order of ranks
     assert r["errs_again"].max() == 0.0
+    assert bool(r["views"]) and r["errs_wide"].max() <= 1e-6
     # equal shards: the mean of the ranks' mean-losses is the full-batch mean-loss
     assert r["errs_full"].max() <= 2e-5, r["errs_full"]
 
