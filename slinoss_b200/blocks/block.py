@@ -70,11 +70,12 @@ class SLinOSSBlock(nn.Module):
         return self._add(x, self._drop(self.ffn(apply_norm(self.ffn_norm, x))))
 
     def forward(self, x, *, state: SLinOSSBlockState | None = None, return_state: bool = False,
-                context=None):
+                context=None, sequence_group=None):
         if x.ndim != 3 or x.shape[-1] != self.d_model:
             raise ValueError(f"Expected x shape (batch, T, {self.d_model}), got {tuple(x.shape)}.")
+        extra = {} if sequence_group is None else {"sequence_group": sequence_group}
         mixed = self.mixer(apply_norm(self.mixer_norm, x),
-                           state=None if state is None else state.mixer, return_state=return_state)
+                           state=None if state is None else state.mixer, return_state=return_state, **extra)
         nxt = None
         if return_state:
             mixed, mixer_state = mixed

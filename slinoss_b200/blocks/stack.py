@@ -40,10 +40,19 @@ class SLinOSSStack(nn.Module):
                              f"Got {len(state.layers)} state layers for {len(self.blocks)} blocks.")
 
     def forward(self, x, *, state: SLinOSSStackState | None = None, return_state: bool = False,
-                context=None):
+                context=None, sequence_group=None):
+        """``sequence_group``: see ``SLinOSSMixer.forward`` (the time axis of ``x`` sharded over the ranks of a
+        process group; norms and FFN branches are per token, only the mixers exchange anything)."""
         if x.ndim != 3 or x.shape[-1] != self.d_model:
             raise ValueError(f"Expected x shape (batch, T, {self.d_model}), got {tuple(x.shape)}.")
         hidden = x
+        if sequence_group is not None:
+            if state is not None or return_state or (self.config.gradient_checkpointing and self.training):
+                raise ValueError("sequence_group cannot be combined with a streaming state or with "
+                                 "gradient checkpointing (its exchanges are collectives).")
+            for block in self.blocks:
+                hidden = block(hidden, context=context, sequence_group=sequence_group)
+            return self._final(hidden).to(dtype=x.dtype)
         if self.config.gradient_checkpointing and self.training:
             if state is not None or return_state:
                 raise ValueError("gradient_checkpointing in SLinOSSStack requires "

@@ -126,9 +126,17 @@ class SLinOSSMixer(nn.Module):
         return self.scanprep(value, params, bc), nstate
 
     def forward(self, x: torch.Tensor, *, state: SLinOSSMixerState | None = None,
-                return_state: bool = False):
+                return_state: bool = False, sequence_group=None):
+        """``sequence_group`` (not part of the reference's signature): a ``torch.distributed`` process group
+        over whose ranks the TIME axis of ``x`` is sharded in rank order.  Each rank passes its slice and gets
+        its slice of the output; the causal conv takes its left context from the previous rank and the scan
+        runs as ``v2x2ssd_sequence_parallel``.  Streaming state is not combined with it."""
         _require(x.ndim == 3 and x.shape[-1] == self.d_model,
                  f"Expected x shape (batch, T, {self.d_model}), got {tuple(x.shape)}.")
+        if sequence_group is not None:
+            _require(state is None and not return_state,
+                     "sequence_group cannot be combined with a streaming state.")
+            return self._forward_sequence_parallel(x, sequence_group)
         batch, T, _ = map(int, x.shape)
         if T == 0:
             empty = x.new_empty((batch, 0, self.d_model))
@@ -148,6 +156,21 @@ class SLinOSSMixer(nn.Module):
         if scan_state is None:
             return out
         return out, SLinOSSMixerState(conv=conv_state, scan=scan_state)
+
+    def _forward_sequence_parallel(self, x: torch.Tensor, group):
+        from ..ops.v2x2ssd.sequence_parallel import previous_rank_value, v2x2ssd_sequence_parallel
+        batch, T, _ = map(int, x.shape)
+        halo = self.d_conv - 1
+        _require(T >= max(halo, 1), f"every rank needs at least {max(halo, 1)} tokens of the sequence.")
+        gate, value_proj, params, bc_flat = split_mixer_projection(
+            x, self.in_proj.weight, d_inner=self.d_inner, param_proj_dim=self.param_proj_dim)
+        bc = bc_flat.view(batch, T, self.bc_groups, self.scanprep.bc_param_rows, self.d_state)
+        conv_state = None
+        if halo > 0:   # the last inputs of the previous rank's slice are this slice's left context
+            conv_state = previous_rank_value(value_proj[:, T - halo:, :], group).transpose(1, 2).contiguous()
+        s, _ = self._frontend(value_proj, params, bc, conv_state, False)
+        Y, _, _, _ = v2x2ssd_sequence_parallel(s.U, s.M, s.K, s.B, s.C, chunk_size=self.chunk_size, group=group)
+        return mixer_tail(Y, gate, self.out_norm, self.out_proj, skip_input=s.U, d_skip=self.d_skip)
 
     def step(self, x: torch.Tensor, state: SLinOSSMixerState | None = None, *,
              inplace: bool | None = None):

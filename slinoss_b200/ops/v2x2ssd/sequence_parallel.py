@@ -44,6 +44,18 @@ class _Gather(torch.autograd.Function):
         return g[ctx.rank], None
 
 
+def previous_rank_value(x, group=None):
+    """``x`` of the previous rank of ``group`` (zeros on rank 0), differentiable: what a rank needs of its
+    predecessor's slice (the last token of B and U for the scan's carried taps, the last rows of the conv
+    input for the causal conv).  Every rank must call it, and its backward, together."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    allx = _Gather.apply(x.contiguous(), group)
+    pick = torch.zeros(world, device=x.device, dtype=x.dtype)
+    if rank > 0:
+        pick[rank - 1] = 1
+    return torch.einsum("w,w...->...", pick, allx)
+
+
 def _scale_state(pi, z):
     """Complex scalar ``pi (batch, heads, 2)`` times the interleaved complex state ``z (batch, heads, P, 2N)``."""
     zz = z.reshape(*z.shape[:-1], -1, 2)
@@ -83,13 +95,8 @@ def v2x2ssd_sequence_parallel(U, M, K, B, C, *, chunk_size=64, group=None, initi
     if U.shape[2] < 1:
         raise ValueError("every rank needs at least one token of the sequence.")
     # ---- the token before each slice: the previous rank's last (b, u) --------------------------------
-    b_all = _Gather.apply(B[:, :, -1, :].contiguous(), group)          # (W, batch, groups, 2N)
-    u_all = _Gather.apply(U[:, :, -1, :].contiguous(), group)          # (W, batch, heads, P)
-    pick = torch.zeros(world, device=U.device, dtype=b_all.dtype)
-    if rank > 0:
-        pick[rank - 1] = 1
-    Bp = torch.einsum("w,w...->...", pick, b_all)                      # zeros on rank 0, connected on every rank
-    Up = torch.einsum("w,w...->...", pick.to(u_all.dtype), u_all)
+    Bp = previous_rank_value(B[:, :, -1, :], group)                    # (batch, groups, 2N); zeros on rank 0,
+    Up = previous_rank_value(U[:, :, -1, :], group)                    # (batch, heads, P);   connected on every rank
     z_first = None
     if rank == 0:
         if B_prev is not None:
@@ -121,4 +128,4 @@ def v2x2ssd_sequence_parallel(U, M, K, B, C, *, chunk_size=64, group=None, initi
     return Y, end, B[:, :, -1, :], U[:, :, -1, :]
 
 
-__all__ = ["transition_product", "v2x2ssd_sequence_parallel"]
+__all__ = ["previous_rank_value", "transition_product", "v2x2ssd_sequence_parallel"]

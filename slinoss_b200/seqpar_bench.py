@@ -23,6 +23,63 @@ from .ops.v2x2ssd import v2x2ssd_cute, v2x2ssd_sequence_parallel
 from .synthetic import make_scan_case
 
 
+def stack_leg(args, world, rank, dev, barrier):
+    """Forward + backward of a stack of blocks whose input is sharded in time (``sequence_group``), against the
+    same stack on rank 0 over the whole sequence."""
+    import torch.distributed as dist
+    import slinoss_b200 as sb
+    torch.manual_seed(0)
+    blk = sb.SLinOSSBlockConfig(d_model=1024, mixer=sb.SLinOSSMixerConfig(d_state=64, expand=2.0, d_head=64),
+                                ffn=sb.SLinOSSMLPConfig(kind="gelu", expand=4.0))
+    stack = sb.SLinOSSStack(sb.SLinOSSStackConfig.uniform(blk, n_layers=args.stack), device=dev,
+                            dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    batch = min(args.batch, 2)
+    x_full = torch.randn(batch, args.T * world, 1024, generator=g).to(torch.bfloat16)
+    w_full = torch.randn(batch, args.T * world, 1024, generator=g).to(torch.bfloat16)
+    sl = slice(rank * args.T, (rank + 1) * args.T)
+    x = x_full[:, sl].to(dev).requires_grad_(True)
+    w = w_full[:, sl].to(dev)
+    group = dist.group.WORLD if world > 1 else None
+
+    def step():
+        stack.zero_grad(set_to_none=True)
+        out = stack(x, sequence_group=group)
+        (gx,) = torch.autograd.grad((out.float() * w.float()).sum(), x)
+        return out, gx
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = shard.reduce_step_ms(e0.elapsed_time(e1) / args.steps, dev)
+    out, gx = step()
+    err = None
+    if rank == 0 and args.T * world <= 16384:
+        xw = x_full.to(dev).requires_grad_(True)
+        ow = stack(xw)
+        (gw,) = torch.autograd.grad((ow.float() * w_full.to(dev).float()).sum(), xw)
+        rel = lambda a, b: float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+        err = max(rel(out.detach(), ow[:, sl].detach()), rel(gx, gw[:, sl]))
+    if rank == 0:
+        line = {"what": f"stack of {args.stack} blocks, forward + backward, time axis sharded over the GPUs",
+                "config": f"batch {batch} x T {args.T} per GPU ({args.T * world} in all), d_model 1024, 32 heads x 64, "
+                          "N 64, GELU FFN x4, bf16",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "tokens_per_s": batch * args.T * world / (ms * 1e-3),
+                "max_rel_err_vs_single_gpu_stack_on_the_whole_sequence": err}
+        text = json.dumps(line)
+        print(text, flush=True)
+        if args.out:
+            with open(args.out, "w") as f:
+                f.write(text + "\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=10)
@@ -30,6 +87,9 @@ def main():
     ap.add_argument("--T", type=int, default=4096, help="tokens per rank")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--stack", type=int, default=0, metavar="LAYERS",
+                    help="time a stack of LAYERS blocks (d_model 1024, 32 heads x 64, N 64, GELU FFN x4) on the "
+                         "sharded sequence instead of the bare scan")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -47,6 +107,11 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.stack > 0:
+        stack_leg(args, world, rank, dev, barrier)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     check = args.T * world <= 16384
     if check:   # the same long sequence on every rank (same seed), of which a rank keeps its slice
         full = make_scan_case(args.batch, args.heads, args.T * world, 64, 64, dtype=torch.bfloat16, seed=0)

@@ -239,3 +239,53 @@ def test_sequence_sharded_over_two_ranks_equals_the_whole_sequence(tmp_path):
     mp.spawn(_seqpar_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
     errs = np.load(out)["errs"]
     assert errs.max() <= 2e-5, errs
+
+
+# ---------------------------------------------------------------------------------------
+def _mixer_seqpar_worker(rank, store_path, out_path):
+    """A two-block stack on a sequence sharded in time: every mixer's conv takes its left context from the
+    previous rank, its scan the start state and taps; outputs and gradients must equal the single-process full
+    sequence."""
+    _init(rank, store_path)
+    import slinoss_b200 as sb
+    try:
+        torch.manual_seed(13)
+        blk = sb.SLinOSSBlockConfig(d_model=16, mixer=sb.SLinOSSMixerConfig(d_state=8, expand=2.0, d_head=8,
+                                                                            chunk_size=8),
+                                    ffn=sb.SLinOSSMLPConfig(kind="gelu", expand=2.0, multiple_of=8))
+        mixer = sb.SLinOSSStack(sb.SLinOSSStackConfig.uniform(blk, n_layers=2))    # two blocks: two exchanges deep
+        x = torch.randn(2, 40, 16)
+        w = torch.randn(2, 40, 16)
+        cut = [0, 17, 40]                                        # ragged slices
+
+        mixer.zero_grad(set_to_none=True)
+        xf = x.clone().requires_grad_(True)
+        out_full = mixer(xf)
+        (out_full * w).sum().backward()
+        full = [p.grad.clone() for p in mixer.parameters()]
+        gx_full = xf.grad.clone()
+
+        mixer.zero_grad(set_to_none=True)
+        sl = slice(cut[rank], cut[rank + 1])
+        xs = x[:, sl].clone().requires_grad_(True)
+        out = mixer(xs, sequence_group=dist.group.WORLD)
+        (out * w[:, sl]).sum().backward()                        # every rank: the exchanges' backward is collective
+        local = [p.grad.clone() for p in mixer.parameters()]
+        for g in local:                                          # every rank saw only its tokens: SUM over ranks
+            dist.all_reduce(g, op=dist.ReduceOp.SUM)
+        errs = [_rel(out.detach().numpy(), out_full[:, sl].detach().numpy()),
+                _rel(xs.grad.numpy(), gx_full[:, sl].numpy())]
+        errs += [_rel(a.numpy(), b.numpy()) for a, b in zip(local, full)]
+        gathered = [None] * WORLD
+        dist.all_gather_object(gathered, errs)
+        if rank == 0:
+            np.savez(out_path, errs=np.array(gathered))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_stack_on_a_time_sharded_sequence_equals_the_whole_sequence(tmp_path):
+    store, out = tmp_path / "store", tmp_path / "out.npz"
+    mp.spawn(_mixer_seqpar_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
+    errs = np.load(out)["errs"]
+    assert errs.max() <= 5e-5, errs
