@@ -56,15 +56,36 @@ class SLinOSSLM(nn.Module):
             raise ValueError(f"Expected ids shape (batch, T), got {tuple(ids.shape)}.")
         return F.linear(self.hidden(ids), self.token_embed.weight)
 
-    def hidden(self, ids: torch.Tensor) -> torch.Tensor:
-        return self.backbone(self.token_embed(ids))
+    def hidden(self, ids: torch.Tensor, *, sequence_group=None) -> torch.Tensor:
+        x = self.token_embed(ids)
+        return self.backbone(x) if sequence_group is None else self.backbone(x, sequence_group=sequence_group)
 
-    def loss(self, ids: torch.Tensor) -> torch.Tensor:
+    def loss(self, ids: torch.Tensor, *, sequence_group=None) -> torch.Tensor:
         """Mean next-token cross-entropy of ``ids`` (float32).  The last position has no target, so
-        its row is dropped before the head GEMM rather than from the logits."""
-        rows = self.hidden(ids)[:, :-1].reshape(-1, self.d_model)
-        logits = F.linear(rows, self.token_embed.weight)
-        return F.cross_entropy(logits.float(), ids[:, 1:].reshape(-1))
+        its row is dropped before the head GEMM rather than from the logits.
+
+        With ``sequence_group`` the TIME axis of ``ids`` is sharded over the ranks of that process group in rank
+        order: a rank's last position is scored against the next rank's first token, and the value returned is
+        this rank's SHARE of the mean over the whole sequence (its summed cross-entropy over the global number
+        of positions) - the shares add up to the loss and their gradients add up to its gradient, so parameter
+        gradients are to be SUMMED over the group."""
+        if sequence_group is None:
+            rows = self.hidden(ids)[:, :-1].reshape(-1, self.d_model)
+            logits = F.linear(rows, self.token_embed.weight)
+            return F.cross_entropy(logits.float(), ids[:, 1:].reshape(-1))
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(sequence_group), dist.get_rank(sequence_group)
+        firsts = [torch.empty_like(ids[:, :1]) for _ in range(world)]
+        dist.all_gather(firsts, ids[:, :1].contiguous(), group=sequence_group)
+        hidden = self.hidden(ids, sequence_group=sequence_group)
+        if rank + 1 < world:
+            rows, targets = hidden, torch.cat((ids[:, 1:], firsts[rank + 1]), dim=1)
+        else:
+            rows, targets = hidden[:, :-1], ids[:, 1:]
+        count = torch.tensor([targets.numel()], device=ids.device, dtype=torch.float64)
+        dist.all_reduce(count, group=sequence_group)
+        logits = F.linear(rows.reshape(-1, self.d_model), self.token_embed.weight)
+        return F.cross_entropy(logits.float(), targets.reshape(-1), reduction="sum") / count.item()
 
 
 def decay_groups(model: nn.Module, weight_decay: float):
@@ -83,8 +104,13 @@ class DataParallelTrainer:
     One instance per rank; every rank feeds its own shard of the batch."""
 
     def __init__(self, model: SLinOSSLM, *, lr: float = 3e-4, weight_decay: float = 0.05,
-                 grad_clip: float = 1.0, bucket_bytes: int = 32 << 20, reduce: bool = True) -> None:
+                 grad_clip: float = 1.0, bucket_bytes: int = 32 << 20, reduce: bool = True,
+                 sequence_parallel: bool = False) -> None:
+        """``sequence_parallel``: the ranks do not hold different sequences but consecutive TIME slices of the
+        same sequences (``ids`` = this rank's slice); the loss shares' gradients then ADD over the ranks, which
+        the averaging reducer delivers when every share is scaled by the world size first."""
         self.model, self.grad_clip = model, grad_clip
+        self.sequence_parallel = bool(sequence_parallel)
         fused = self.fused = next(model.parameters()).is_cuda
         self.opt = torch.optim.AdamW(decay_groups(model, weight_decay), lr=lr, betas=(0.9, 0.95),
                                      fused=fused)
@@ -93,14 +119,24 @@ class DataParallelTrainer:
 
     def step(self, ids: torch.Tensor) -> torch.Tensor:
         self.opt.zero_grad(set_to_none=True)
-        loss = self.model.loss(ids)
-        loss.backward()
+        if self.sequence_parallel:
+            import torch.distributed as dist
+            loss = self.model.loss(ids, sequence_group=dist.group.WORLD)
+            (loss * dist.get_world_size()).backward()
+        else:
+            loss = self.model.loss(ids)
+            loss.backward()
         if self.reducer is not None:
             self.reducer.finish()
         if self.grad_clip and self.grad_clip > 0:
             self._clip()
         self.opt.step()
-        return loss.detach()
+        loss = loss.detach()
+        if self.sequence_parallel:       # the shares add up to the loss of the whole sequences
+            import torch.distributed as dist
+            loss = loss.clone()
+            dist.all_reduce(loss)
+        return loss
 
     def _clip(self) -> None:
         """Global-norm clipping.  With the fused optimizer the coefficient is not applied as a pass over

@@ -71,6 +71,9 @@ def main():
     ap.add_argument("--bucket-mb", type=int, default=32)
     ap.add_argument("--ffn-remat", choices=["full", "rows", "none"], default=None,
                     help="what the FFN branch rebuilds in the backward pass (default: the block's own)")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="the ranks hold consecutive time slices of the same --batch-per-gpu sequences (context "
+                         "length = --seq x ranks) instead of different sequences")
     ap.add_argument("--kernel-table", type=int, default=0, metavar="ROWS",
                     help="after the timed steps, profile two more steps (torch profiler) on rank 0 and print "
                          "the ROWS kernels with the most device time to stderr")
@@ -101,10 +104,17 @@ def main():
             blk.ffn_remat = args.ffn_remat
     ffn_remat = model.backbone.blocks[0].ffn_remat
     n_params = sum(p.numel() for p in model.parameters())
-    g = torch.Generator(device=dev).manual_seed(shard.rank_seed(1, rank))
-    ids = torch.randint(0, args.vocab, (args.batch_per_gpu, args.seq), generator=g, device=dev)
+    seqpar = args.sequence_parallel and world > 1
+    if seqpar:   # the same long sequences on every rank, of which a rank keeps its time slice
+        g = torch.Generator(device=dev).manual_seed(1)
+        ids = torch.randint(0, args.vocab, (args.batch_per_gpu, args.seq * world), generator=g, device=dev)
+        ids = ids[:, rank * args.seq:(rank + 1) * args.seq].contiguous()
+    else:
+        g = torch.Generator(device=dev).manual_seed(shard.rank_seed(1, rank))
+        ids = torch.randint(0, args.vocab, (args.batch_per_gpu, args.seq), generator=g, device=dev)
 
-    trainer = DataParallelTrainer(model, bucket_bytes=args.bucket_mb << 20, reduce=world > 1)
+    trainer = DataParallelTrainer(model, bucket_bytes=args.bucket_mb << 20, reduce=world > 1,
+                                  sequence_parallel=seqpar)
     ms, losses = timed_steps(trainer, ids, args.steps, args.warmup, barrier)
     ms = shard.reduce_step_ms(ms, dev)
     ms_plain = None
@@ -126,7 +136,9 @@ def main():
             "config": {"layers": args.layers, "d_model": args.d_model, "heads": args.d_model // 64,
                        "d_state": 64, "vocab": args.vocab, "seq": args.seq,
                        "batch_per_gpu": args.batch_per_gpu, "global_batch": world * args.batch_per_gpu,
-                       "dtype": "bf16", "parameters": n_params, "ffn_remat": ffn_remat, "data": "synthetic uniform ids"},
+                       "dtype": "bf16", "parameters": n_params, "ffn_remat": ffn_remat,
+                       "sharding": (f"sequence parallel: {args.batch_per_gpu} sequences of {args.seq * world} tokens, "
+                                    "one time slice per GPU") if seqpar else "data parallel", "data": "synthetic uniform ids"},
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
             "ms_per_step_without_allreduce": ms_plain,

@@ -289,3 +289,41 @@ def test_stack_on_a_time_sharded_sequence_equals_the_whole_sequence(tmp_path):
     mp.spawn(_mixer_seqpar_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
     errs = np.load(out)["errs"]
     assert errs.max() <= 5e-5, errs
+
+
+# ---------------------------------------------------------------------------------------
+def _lm_seqpar_worker(rank, store_path, out_path):
+    """The LM loss on token ids sharded in time: the shares add up to the single-process loss, their
+    gradients (summed over ranks) to its gradient."""
+    _init(rank, store_path)
+    from slinoss_b200.lm import SLinOSSLM, lm_stack_config
+    try:
+        torch.manual_seed(7)
+        model = SLinOSSLM(50, lm_stack_config(d_model=16, n_layers=2, d_state=4, d_head=8, ffn_expand=2.0))
+        ids = torch.randint(0, 50, (3, 30))
+        model.zero_grad(set_to_none=True)
+        full = model.loss(ids)
+        full.backward()
+        want = [p.grad.clone() for p in model.parameters()]
+        cut = [0, 13, 30]
+        model.zero_grad(set_to_none=True)
+        share = model.loss(ids[:, cut[rank]:cut[rank + 1]], sequence_group=dist.group.WORLD)
+        share.backward()
+        got = [p.grad.clone() for p in model.parameters()]
+        total = share.detach().clone()
+        dist.all_reduce(total)
+        for g in got:
+            dist.all_reduce(g)
+        if rank == 0:
+            errs = [abs(float(total) - float(full)) / abs(float(full))]
+            errs += [_rel(a.numpy(), b.numpy()) for a, b in zip(got, want)]
+            np.savez(out_path, errs=np.array(errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_lm_loss_on_time_sharded_ids_adds_up_to_the_whole_sequence(tmp_path):
+    store, out = tmp_path / "store", tmp_path / "out.npz"
+    mp.spawn(_lm_seqpar_worker, args=(str(store), str(out)), nprocs=WORLD, join=True)
+    errs = np.load(out)["errs"]
+    assert errs.max() <= 5e-5, errs
