@@ -50,18 +50,14 @@ def previous_rank_value(x, group=None):
     input for the causal conv).  Every rank must call it, and its backward, together."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     allx = _Gather.apply(x.contiguous(), group)
-    pick = torch.zeros(world, device=x.device, dtype=x.dtype)
-    if rank > 0:
-        pick[rank - 1] = 1
-    return torch.einsum("w,w...->...", pick, allx)
+    # rank 0 multiplies the (unused) gathered rows by zero: its autograd graph stays attached to the gather
+    return (allx[rank - 1] if rank > 0 else allx[0] * 0).contiguous()
 
 
 def _scale_state(pi, z):
-    """Complex scalar ``pi (batch, heads, 2)`` times the interleaved complex state ``z (batch, heads, P, 2N)``."""
-    zz = z.reshape(*z.shape[:-1], -1, 2)
-    pr, pim = pi[..., 0, None, None], pi[..., 1, None, None]
-    out = torch.stack((pr * zz[..., 0] - pim * zz[..., 1], pr * zz[..., 1] + pim * zz[..., 0]), -1)
-    return out.reshape(z.shape)
+    """Complex scalar ``pi (batch, heads)`` (complex64) times the interleaved complex state ``z (batch, heads, P, 2N)``."""
+    zc = torch.view_as_complex(z.reshape(*z.shape[:-1], -1, 2))
+    return torch.view_as_real(zc * pi[..., None, None]).reshape(z.shape)
 
 
 def transition_product(M):
@@ -72,6 +68,20 @@ def transition_product(M):
     angle = torch.atan2(m[..., 1], m[..., 0]).sum(-1)
     mag = torch.exp(logmag)
     return torch.stack((mag * torch.cos(angle), mag * torch.sin(angle)), -1).float()
+
+
+def _gather_packed(parts, group):
+    """One differentiable gather for several per-batch tensors of one dtype: returns, per tensor, the stack over
+    ranks ``(W, *shape)``."""
+    batch = parts[0].shape[0]
+    flat = torch.cat([p.reshape(batch, -1) for p in parts], dim=1)
+    allx = _Gather.apply(flat, group)                                  # (W, batch, sum of widths)
+    outs, off = [], 0
+    for p in parts:
+        n = p[0].numel()
+        outs.append(allx[:, :, off:off + n].reshape(allx.shape[0], *p.shape))
+        off += n
+    return outs
 
 
 @torch.compiler.disable
@@ -94,9 +104,12 @@ def v2x2ssd_sequence_parallel(U, M, K, B, C, *, chunk_size=64, group=None, initi
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     if U.shape[2] < 1:
         raise ValueError("every rank needs at least one token of the sequence.")
-    # ---- the token before each slice: the previous rank's last (b, u) --------------------------------
-    Bp = previous_rank_value(B[:, :, -1, :], group)                    # (batch, groups, 2N); zeros on rank 0,
-    Up = previous_rank_value(U[:, :, -1, :], group)                    # (batch, heads, P);   connected on every rank
+    # ---- the token before each slice: the previous rank's last (b, u), one exchange for both ------------
+    b_all, u_all = _gather_packed([B[:, :, -1, :], U[:, :, -1, :]], group)
+    if rank > 0:
+        Bp, Up = b_all[rank - 1].contiguous(), u_all[rank - 1].contiguous()   # (batch, groups, 2N), (batch, heads, P)
+    else:                                                              # zeros, attached to the gather's graph
+        Bp, Up = (b_all[0] * 0).contiguous(), (u_all[0] * 0).contiguous()
     z_first = None
     if rank == 0:
         if B_prev is not None:
@@ -105,25 +118,21 @@ def v2x2ssd_sequence_parallel(U, M, K, B, C, *, chunk_size=64, group=None, initi
     # ---- pass A: the slice from a zero state ------------------------------------------------------------
     _, f0, _, _ = v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=z_first, B_prev=Bp, U_prev=Up,
                                output_dtype=torch.float32, return_state=True, path=path)
-    pi = transition_product(M)
-    f_all = _Gather.apply(f0.float().contiguous(), group)              # (W, batch, heads, P, 2N)
-    pi_all = _Gather.apply(pi.contiguous(), group)                     # (W, batch, heads, 2)
-    # ---- the state at the start of this rank's slice ------------------------------------------------------
-    carry = torch.zeros_like(f_all[0])
-    start = end = None
-    for q in range(world):
-        if q == rank:
-            start = carry
-        carry = _scale_state(pi_all[q], carry) + f_all[q]
-        if q == rank:
-            end = carry                                                # float32 end state of this slice
-    # keep every rank's autograd graph attached to both gathers (whose backward is a collective), whatever
-    # part of them this rank's result uses
-    start = start + 0.0 * (f_all.sum(0) + _scale_state(pi_all.sum(0), torch.ones_like(carry)))
+    f_all, pi_all = _gather_packed([f0.float(), transition_product(M)], group)   # (W, batch, heads, P, 2N), (W, batch, heads, 2)
+    pi_c = torch.view_as_complex(pi_all.contiguous())                  # (W, batch, heads)
+    # ---- the state at the start and at the end of this rank's slice -----------------------------------------
+    # (the term multiplied by zero keeps every rank's autograd graph attached to the gather, whose backward is
+    # a collective, whatever part of it this rank's result uses)
+    start = f_all[rank] * 0 if rank == 0 else f_all[0]
+    for q in range(1, rank):
+        start = _scale_state(pi_c[q], start) + f_all[q]
+    end = f_all[0] if rank == 0 else _scale_state(pi_c[rank], start) + f_all[rank]
+    if rank + 1 < world:
+        start = start + 0.0 * (f_all[rank + 1:].sum() + pi_all[rank + 1:].sum())
     if rank == 0 and initial_states is not None:
         start = start + initial_states.float()
     # ---- pass B: the slice from its true start state -------------------------------------------------------
-    Y = v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=start, B_prev=Bp, U_prev=Up,
+    Y = v2x2ssd_cute(U, M, K, B, C, chunk_size=chunk_size, initial_states=start.contiguous(), B_prev=Bp, U_prev=Up,
                      output_dtype=output_dtype, return_state=False, path=path)
     return Y, end, B[:, :, -1, :], U[:, :, -1, :]
 
