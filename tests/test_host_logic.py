@@ -194,3 +194,21 @@ def test_measure_module_imports_without_a_gpu_and_refuses_to_run(monkeypatch):
     monkeypatch.setattr("sys.argv", ["measure"])
     with pytest.raises(SystemExit, match="no CPU path"):
         measure.main()
+
+
+def test_transition_product_matches_the_running_complex_product():
+    import torch
+    from slinoss_b200.ops.v2x2ssd.sequence_parallel import _scale_state, transition_product
+    g = torch.Generator().manual_seed(0)
+    r = 0.8 + 0.2 * torch.rand(2, 3, 500, generator=g, dtype=torch.float64)
+    th = (2 * torch.rand(2, 3, 500, generator=g, dtype=torch.float64) - 1) * torch.pi
+    M = torch.stack((r * torch.cos(th), r * torch.sin(th)), -1)
+    want = torch.view_as_complex(M.contiguous()).prod(-1)            # 0.9^500 ~ 1e-23: still a normal float64
+    got = torch.view_as_complex(transition_product(M.float()).double())
+    assert ((got - want).abs() / want.abs()).max() < 1e-4             # float32 inputs, float64 accumulation
+    # complex scalar times interleaved state
+    z = torch.randn(2, 3, 4, 10, generator=g)
+    pi = torch.view_as_complex(torch.randn(2, 3, 2, generator=g))
+    out = _scale_state(pi, z)
+    ref = torch.view_as_real(torch.view_as_complex(z.reshape(2, 3, 4, 5, 2)) * pi[..., None, None]).reshape(z.shape)
+    assert torch.equal(out, ref)
